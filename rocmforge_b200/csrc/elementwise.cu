@@ -1,0 +1,202 @@
+// Embedding gather, residual-add + RMSNorm, rotary position encoding fused with the
+// cache write, and SwiGLU.  Each kernel is templated on the compute dtype (float for
+// the true 32-bit path, bfloat16 for serving); the residual stream is 32-bit in both.
+//
+// What they compute follows maeddesg/ROCmForge's hip_kernels/norm.hip:18-84 (RMSNorm),
+// rope.hip:48-91 and attention.hip:1561-1621 (NeoX rotation fused with the cache
+// write), elementwise.hip:72-82 (SiLU, multiply) and the embedding gathers of
+// elementwise.hip:243-445; how they are launched and laid out is this library's own.
+#include "common.cuh"
+
+// ---------------------------------------------------------------- embedding
+// out[t, :] = table[ids[t], :] widened to 32-bit (the residual stream).
+template <typename T>
+__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                             float* __restrict__ out, int H, int V) {
+    const int t = blockIdx.x;
+    int id = ids[t];
+    id = id < 0 ? 0 : (id >= V ? V - 1 : id);   // ids are validated on the host; never read outside
+    const T* row = table + (size_t)id * H;
+    float* o = out + (size_t)t * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = Cvt<T>::to_f32(row[i]);
+}
+
+// ---------------------------------------------------------------- add + RMSNorm
+// v = h[row] + sum_s pending[s][row];  y = v * rsqrt(mean(v^2) + eps) * w.
+// pending_kind: 0 none, 1 = n_pending 32-bit partial sums [S, T, H] (split-K outputs,
+// added in index order), 2 = one [T, H] tensor in the compute dtype.
+// rows == nullptr: one block per token, h is updated in place.
+// rows != nullptr: block r reads token rows[r], writes y[r] and leaves h alone.
+template <typename T>
+__global__ void add_rmsnorm_kernel(float* __restrict__ h, const void* __restrict__ pending,
+                                   int pending_kind, int n_pending, size_t pending_stride,
+                                   const void* __restrict__ w, int w_is_f32, float eps,
+                                   T* __restrict__ y, const int* __restrict__ rows, int H) {
+    extern __shared__ float row_buf[];          // H floats + 33 for the reduction
+    float* red = row_buf + H;
+    const int r = blockIdx.x;
+    const int t = rows ? rows[r] : r;
+    float* hrow = h + (size_t)t * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = hrow[i];
+        if (pending_kind == 1) {
+            const float* p = reinterpret_cast<const float*>(pending) + (size_t)t * H + i;
+            for (int s = 0; s < n_pending; ++s) v += p[(size_t)s * pending_stride];
+        } else if (pending_kind == 2) {
+            v += Cvt<T>::to_f32(reinterpret_cast<const T*>(pending)[(size_t)t * H + i]);
+        }
+        row_buf[i] = v;
+        ss += v * v;
+    }
+    const float total = block_sum(ss, red);
+    const float inv = rsqrtf(total / (float)H + eps);
+    T* yrow = y + (size_t)r * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = row_buf[i];
+        if (!rows && pending_kind != 0) hrow[i] = v;
+        yrow[i] = Cvt<T>::from_f32(v * inv * load_vec(w, w_is_f32, i));
+    }
+}
+
+// ---------------------------------------------------------------- rotation + cache write
+// qkv: [T, (nh + 2*nkv) * hd] rows of q | k | v.  q is rotated in place; k is rotated and
+// v copied into the page of (slot, position): pages are [n_pages, nkv, RF_PAGE, hd].
+// The angle is float(pos) * inv_freq[i] in 32-bit; sincosf is the accurate one.
+template <typename T>
+__global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, int nh, int nkv, int hd,
+                                     const float* __restrict__ inv_freq,
+                                     const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                                     const int* __restrict__ seq_slot,
+                                     const int* __restrict__ block_table, int max_pages,
+                                     T* __restrict__ k_pages, T* __restrict__ v_pages, int write_kv) {
+    const int t = blockIdx.x;
+    const int pos = tok_pos[t];
+    const int half = hd >> 1;
+    T* row = qkv + (size_t)t * row_stride;
+    size_t page_base = 0;
+    if (write_kv) {
+        const int slot = seq_slot[tok_seq[t]];
+        const int page = block_table[(size_t)slot * max_pages + pos / RF_PAGE];
+        page_base = (size_t)page * nkv * RF_PAGE * hd + (size_t)(pos % RF_PAGE) * hd;
+    }
+    const int n_rot = (nh + nkv) * half;
+    for (int idx = threadIdx.x; idx < n_rot; idx += blockDim.x) {
+        const int head = idx / half, i = idx - head * half;
+        const float angle = (float)pos * inv_freq[i];
+        float s, c;
+        sincosf(angle, &s, &c);
+        T* x = row + (size_t)head * hd;
+        const float x0 = Cvt<T>::to_f32(x[i]), x1 = Cvt<T>::to_f32(x[i + half]);
+        const float r0 = x0 * c - x1 * s, r1 = x0 * s + x1 * c;
+        if (head < nh) {
+            x[i] = Cvt<T>::from_f32(r0);
+            x[i + half] = Cvt<T>::from_f32(r1);
+        } else if (write_kv) {
+            T* dst = k_pages + page_base + (size_t)(head - nh) * RF_PAGE * hd;
+            dst[i] = Cvt<T>::from_f32(r0);
+            dst[i + half] = Cvt<T>::from_f32(r1);
+        }
+    }
+    if (write_kv) {
+        const T* vsrc = row + (size_t)(nh + nkv) * hd;
+        for (int idx = threadIdx.x; idx < nkv * hd; idx += blockDim.x) {
+            const int head = idx / hd, i = idx - head * hd;
+            v_pages[page_base + (size_t)head * RF_PAGE * hd + i] = vsrc[idx];
+        }
+    }
+}
+
+// ---------------------------------------------------------------- SwiGLU
+// gu: [T, 2I] with gate_j at column 2j and up_j at column 2j+1 (the fused weight is
+// interleaved row by row at load time); a[t, j] = silu(gate) * up, evaluated in 32-bit.
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ a, size_t n_out, int I) {
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n_out;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / I, j = idx - t * I;
+        const float g = Cvt<T>::to_f32(gu[t * 2 * I + 2 * j]);
+        const float u = Cvt<T>::to_f32(gu[t * 2 * I + 2 * j + 1]);
+        a[idx] = Cvt<T>::from_f32(g / (1.f + expf(-g)) * u);
+    }
+}
+
+// ---------------------------------------------------------------- launchers
+template <typename T>
+static int launch_embed(const void* table, const int* ids, float* out, int T_, int H, int V, cudaStream_t st) {
+    if (T_ <= 0) return 0;
+    embed_kernel<T><<<T_, 256, 0, st>>>(reinterpret_cast<const T*>(table), ids, out, H, V);
+    RF_LAUNCH_CHECK();
+    return 0;
+}
+
+template <typename T>
+static int launch_add_rmsnorm(float* h, const void* pending, int kind, int n_pending, size_t pstride,
+                              const void* w, int w_is_f32, float eps, void* y, const int* rows,
+                              int n_rows, int H, cudaStream_t st) {
+    if (n_rows <= 0) return 0;
+    const size_t smem = (size_t)(H + 33) * sizeof(float);
+    if (smem > 200 * 1024) return RF_ERR_UNSUPPORTED;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel<T>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    const int threads = H >= 2048 ? 512 : 256;
+    add_rmsnorm_kernel<T><<<n_rows, threads, smem, st>>>(h, pending, kind, n_pending, pstride, w, w_is_f32,
+                                                         eps, reinterpret_cast<T*>(y), rows, H);
+    RF_LAUNCH_CHECK();
+    return 0;
+}
+
+template <typename T>
+static int launch_rope_kv_write(void* qkv, int row_stride, int nh, int nkv, int hd, const float* inv_freq,
+                                const int* tok_seq, const int* tok_pos, const int* seq_slot,
+                                const int* block_table, int max_pages, void* k_pages, void* v_pages,
+                                int write_kv, int T_, cudaStream_t st) {
+    if (T_ <= 0) return 0;
+    if (hd % 2) return RF_ERR_BAD_ARG;
+    rope_kv_write_kernel<T><<<T_, 256, 0, st>>>(reinterpret_cast<T*>(qkv), row_stride, nh, nkv, hd, inv_freq,
+                                                tok_seq, tok_pos, seq_slot, block_table, max_pages,
+                                                reinterpret_cast<T*>(k_pages), reinterpret_cast<T*>(v_pages),
+                                                write_kv);
+    RF_LAUNCH_CHECK();
+    return 0;
+}
+
+template <typename T>
+static int launch_swiglu(const void* gu, void* a, int T_, int I, cudaStream_t st) {
+    const size_t n = (size_t)T_ * I;
+    if (n == 0) return 0;
+    const int blocks = (int)((n + 255) / 256 > 148 * 16 ? 148 * 16 : (n + 255) / 256);
+    swiglu_kernel<T><<<blocks, 256, 0, st>>>(reinterpret_cast<const T*>(gu), reinterpret_cast<T*>(a), n, I);
+    RF_LAUNCH_CHECK();
+    return 0;
+}
+
+// dtype: 0 = float32, 1 = bfloat16
+extern "C" {
+int rf_embed(int dtype, const void* table, const int* ids, float* out, int T_, int H, int V, cudaStream_t st) {
+    return dtype == 0 ? launch_embed<float>(table, ids, out, T_, H, V, st)
+                      : launch_embed<__nv_bfloat16>(table, ids, out, T_, H, V, st);
+}
+int rf_add_rmsnorm(int dtype, float* h, const void* pending, int kind, int n_pending, long long pstride,
+                   const void* w, int w_is_f32, float eps, void* y, const int* rows, int n_rows, int H,
+                   cudaStream_t st) {
+    return dtype == 0
+        ? launch_add_rmsnorm<float>(h, pending, kind, n_pending, (size_t)pstride, w, w_is_f32, eps, y, rows, n_rows, H, st)
+        : launch_add_rmsnorm<__nv_bfloat16>(h, pending, kind, n_pending, (size_t)pstride, w, w_is_f32, eps, y, rows, n_rows, H, st);
+}
+int rf_rope_kv_write(int dtype, void* qkv, int row_stride, int nh, int nkv, int hd, const float* inv_freq,
+                     const int* tok_seq, const int* tok_pos, const int* seq_slot, const int* block_table,
+                     int max_pages, void* k_pages, void* v_pages, int write_kv, int T_, cudaStream_t st) {
+    return dtype == 0
+        ? launch_rope_kv_write<float>(qkv, row_stride, nh, nkv, hd, inv_freq, tok_seq, tok_pos, seq_slot,
+                                      block_table, max_pages, k_pages, v_pages, write_kv, T_, st)
+        : launch_rope_kv_write<__nv_bfloat16>(qkv, row_stride, nh, nkv, hd, inv_freq, tok_seq, tok_pos, seq_slot,
+                                              block_table, max_pages, k_pages, v_pages, write_kv, T_, st);
+}
+int rf_swiglu(int dtype, const void* gu, void* a, int T_, int I, cudaStream_t st) {
+    return dtype == 0 ? launch_swiglu<float>(gu, a, T_, I, st) : launch_swiglu<__nv_bfloat16>(gu, a, T_, I, st);
+}
+}

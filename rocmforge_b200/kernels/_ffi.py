@@ -1,0 +1,62 @@
+"""Glue between torch tensors and the ``extern "C"`` launchers of ``csrc``."""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from ..csrc import build
+
+c_void_p, c_int, c_float, c_ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_CODES = {-1: "bad argument", -2: "size not supported by this kernel",
+          -3: "device error flag set by the kernel (a bounded wait ran out)"}
+
+
+def check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code < 0:
+        raise KernelError(f"{what}: {_CODES.get(code, f'error {code}')}")
+    raise KernelError(f"{what}: CUDA error {code} at launch")
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return 0
+    if dt == torch.bfloat16:
+        return 1
+    raise KernelError(f"compute dtype {dt} is not supported (float32 or bfloat16)")
+
+
+def ptr(t) -> c_void_p:
+    return c_void_p(0) if t is None else c_void_p(t.data_ptr())
+
+
+def stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def need_cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("rocmforge_b200 kernels run on a CUDA device only; got a tensor on "
+                              f"{t.device} (there is no CPU fallback)")
+
+
+def need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise KernelError(msg)
+
+
+def fn(module: str, name: str, argtypes):
+    lib = build.load(module)
+    f = getattr(lib, name)
+    f.argtypes = argtypes
+    f.restype = c_int
+    return f

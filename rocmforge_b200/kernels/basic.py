@@ -1,0 +1,173 @@
+"""Python faces of the plain kernels: embedding, add+RMSNorm, rotation + cache write,
+SwiGLU, the CUDA-core matrix product, the generic attention and argmax.
+
+Each function checks shapes and dtypes, then launches on torch's current stream.
+"""
+from __future__ import annotations
+
+import functools
+
+import torch
+
+from ._ffi import (KernelError, c_float, c_int, c_ll, c_void_p, check, dtype_code, fn, need, need_cuda,
+                   ptr, stream)
+
+PAGE = 64      # tokens per cache page (RF_PAGE in csrc/common.cuh)
+
+
+@functools.lru_cache(None)
+def _f(module, name, *argtypes):
+    return fn(module, name, list(argtypes))
+
+
+def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """out[t] = table[ids[t]] widened to float32."""
+    need_cuda(table, ids)
+    need(table.dim() == 2 and table.is_contiguous(), "embed: table must be a contiguous matrix")
+    need(ids.dtype == torch.int32 and ids.dim() == 1, "embed: ids must be a 1-d int32 tensor")
+    V, H = table.shape
+    T = ids.shape[0]
+    if out is None:
+        out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+    f = _f("elementwise", "rf_embed", c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p)
+    check(f(dtype_code(table.dtype), ptr(table), ptr(ids), ptr(out), T, H, V, stream()), "embed")
+    return out
+
+
+def add_rmsnorm(h: torch.Tensor, weight: torch.Tensor, eps: float, compute_dtype: torch.dtype,
+                pending: torch.Tensor | None = None, rows: torch.Tensor | None = None,
+                out: torch.Tensor | None = None) -> torch.Tensor:
+    """y = rmsnorm(h + pending) * weight.
+
+    ``h`` [T, H] float32 is the residual stream.  ``pending`` is None, a float32
+    [S, T, H] stack of partial sums, or a [T, H] tensor of the compute dtype; without
+    ``rows`` it is added into ``h`` in place.  With ``rows`` (int32 indices) only those
+    rows are normalised and ``h`` is left untouched.
+    """
+    need_cuda(h, weight, pending, rows)
+    need(h.dtype == torch.float32 and h.dim() == 2 and h.is_contiguous(), "add_rmsnorm: h must be [T,H] float32")
+    T, H = h.shape
+    need(weight.shape == (H,) and weight.dtype in (torch.float32, torch.bfloat16),
+         "add_rmsnorm: weight must be [H] in float32 or bfloat16")
+    kind, n_pending, pstride = 0, 0, 0
+    if pending is not None:
+        need(pending.is_contiguous(), "add_rmsnorm: pending must be contiguous")
+        if pending.dtype == torch.float32 and pending.dim() == 3 and pending.shape[1:] == (T, H):
+            kind, n_pending, pstride = 1, pending.shape[0], T * H
+        elif pending.dtype == torch.float32 and pending.shape == (T, H) and compute_dtype == torch.float32:
+            kind = 2
+        elif pending.dtype == torch.float32 and pending.shape == (T, H):
+            kind, n_pending, pstride = 1, 1, T * H
+        elif pending.dtype == compute_dtype and pending.shape == (T, H):
+            kind = 2
+        else:
+            raise KernelError(f"add_rmsnorm: pending of shape {tuple(pending.shape)} / {pending.dtype} "
+                              f"does not fit h {tuple(h.shape)}")
+    n_rows = T
+    if rows is not None:
+        need(rows.dtype == torch.int32 and rows.dim() == 1, "add_rmsnorm: rows must be 1-d int32")
+        n_rows = rows.shape[0]
+    if out is None:
+        out = torch.empty((n_rows, H), dtype=compute_dtype, device=h.device)
+    f = _f("elementwise", "rf_add_rmsnorm", c_int, c_void_p, c_void_p, c_int, c_int, c_ll, c_void_p, c_int,
+           c_float, c_void_p, c_void_p, c_int, c_int, c_void_p)
+    check(f(dtype_code(compute_dtype), ptr(h), ptr(pending), kind, n_pending, pstride, ptr(weight),
+            int(weight.dtype == torch.float32), float(eps), ptr(out), ptr(rows), n_rows, H, stream()),
+          f"add_rmsnorm (H={H})")
+    return out
+
+
+def rope_kv_write(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, inv_freq: torch.Tensor,
+                  tok_seq, tok_pos, seq_slot, block_table: torch.Tensor,
+                  k_pages: torch.Tensor | None, v_pages: torch.Tensor | None, write_kv: bool = True) -> None:
+    """Rotate q (in place) and k by position; write rotated k and v into their cache pages."""
+    need_cuda(qkv, inv_freq, tok_seq, tok_pos, seq_slot, block_table, k_pages, v_pages)
+    T = qkv.shape[0]
+    need(qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] == (n_heads + 2 * n_kv_heads) * head_dim,
+         "rope_kv_write: qkv must be [T, (heads + 2 kv_heads) * head_dim]")
+    need(inv_freq.dtype == torch.float32 and inv_freq.numel() == head_dim // 2,
+         "rope_kv_write: inv_freq must hold head_dim/2 float32 frequencies")
+    if write_kv:
+        for p in (k_pages, v_pages):
+            need(p is not None and p.dtype == qkv.dtype and p.is_contiguous()
+                 and tuple(p.shape[1:]) == (n_kv_heads, PAGE, head_dim),
+                 "rope_kv_write: pages must be [n_pages, kv_heads, 64, head_dim] of the compute dtype")
+    f = _f("elementwise", "rf_rope_kv_write", c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+           c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p)
+    check(f(dtype_code(qkv.dtype), ptr(qkv), qkv.stride(0), n_heads, n_kv_heads, head_dim, ptr(inv_freq),
+            ptr(tok_seq), ptr(tok_pos), ptr(seq_slot), ptr(block_table), block_table.shape[1],
+            ptr(k_pages), ptr(v_pages), int(write_kv), T, stream()), "rope_kv_write")
+
+
+def swiglu(gu: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """a[t, j] = silu(gu[t, 2j]) * gu[t, 2j+1]."""
+    need_cuda(gu)
+    need(gu.dim() == 2 and gu.is_contiguous() and gu.shape[1] % 2 == 0, "swiglu: input must be [T, 2I]")
+    T, I2 = gu.shape
+    if out is None:
+        out = torch.empty((T, I2 // 2), dtype=gu.dtype, device=gu.device)
+    f = _f("elementwise", "rf_swiglu", c_int, c_void_p, c_void_p, c_int, c_int, c_void_p)
+    check(f(dtype_code(gu.dtype), ptr(gu), ptr(out), T, I2 // 2, stream()), "swiglu")
+    return out
+
+
+def gemm_simt(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, *,
+              out: torch.Tensor | None = None, out_f32: bool = False, accumulate: bool = False) -> torch.Tensor:
+    """y = x @ w.T (+ bias) on CUDA cores with 32-bit sums.
+
+    out_f32: the result is float32 whatever the inputs; accumulate: added into ``out`` (float32).
+    """
+    need_cuda(x, w, bias, out)
+    need(x.dim() == 2 and w.dim() == 2 and x.dtype == w.dtype and x.stride(1) == 1 and w.is_contiguous(),
+         "gemm: x [M,K] and w [N,K] must share a dtype and be row-major")
+    M, K = x.shape
+    N = w.shape[0]
+    need(w.shape[1] == K, f"gemm: inner sizes differ ({K} vs {w.shape[1]})")
+    if bias is not None:
+        need(bias.shape == (N,) and bias.dtype in (torch.float32, torch.bfloat16), "gemm: bias must be [N]")
+    mode = 2 if accumulate else (1 if out_f32 else 0)
+    odt = torch.float32 if mode else x.dtype
+    if out is None:
+        need(not accumulate, "gemm: accumulate needs an output tensor")
+        out = torch.empty((M, N), dtype=odt, device=x.device)
+    need(out.shape == (M, N) and out.dtype == odt and out.stride(1) == 1, "gemm: output has the wrong shape or dtype")
+    f = _f("gemm_simt", "rf_gemm_simt", c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
+           c_int, c_int, c_int, c_int, c_void_p)
+    check(f(dtype_code(x.dtype), ptr(x), ptr(w), ptr(bias), int(bias is not None and bias.dtype == torch.float32),
+            ptr(out), M, N, K, x.stride(0), out.stride(0), mode, stream()), f"gemm_simt ({M}x{N}x{K})")
+    return out
+
+
+def attention_generic(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, k_pages, v_pages,
+                      tok_seq, tok_pos, seq_slot, block_table, scale: float, window: int | None,
+                      out: torch.Tensor | None = None) -> torch.Tensor:
+    """Attention of the T new tokens over the paged cache (their own keys included)."""
+    need_cuda(q, k_pages, v_pages, tok_seq, tok_pos, seq_slot, block_table)
+    T = q.shape[0]
+    need(q.dim() == 2 and q.stride(1) == 1, "attention: q must be [T, >= heads*head_dim] with unit inner stride")
+    need(k_pages.dtype == q.dtype and v_pages.dtype == q.dtype, "attention: cache dtype differs from q")
+    need(tuple(k_pages.shape[1:]) == (n_kv_heads, PAGE, head_dim) and k_pages.is_contiguous()
+         and v_pages.shape == k_pages.shape and v_pages.is_contiguous(), "attention: bad cache page shape")
+    if out is None:
+        out = torch.empty((T, n_heads * head_dim), dtype=q.dtype, device=q.device)
+    f = _f("attention_generic", "rf_attention_generic", c_int, c_void_p, c_int, c_void_p, c_int, c_void_p,
+           c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
+           c_void_p)
+    check(f(dtype_code(q.dtype), ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(k_pages), ptr(v_pages),
+            ptr(tok_seq), ptr(tok_pos), ptr(seq_slot), ptr(block_table), block_table.shape[1], n_heads,
+            n_kv_heads, head_dim, float(scale), int(window or 0), T, stream()),
+          f"attention_generic (heads={n_heads}, kv_heads={n_kv_heads}, head_dim={head_dim})")
+    return out
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Row-wise argmax of float32 logits; of equal maxima the highest index."""
+    need_cuda(logits)
+    need(logits.dim() == 2 and logits.dtype == torch.float32 and logits.stride(1) == 1,
+         "argmax: logits must be [rows, vocab] float32")
+    R, V = logits.shape
+    if out is None:
+        out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    f = _f("sampling", "rf_argmax", c_void_p, c_int, c_int, c_ll, c_void_p, c_void_p)
+    check(f(ptr(logits), R, V, logits.stride(0), ptr(out), stream()), "argmax")
+    return out
