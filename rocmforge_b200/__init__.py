@@ -9,6 +9,9 @@ from .config import load_config, Qwen2Config, ConfigError
 from .engine import Model, ModelSpec, ScheduleEntry, StepRequest, Options
 from .cache import SequenceCache, CacheError
 from .weights import WeightError, write_model_folder
+from .sampling import SamplingParams
+from .api import LLM
+from .engine.generate import generate, GenerationResult
 
 __all__ = ["load_config", "Qwen2Config", "ConfigError", "Model", "ModelSpec", "ScheduleEntry",
-           "StepRequest", "Options", "SequenceCache", "CacheError", "WeightError", "write_model_folder"]
+           "StepRequest", "Options", "LLM", "SamplingParams", "generate", "GenerationResult", "SequenceCache", "CacheError", "WeightError", "write_model_folder"]

@@ -27,13 +27,16 @@ class Options:
 class StepContext:
     """Device arrays of the batch and the kernel dispatch for one step."""
 
-    def __init__(self, model, views, *, T: int, B: int, R: int, is_decode: bool, max_new: int, max_end: int):
+    def __init__(self, model, views, *, T: int, B: int, R: int, is_decode: bool, max_new: int, max_end: int,
+                 host=None):
         self.model = model
         self.options: Options = model.options
         self.compute_dtype: torch.dtype = model.compute_dtype
         self.device = model.device
         self.T, self.B, self.R = T, B, R
         self.is_decode, self.max_new, self.max_end = is_decode, max_new, max_end
+        self.host = host                     # the StepBatch (host arrays); None inside a replayed graph
+        self.replayed = False                # True inside a CUDA graph: launch shapes must be fixed
         self.tokens = views["tokens"]
         self.tok_seq = views["tok_seq"]
         self.tok_pos = views["tok_pos"]

@@ -1,0 +1,78 @@
+"""Decode steps replayed from CUDA graphs.
+
+maeddesg/ROCmForge captures the tail of its decode step (norm, output matrix, argmax) as a HIP
+graph and replays it per token (src/gpu/forward.rs:474-571); its full-step graph reads
+position and length from a two-int device buffer uploaded before each replay
+(src/gpu/cache.rs:707-734) but is switched off for a driver fault (forward.rs:2258-2275).
+Here the whole step of a batch of B single tokens is one graph per B: token ids, slots and
+positions live in a device descriptor that is rewritten before each replay, block tables
+are read from the cache's device tables, so the graph's launches never change.
+"""
+from __future__ import annotations
+
+from typing import Dict, Sequence
+
+import torch
+
+from .batch import DeviceDescriptor, StepBatch, StepRequest
+from .context import StepContext
+
+
+class _Captured:
+    def __init__(self, graph, logits):
+        self.graph = graph
+        self.logits = logits
+
+
+class DecodeRunner:
+    """Runs one-token-per-sequence steps of a model over one cache, a graph per batch size."""
+
+    def __init__(self, model, cache, max_batch: int = 1024):
+        self.model = model
+        self.cache = cache
+        self.desc = DeviceDescriptor(model.device, capacity=StepBatch.layout(max_batch, max_batch, max_batch)[1])
+        self.max_batch = max_batch
+        self.graphs: Dict[int, _Captured] = {}
+        from ..sampling import DeviceSampler
+        self.sampler = DeviceSampler(model.device)
+        self.replays = 0
+
+    def _context(self, B: int) -> StepContext:
+        views = self.desc.views(B, B, B)
+        ctx = StepContext(self.model, views, T=B, B=B, R=B, is_decode=True, max_new=1,
+                          max_end=self.cache.max_seq_len)
+        ctx.replayed = True          # launch shapes must not depend on this step's lengths
+        return ctx
+
+    def _capture(self, B: int) -> _Captured:
+        ctx = self._context(B)
+        side = torch.cuda.Stream(device=self.model.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self.model.forward(ctx, self.cache)            # warm-up: loads modules, sizes the allocator
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            logits = self.model.forward(ctx, self.cache)
+        return _Captured(graph, logits)
+
+    def logits(self, slots: Sequence[int], tokens: Sequence[int]) -> torch.Tensor:
+        """Step one token per slot; float32 logits [B, vocab] (a buffer reused by the next call)."""
+        B = len(slots)
+        if B > self.max_batch:
+            raise ValueError(f"a decode batch of {B} exceeds the runner's limit of {self.max_batch}")
+        requests = [StepRequest(s, [int(t)], [0]) for s, t in zip(slots, tokens)]
+        starts = [self.cache.length(s) for s in slots]
+        batch = StepBatch(requests, starts, self.model.spec.vocab_size)
+        self.cache.prepare(slots, [1] * B)
+        self.desc.upload(batch.pack())
+        cap = self.graphs.get(B)
+        if cap is None:
+            cap = self.graphs[B] = self._capture(B)
+        cap.graph.replay()
+        self.replays += 1
+        self.cache.commit(slots, [1] * B)
+        return cap.logits
+
+    def run(self, slots, tokens, requests, draws, sampling) -> torch.Tensor:
+        return self.sampler.sample(self.logits(slots, tokens), sampling, requests, draws)

@@ -154,7 +154,7 @@ class Model:
         self._desc.upload(batch.pack())
         views = self._desc.views(batch.T, batch.B, batch.R)
         ctx = StepContext(self, views, T=batch.T, B=batch.B, R=batch.R, is_decode=batch.is_decode,
-                          max_new=batch.max_new, max_end=batch.max_end)
+                          max_new=batch.max_new, max_end=batch.max_end, host=batch)
         logits = self.forward(ctx, cache)
         cache.commit(slots, n_new)
         return logits

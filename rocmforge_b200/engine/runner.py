@@ -1,0 +1,52 @@
+"""The StepEngine of a real model: Model.step + the device sampler over one cache."""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import torch
+
+from ..cache import pages_for
+from ..sampling import DeviceSampler, SamplingParams
+from .batch import StepRequest
+from .generate import StepEngine
+
+
+class ModelEngine(StepEngine):
+    def __init__(self, model, cache, max_batch: int = 64):
+        self.model = model
+        self.cache = cache
+        self.max_batch = max_batch
+        self.max_seq_len = cache.max_seq_len
+        self.sampler = DeviceSampler(model.device)
+        self.decode_runner = None
+        if model.options.decode_graphs:
+            from .graph import DecodeRunner
+            self.decode_runner = DecodeRunner(model, cache)
+
+    def admit(self, prompt_lens: Sequence[int], max_new_tokens: int) -> int:
+        free = min(self.cache.free_pages()) if self.cache.groups else 1 << 30
+        slots = self.cache.slots.n_free
+        n = 0
+        for plen in prompt_lens:
+            need = pages_for(min(plen + max_new_tokens, self.max_seq_len))
+            if n >= self.max_batch or n >= slots or need > free:
+                break
+            free -= need
+            n += 1
+        return n
+
+    def alloc_slot(self) -> int:
+        return self.cache.alloc_slot()
+
+    def free_slot(self, slot: int) -> None:
+        self.cache.free_slot(slot)
+
+    def run(self, slots, tokens, requests, draws, sampling: SamplingParams) -> List[int]:
+        decode = all(len(t) == 1 for t in tokens)
+        if decode and self.decode_runner is not None:
+            out = self.decode_runner.run(slots, [t[0] for t in tokens], requests, draws, sampling)
+        else:
+            reqs = [StepRequest(s, t, [len(t) - 1]) for s, t in zip(slots, tokens)]
+            logits = self.model.step(self.cache, reqs)
+            out = self.sampler.sample(logits, sampling, requests, draws)
+        return out.cpu().tolist()

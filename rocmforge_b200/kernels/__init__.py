@@ -1,2 +1,2 @@
 from ._ffi import KernelError
-from .basic import (PAGE, embed, add_rmsnorm, rope_kv_write, swiglu, gemm_simt, attention_generic, argmax)
+from .basic import (PAGE, embed, add_rmsnorm, rope_kv_write, swiglu, gemm_simt, attention_generic, argmax, sample)

@@ -171,3 +171,25 @@ def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tenso
     f = _f("sampling", "rf_argmax", c_void_p, c_int, c_int, c_ll, c_void_p, c_void_p)
     check(f(ptr(logits), R, V, logits.stride(0), ptr(out), stream()), "argmax")
     return out
+
+
+def sample(logits: torch.Tensor, temperature: float, top_p: float, top_k: int, seeds: torch.Tensor,
+           draw_counter: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """One seeded draw per row after temperature, top-k and nucleus filtering.
+
+    ``seeds`` [rows] int64 holds each row's 64-bit LCG seed; ``draw_counter`` (a device int32
+    scalar) is added to every seed, so that a replayed step can advance its draws without the host.
+    """
+    need_cuda(logits, seeds, draw_counter)
+    need(logits.dim() == 2 and logits.dtype == torch.float32 and logits.stride(1) == 1,
+         "sample: logits must be [rows, vocab] float32")
+    R, V = logits.shape
+    need(seeds.dtype == torch.int64 and seeds.shape == (R,), "sample: seeds must be [rows] int64")
+    need(temperature > 0.0, "sample: temperature must be positive (0 means argmax)")
+    if out is None:
+        out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    f = _f("sampling", "rf_sample", c_void_p, c_int, c_int, c_ll, c_float, c_float, c_int, c_void_p, c_void_p,
+           c_void_p, c_void_p)
+    check(f(ptr(logits), R, V, logits.stride(0), float(temperature), float(top_p), int(top_k), ptr(seeds),
+            ptr(draw_counter), ptr(out), stream()), "sample")
+    return out

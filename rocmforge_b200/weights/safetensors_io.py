@@ -12,6 +12,7 @@ import json
 import mmap
 import os
 import struct
+import warnings
 from dataclasses import dataclass
 from typing import Dict, Iterable, Tuple
 
@@ -85,7 +86,9 @@ class SafetensorsFile:
         n = 1
         for s in e.shape:
             n *= s
-        t = torch.frombuffer(self._map, dtype=e.dtype, count=n, offset=e.begin)
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore", UserWarning)      # the map is read-only by design
+            t = torch.frombuffer(self._map, dtype=e.dtype, count=n, offset=e.begin)
         return t.view(e.shape)
 
     def close(self):

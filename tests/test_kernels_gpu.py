@@ -1,0 +1,283 @@
+"""Each kernel alone against a plain PyTorch float64 reference of the same operation, at sizes
+other than the tiny models' (needs a GPU)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from plain import qwen2_plain as P
+from plain import sampling_plain as S
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTS = [torch.float32, torch.bfloat16]
+
+
+def tol(dt):
+    return dict(atol=1e-5, rtol=1e-5) if dt == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+
+
+def rnd(*shape, dt=torch.float32, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dt).to(DEV)
+
+
+@pytest.mark.parametrize("dt", DTS)
+def test_embed(dt):
+    from rocmforge_b200 import kernels
+    table = rnd(1000, 136, dt=dt)
+    ids = torch.tensor([0, 999, 5, 5, 123], dtype=torch.int32, device=DEV)
+    out = kernels.embed(table, ids)
+    assert out.dtype == torch.float32 and torch.equal(out, table[ids.long()].float())
+
+
+@pytest.mark.parametrize("dt", DTS)
+@pytest.mark.parametrize("H", [24, 1000, 3584, 5120])
+def test_add_rmsnorm(dt, H):
+    from rocmforge_b200 import kernels
+    T = 7
+    h = rnd(T, H, seed=1)
+    for wdt in (torch.float32, torch.bfloat16):
+        w = rnd(H, dt=wdt, seed=2) + 1.0
+        # no pending
+        h0 = h.clone()
+        y = kernels.add_rmsnorm(h0, w, 1e-5, dt)
+        ref = P.rms_norm(h.double(), w.double(), 1e-5)
+        assert torch.equal(h0, h) and y.dtype == dt
+        torch.testing.assert_close(y.double(), ref, **tol(dt))
+        # split partial sums, added in 32-bit and written back
+        parts = rnd(3, T, H, seed=3)
+        h1 = h.clone()
+        y = kernels.add_rmsnorm(h1, w, 1e-5, dt, pending=parts)
+        total = h.double() + parts.double().sum(0)
+        torch.testing.assert_close(h1.double(), total, atol=1e-5, rtol=1e-6)
+        torch.testing.assert_close(y.double(), P.rms_norm(total, w.double(), 1e-5), **tol(dt))
+        # pending in the compute dtype
+        pend = rnd(T, H, dt=dt, seed=4)
+        h2 = h.clone()
+        y = kernels.add_rmsnorm(h2, w, 1e-5, dt, pending=pend)
+        total = h.double() + pend.double()
+        torch.testing.assert_close(h2.double(), total, atol=1e-5, rtol=1e-6)
+        torch.testing.assert_close(y.double(), P.rms_norm(total, w.double(), 1e-5), **tol(dt))
+        # rows: only those rows, h untouched
+        rows = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+        h3 = h.clone()
+        y = kernels.add_rmsnorm(h3, w, 1e-5, dt, pending=pend, rows=rows)
+        assert torch.equal(h3, h) and tuple(y.shape) == (3, H)
+        torch.testing.assert_close(y.double(), P.rms_norm(total[rows.long()], w.double(), 1e-5), **tol(dt))
+
+
+@pytest.mark.parametrize("dt", DTS)
+@pytest.mark.parametrize("M,N,K", [(1, 7, 5), (5, 130, 33), (65, 64, 64), (130, 200, 257), (3, 1000, 3584)])
+def test_gemm_simt(dt, M, N, K):
+    from rocmforge_b200 import kernels
+    x, w = rnd(M, K, dt=dt, seed=1), rnd(N, K, dt=dt, seed=2, scale=0.1)
+    bias = rnd(N, seed=3)
+    ref = x.double() @ w.double().t()
+    y = kernels.gemm_simt(x, w)
+    assert y.dtype == dt
+    torch.testing.assert_close(y.double(), ref, **tol(dt))
+    y = kernels.gemm_simt(x, w, bias, out_f32=True)
+    assert y.dtype == torch.float32
+    torch.testing.assert_close(y.double(), ref + bias.double(), atol=1e-4, rtol=1e-5)
+    acc = rnd(M, N, seed=4)
+    acc0 = acc.clone()
+    kernels.gemm_simt(x, w, out=acc, accumulate=True)
+    torch.testing.assert_close(acc.double(), acc0.double() + ref, atol=1e-4, rtol=1e-5)
+    # a row's result does not depend on the other rows of the batch
+    if M > 1:
+        alone = kernels.gemm_simt(x[M - 1:M].contiguous(), w, out_f32=True)
+        assert torch.equal(alone, kernels.gemm_simt(x, w, out_f32=True)[M - 1:M])
+
+
+@pytest.mark.parametrize("dt", DTS)
+def test_swiglu(dt):
+    from rocmforge_b200 import kernels
+    gu = rnd(9, 2 * 301, dt=dt, scale=3.0)
+    a = kernels.swiglu(gu)
+    g, u = gu.double()[:, 0::2], gu.double()[:, 1::2]
+    torch.testing.assert_close(a.double(), P.silu(g) * u, **tol(dt))
+
+
+def paged(seq_lens, nkv, hd, dt, n_pages=40, seed=0, shuffle=True):
+    """Random keys/values for sequences of the given lengths, scattered over shuffled pages."""
+    g = torch.Generator().manual_seed(seed)
+    order = torch.randperm(n_pages, generator=g).tolist() if shuffle else list(range(n_pages))
+    max_pages = max((n + 63) // 64 for n in seq_lens) + 1
+    table = torch.zeros(len(seq_lens) + 2, max_pages, dtype=torch.int32)
+    k_pages = torch.full((n_pages, nkv, 64, hd), float("nan"), dtype=dt)
+    v_pages = torch.full((n_pages, nkv, 64, hd), float("nan"), dtype=dt)
+    ks, vs = [], []
+    for s, n in enumerate(seq_lens):
+        k = torch.randn(n, nkv, hd, generator=g).to(dt)
+        v = torch.randn(n, nkv, hd, generator=g).to(dt)
+        ks.append(k); vs.append(v)
+        for p in range((n + 63) // 64):
+            page = order.pop()
+            table[s + 1, p] = page                      # sequence s lives in slot s + 1
+            m = min(64, n - p * 64)
+            k_pages[page, :, :m] = k[p * 64:p * 64 + m].transpose(0, 1)
+            v_pages[page, :, :m] = v[p * 64:p * 64 + m].transpose(0, 1)
+    return ks, vs, k_pages.to(DEV), v_pages.to(DEV), table.to(DEV)
+
+
+def attention_reference(q, k, v, pos, scale, window):
+    """q [nh, hd] at absolute position pos over k/v [n, nkv, hd] (float64)."""
+    nh, hd = q.shape
+    nkv = k.shape[1]
+    lo = 0 if not window else max(0, pos - window + 1)
+    out = torch.zeros(nh, hd, dtype=torch.float64)
+    for h in range(nh):
+        kh = h // (nh // nkv)
+        s = (k[lo:pos + 1, kh].double() @ q[h].double()) * scale
+        w = torch.softmax(s, dim=0)
+        out[h] = w @ v[lo:pos + 1, kh].double()
+    return out
+
+
+@pytest.mark.parametrize("dt", DTS)
+@pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 16, None), (6, 1, 48, None), (8, 8, 80, 70),
+                                              (14, 2, 64, None), (28, 4, 128, 200), (2, 2, 256, None)])
+def test_attention_generic(dt, nh, nkv, hd, window):
+    """New tokens of three sequences (a whole prompt, an appended chunk, one decoded token)."""
+    from rocmforge_b200 import kernels
+    lens = [150, 333, 65]
+    new = [150, 20, 1]
+    ks, vs, k_pages, v_pages, table = paged(lens, nkv, hd, dt, seed=nh)
+    g = torch.Generator().manual_seed(1)
+    T = sum(new)
+    q = torch.randn(T, nh * hd, generator=g).to(dt)
+    tok_seq = torch.tensor(sum(([i] * n for i, n in enumerate(new)), []), dtype=torch.int32)
+    tok_pos = torch.tensor(sum((list(range(L - n, L)) for L, n in zip(lens, new)), []), dtype=torch.int32)
+    seq_slot = torch.tensor([1, 2, 3], dtype=torch.int32)
+    scale = 1.0 / math.sqrt(hd)
+    out = kernels.attention_generic(q.to(DEV), nh, nkv, hd, k_pages, v_pages, tok_seq.to(DEV), tok_pos.to(DEV),
+                                    seq_slot.to(DEV), table, scale, window)
+    assert torch.isfinite(out).all(), "a page that holds no key of the sequence was read"
+    for t in range(T):
+        s = int(tok_seq[t])
+        ref = attention_reference(q[t].view(nh, hd), ks[s], vs[s], int(tok_pos[t]), scale, window)
+        torch.testing.assert_close(out[t].cpu().double().view(nh, hd), ref, **tol(dt))
+
+
+@pytest.mark.parametrize("dt", DTS)
+def test_attention_finds_one_far_key_and_the_window_edge(dt):
+    """Random weights hide a key that is never read: make one far key (and the two keys at the
+    window's edge) stand out by a large, aligned score, and check whose value comes out."""
+    from rocmforge_b200 import kernels
+    nh = nkv = 1
+    hd, n = 32, 700
+    ks, vs, k_pages, v_pages, table = paged([n], nkv, hd, dt, n_pages=16, seed=3)
+    q = torch.zeros(1, hd); q[0, 0] = 8.0
+    args = (torch.zeros(1, dtype=torch.int32, device=DEV), torch.tensor([n - 1], dtype=torch.int32, device=DEV),
+            torch.tensor([1], dtype=torch.int32, device=DEV), table)
+
+    def run(target, window):
+        kp = k_pages.clone()
+        page = int(table[1, target // 64])
+        kp[page, 0, target % 64] = 0
+        kp[page, 0, target % 64, 0] = 40.0              # score 8 * 40 / sqrt(32): dwarfs every other key
+        return kernels.attention_generic(q.to(dt).to(DEV), nh, nkv, hd, kp, v_pages, *args,
+                                         1.0 / math.sqrt(hd), window)[0].float().cpu()
+
+    for target in (0, 3, 63, 64, 320, 698):
+        torch.testing.assert_close(run(target, None), vs[0][target, 0].float(), atol=1e-3, rtol=1e-3)
+    W = 100                                             # the query at 699 sees keys 600..699
+    torch.testing.assert_close(run(600, W), vs[0][600, 0].float(), atol=1e-3, rtol=1e-3)
+    out = run(599, W)                                   # one position outside: must be ignored
+    assert (out - vs[0][599, 0].float()).abs().max() > 0.1
+    ref = attention_reference(q.to(dt).view(1, hd), ks[0], vs[0], n - 1, 1.0 / math.sqrt(hd), W)
+    torch.testing.assert_close(out.double().view(1, hd), ref, **tol(dt))
+
+
+@pytest.mark.parametrize("dt", DTS)
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (3, 1, 48), (28, 4, 128)])
+def test_rope_kv_write(dt, nh, nkv, hd):
+    from rocmforge_b200 import kernels
+    from rocmforge_b200.parts import NeoxRope
+    theta = 1e6
+    rope = NeoxRope(hd, theta); rope.prepare(DEV)
+    pos = torch.tensor([0, 1, 63, 64, 65, 4000, 7], dtype=torch.int32)
+    seq = torch.tensor([0, 0, 0, 0, 0, 1, 2], dtype=torch.int32)
+    T = len(pos)
+    qkv = rnd(T, (nh + 2 * nkv) * hd, dt=dt, seed=5)
+    before = qkv.clone()
+    n_pages, max_pages = 80, 64
+    table = torch.zeros(4, max_pages, dtype=torch.int32)
+    table[1, 0], table[1, 1], table[2, 4000 // 64], table[3, 0] = 7, 3, 11, 5
+    k_pages = torch.zeros(n_pages, nkv, 64, hd, dtype=dt, device=DEV)
+    v_pages = torch.zeros_like(k_pages)
+    kernels.rope_kv_write(qkv, nh, nkv, hd, rope.inv_freq, seq.to(DEV), pos.to(DEV),
+                          torch.tensor([1, 2, 3], dtype=torch.int32, device=DEV), table.to(DEV), k_pages, v_pages)
+    b = before.double().cpu()
+    q_ref = P.rope_neox(b[:, :nh * hd].view(T, nh, hd), pos, theta)
+    k_ref = P.rope_neox(b[:, nh * hd:(nh + nkv) * hd].view(T, nkv, hd), pos, theta)
+    v_ref = b[:, (nh + nkv) * hd:].view(T, nkv, hd)
+    t = tol(dt)
+    torch.testing.assert_close(qkv[:, :nh * hd].double().cpu().view(T, nh, hd), q_ref, **t)
+    assert torch.equal(qkv[:, nh * hd:], before[:, nh * hd:])          # k and v columns stay as they were
+    where = [(7, 0), (7, 1), (7, 63), (3, 0), (3, 1), (11, 4000 % 64), (5, 7)]
+    for i, (page, off) in enumerate(where):
+        torch.testing.assert_close(k_pages[page, :, off].double().cpu(), k_ref[i], **t)
+        torch.testing.assert_close(v_pages[page, :, off].double().cpu(), v_ref[i], atol=0, rtol=0)
+    assert int((k_pages.float().abs().sum(dim=(1, 3)) > 0).sum()) == T    # nothing else was written
+    # a layer that reads another layer's cache rotates q and writes nothing
+    qkv2 = before.clone()
+    k2 = torch.zeros_like(k_pages)
+    kernels.rope_kv_write(qkv2, nh, nkv, hd, rope.inv_freq, seq.to(DEV), pos.to(DEV),
+                          torch.tensor([1, 2, 3], dtype=torch.int32, device=DEV), table.to(DEV), k2, k2,
+                          write_kv=False)
+    assert torch.equal(qkv2, qkv) and float(k2.abs().sum()) == 0
+
+
+def test_argmax_ties_and_sizes():
+    from rocmforge_b200 import kernels
+    x = rnd(5, 152064, seed=9)
+    x[0, 17] = x[0, 150000] = 50.0
+    x[1, 0] = 60.0
+    x[2, 152063] = 60.0
+    x[3] = 0.0
+    got = kernels.argmax(x).cpu().tolist()
+    assert got[:4] == [150000, 0, 152063, 152063]            # equal maxima: the highest index
+    assert got[4] == S.greedy(x[4].cpu())
+    y = rnd(3, 300, seed=1)
+    assert kernels.argmax(y).cpu().tolist() == [S.greedy(r) for r in y.cpu()]
+
+
+@pytest.mark.parametrize("V", [300, 5000, 152064])
+def test_sample_kernel_follows_the_plain_sampler(V):
+    from rocmforge_b200 import kernels
+    from rocmforge_b200.sampling import as_int64, draw_seed
+    R = 24
+    logits = rnd(R, V, seed=V, scale=2.5)
+    logits[:, 5] = logits[:, 77]                              # equal logits somewhere in every row
+    logits[3, :] = 0.25                                       # a row of all-equal logits
+    cpu = logits.cpu()
+    for temperature, top_p, top_k in ((0.8, 1.0, 0), (0.8, 0.9, 0), (1.0, 0.5, 0), (1.5, 1.0, 40),
+                                      (0.7, 0.8, 10), (1.0, 0.95, 1), (1e-7, 1.0, 0), (1.0, 0.0, 0)):
+        seeds = [draw_seed(1234, r, 3) for r in range(R)]
+        got = kernels.sample(logits, temperature, top_p, top_k,
+                             torch.tensor([as_int64(s) for s in seeds], dtype=torch.int64, device=DEV)).cpu().tolist()
+        want = [S.sample(cpu[r], temperature, top_p, top_k, seeds[r]) for r in range(R)]
+        assert got == want, f"temperature={temperature} top_p={top_p} top_k={top_k}"
+    # the draw counter advances the seed on the device
+    base = torch.tensor([as_int64(draw_seed(99, r, 0)) for r in range(R)], dtype=torch.int64, device=DEV)
+    counter = torch.tensor([5], dtype=torch.int32, device=DEV)
+    got = kernels.sample(logits, 0.9, 0.9, 0, base, draw_counter=counter).cpu().tolist()
+    assert got == [S.sample(cpu[r], 0.9, 0.9, 0, draw_seed(99, r, 5)) for r in range(R)]
+
+
+def test_kernels_refuse_what_they_cannot_do():
+    from rocmforge_b200 import kernels
+    from rocmforge_b200.kernels import KernelError
+    with pytest.raises(KernelError):
+        kernels.embed(torch.zeros(4, 4), torch.zeros(2, dtype=torch.int32))            # CPU tensors
+    with pytest.raises(KernelError):
+        kernels.gemm_simt(rnd(2, 8), rnd(3, 9))                                          # inner sizes differ
+    with pytest.raises(KernelError):
+        kernels.gemm_simt(rnd(2, 8, dt=torch.float16), rnd(3, 8, dt=torch.float16))      # dtype without a kernel
+    with pytest.raises(KernelError):
+        kernels.add_rmsnorm(rnd(2, 60000), rnd(60000), 1e-6, torch.float32)             # row larger than shared memory
+    with pytest.raises(KernelError):
+        kernels.swiglu(rnd(2, 7))
