@@ -1,0 +1,279 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the Qwen2.5-7B shape with random weights on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--impl ours|reference]
+
+Prints ONE JSON line.  ``value`` is decoded tokens per second at the given batch, timed on
+the device with CUDA events around K replayed decode steps whose sampled ids feed the next
+step; ``e2e`` is the same rate through ``rocmforge_b200.LLM.generate`` with token ids going
+in from the host and coming back to it every step; ``prefill`` is one step of 2,048 prompt
+tokens; ``roofline`` relates the decode step to the HBM bandwidth; ``points`` holds batch 1
+and batch 64.  maeddesg/ROCmForge publishes no number for this metric (its figures are for
+4-bit weights on an RX 9070 XT), so ``vs_baseline`` is null.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "Qwen2.5-7B bf16 decode tok/s at batch 1/8/64; prefill tok/s at 2,048 tokens"
+
+# BASELINE.json configs[2]
+SHAPE_7B = dict(architectures=["Qwen2ForCausalLM"], num_hidden_layers=28, hidden_size=3584,
+                num_attention_heads=28, num_key_value_heads=4, head_dim=128, intermediate_size=18944,
+                vocab_size=152064, rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=False,
+                use_sliding_window=False, max_position_embeddings=4096)
+CONTEXT = 4096
+PROMPT_LEN = 512
+PREFILL_TOKENS = 2048
+
+
+def peaks():
+    """Measured peaks if the driver wrote them, else the pool's earlier measurement."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    out = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    if os.path.exists(path):
+        try:
+            raw = json.load(open(path))
+            out["hbm_gbs"] = float(raw.get("hbm_gbs", out["hbm_gbs"]))
+            out["bf16_tflops"] = float(raw.get("bf16_tflops", out["bf16_tflops"]))
+            if "bf16_tflops_sustained" in raw:
+                out["bf16_tflops_sustained"] = float(raw["bf16_tflops_sustained"])
+            out["source"] = "measured"
+        except Exception:
+            pass
+    return out
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                pass
+
+    def summary(self, t0, t1):
+        rows = [r for t, r in self.rows if t0 <= t <= t1] or [r for _, r in self.rows[-3:]]
+        sm, mx, reasons = [], 0, set()
+        for r in rows:
+            try:
+                sm.append(float(r[0]))
+                mx = max(mx, float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def step_bytes(cfg, model, batch, mean_ctx):
+    """Bytes a decode step has to read: every weight it uses once, and the cache of the live requests."""
+    L, H, V = cfg.num_hidden_layers, cfg.hidden_size, cfg.vocab_size
+    Q, KV, I = cfg.num_attention_heads * cfg.head_dim, cfg.num_key_value_heads * cfg.head_dim, cfg.intermediate_size
+    per_layer = (H * (Q + 2 * KV) + Q * H + 3 * H * I) * 2 + (Q + 2 * KV + 2 * H) * 2
+    weights = L * per_layer + V * H * 2 + H * 2
+    kv = batch * mean_ctx * 2 * KV * 2 * L
+    return weights + kv
+
+
+def prefill_flops(cfg, T):
+    L, H, V = cfg.num_hidden_layers, cfg.hidden_size, cfg.vocab_size
+    Q, KV, I = cfg.num_attention_heads * cfg.head_dim, cfg.num_key_value_heads * cfg.head_dim, cfg.intermediate_size
+    linear = 2.0 * T * (H * (Q + 2 * KV) + Q * H + 3 * H * I)
+    attn = 2.0 * 2.0 * (T * (T + 1) / 2.0) * cfg.head_dim * cfg.num_attention_heads
+    return L * (linear + attn) + 2.0 * V * H
+
+
+def random_prompts(n, length, vocab, seed):
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, vocab, (length,), generator=g).tolist() for _ in range(n)]
+
+
+def decode_rate(model, batch, steps, warmup, seed):
+    """Device-timed decode: prefill `batch` prompts of PROMPT_LEN tokens, then `steps` replayed steps."""
+    import torch
+    from rocmforge_b200 import StepRequest, kernels
+    from rocmforge_b200.engine.graph import DecodeRunner
+    cache = model.new_cache(max_tokens=batch * (PROMPT_LEN + warmup + steps + 64), max_slots=batch)
+    runner = DecodeRunner(model, cache)
+    prompts = random_prompts(batch, PROMPT_LEN, model.spec.vocab_size, seed)
+    slots = [cache.alloc_slot() for _ in range(batch)]
+    first = []
+    for i in range(0, batch, 8):                       # prompts in steps of 8 sequences
+        logits = model.step(cache, [StepRequest(s, p, [len(p) - 1]) for s, p in zip(slots[i:i + 8], prompts[i:i + 8])])
+        first += kernels.argmax(logits).cpu().tolist()
+    ids, _, _, _ = runner.greedy_loop(slots, first, warmup)
+    torch.cuda.synchronize()
+    t0 = time.time()
+    ids2, start, end, launches = runner.greedy_loop(slots, ids[-1].cpu().tolist(), steps)
+    torch.cuda.synchronize()
+    t1 = time.time()
+    ms = start.elapsed_time(end)
+    mean_ctx = PROMPT_LEN + warmup + steps / 2.0
+    del runner, cache
+    torch.cuda.empty_cache()
+    return {"tok_s": batch * steps / (ms / 1e3), "ms_per_step": ms / steps, "launches": launches * steps,
+            "mean_ctx": mean_ctx, "t0": t0, "t1": t1}
+
+
+def e2e_rate(llm, batch, steps, seed):
+    """The same through LLM.generate: token ids from the host in, sampled ids back to the host, every step."""
+    import torch
+    prompts = random_prompts(batch, PROMPT_LEN, llm.model.spec.vocab_size, seed)
+    stamps = []
+
+    def on_token(i, tok):
+        if i == 0:
+            stamps.append(time.perf_counter())
+    llm.generate(prompts, max_tokens=min(steps, 8) + 1, temperature=0.0, stop_token_ids=[])     # warm-up, graphs
+    stamps.clear()
+    out = llm.generate(prompts, max_tokens=steps + 1, temperature=0.0, stop_token_ids=[], on_token=on_token)
+    torch.cuda.synchronize()
+    n = len(stamps) - 1
+    dt = stamps[-1] - stamps[0]
+    from rocmforge_b200.engine.batch import StepBatch
+    h2d = StepBatch.layout(batch, batch, batch)[1] * 4 + batch * 4 / 64.0     # descriptor + a block-table entry per 64 steps
+    return {"value": batch * n / dt, "unit": "tok/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": batch * 4,
+            "steps": n, "generated": sum(len(r.tokens) for r in out)}
+
+
+def prefill_rate(model, tokens, repeats, seed):
+    import torch
+    from rocmforge_b200 import StepRequest
+    cache = model.new_cache(max_tokens=tokens + 64, max_slots=2)
+    prompt = random_prompts(1, tokens, model.spec.vocab_size, seed)[0]
+    times = []
+    for r in range(repeats + 1):
+        s = cache.alloc_slot()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        model.step(cache, [StepRequest(s, prompt, [tokens - 1])])
+        end.record()
+        torch.cuda.synchronize()
+        if r > 0:                                       # the first run warms up
+            times.append(start.elapsed_time(end))
+        cache.free_slot(s)
+    times.sort()
+    return times[len(times) // 2]
+
+
+def reference_arm():
+    # maeddesg/ROCmForge is a Rust crate with HIP kernels for AMD GPUs: it has no Python package to
+    # install with pip, no Rust toolchain is present, and it has no CUDA path or bf16/safetensors support.
+    print(json.dumps({"impl": "reference",
+                      "unavailable": "maeddesg/ROCmForge is a Rust+HIP (AMD ROCm) crate: not pip-installable, "
+                                     "no cargo/rustc/hipcc here, no CUDA or bf16 path to run on a B200"}))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-points", action="store_true", help="only the headline batch (quick check)")
+    ap.add_argument("--seed", type=int, default=0)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm()
+    if args.gpus != 1:
+        print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not measured")
+        return 2
+    warmup = max(args.warmup, 3)
+
+    import torch
+    import rocmforge_b200 as rf
+    from rocmforge_b200.config import Qwen2Config
+
+    raw = dict(SHAPE_7B)
+    if args.layers:
+        raw["num_hidden_layers"] = args.layers
+    cfg = Qwen2Config.from_dict(raw)
+    pk = peaks()
+    model = rf.Model.random(cfg, seed=args.seed, dtype=torch.bfloat16)
+    llm = rf.LLM(model, cache_tokens=args.batch * (PROMPT_LEN + args.steps + 80), max_batch=args.batch)
+
+    sampler = ClockSampler()
+    sampler.start()
+    main_run = decode_rate(model, args.batch, args.steps, warmup, args.seed)
+    clocks = sampler.summary(main_run["t0"], main_run["t1"])
+    e2e = e2e_rate(llm, args.batch, args.steps, args.seed + 1)
+    llm.cache = llm.engine = None
+    torch.cuda.empty_cache()
+    pre_ms = prefill_rate(model, PREFILL_TOKENS, 3, args.seed + 2)
+    points = {}
+    if not args.skip_points:
+        points["decode_b1"] = round(decode_rate(model, 1, args.steps, warmup, args.seed + 3)["tok_s"], 1)
+        points["decode_b64"] = round(decode_rate(model, 64, max(args.steps // 2, 16), warmup, args.seed + 4)["tok_s"], 1)
+    sampler.stop()
+
+    nbytes = step_bytes(cfg, model, args.batch, main_run["mean_ctx"])
+    achieved = nbytes / (main_run["ms_per_step"] / 1e3) / 1e9
+    flops = prefill_flops(cfg, PREFILL_TOKENS)
+    line = {
+        "metric": METRIC, "value": round(main_run["tok_s"], 1), "unit": "tok/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": warmup, "ms_per_step": round(main_run["ms_per_step"], 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: seeded random token ids, random-init weights N(0, 0.02)", "impl": "ours",
+        "config": {"model": "Qwen2.5-7B shape", "layers": cfg.num_hidden_layers, "layers_of_config": 28,
+                   "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+                   "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+                   "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": PROMPT_LEN,
+                   "context_at_timing": int(main_run["mean_ctx"]), "parallelism": "none (1 GPU)",
+                   "cache_page": 64, "l2": "inputs larger than L2 (15 GB of weights per step)",
+                   "peaks": pk["source"]},
+        "e2e": e2e,
+        "gpu_launches": main_run["launches"],
+        "clocks": clocks,
+        "prefill": {"value": round(PREFILL_TOKENS / (pre_ms / 1e3), 1), "tokens": PREFILL_TOKENS,
+                    "ms": round(pre_ms, 3), "frac": round(flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -293,3 +293,24 @@ extern "C" int rf_sample(const float* logits, int rows, int V, long long row_str
     RF_LAUNCH_CHECK();
     return 0;
 }
+
+// ---------------------------------------------------------------- feeding a replayed decode step
+// After a decode step that is replayed without host work: the sampled ids become the next
+// step's tokens and every sequence moves one position on (the reference's
+// increment_decode_state_kernel, hip_kernels/elementwise.hip:721-753).
+__global__ void advance_decode_kernel(int* tokens, int* tok_pos, int* seq_start, const int* sampled, int B) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < B) {
+        tokens[i] = sampled[i];
+        tok_pos[i] += 1;
+        seq_start[i] += 1;
+    }
+}
+
+extern "C" int rf_advance_decode(int* tokens, int* tok_pos, int* seq_start, const int* sampled, int B,
+                                 cudaStream_t st) {
+    if (B <= 0) return 0;
+    advance_decode_kernel<<<(B + 127) / 128, 128, 0, st>>>(tokens, tok_pos, seq_start, sampled, B);
+    RF_LAUNCH_CHECK();
+    return 0;
+}

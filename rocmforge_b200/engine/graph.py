@@ -74,5 +74,48 @@ class DecodeRunner:
         self.cache.commit(slots, [1] * B)
         return cap.logits
 
+    # ---------------------------------------------------------------- replay without host work
+    def greedy_loop(self, slots: Sequence[int], tokens: Sequence[int], steps: int):
+        """``steps`` greedy decode steps whose sampled ids feed the next step on the device.
+
+        Returns (ids [steps, B] int32 on the device, start event, end event, launches per step).
+        Pages for all steps are taken first, so the loop itself is nothing but graph replays.
+        """
+        from .. import kernels
+        B = len(slots)
+        for s in slots:
+            self.cache.reserve(s, self.cache.length(s) + steps)
+        requests = [StepRequest(s, [int(t)], [0]) for s, t in zip(slots, tokens)]
+        batch = StepBatch(requests, [self.cache.length(s) for s in slots], self.model.spec.vocab_size)
+        self.desc.upload(batch.pack())
+        key = ("loop", B)
+        out = torch.empty((steps, B), dtype=torch.int32, device=self.model.device)
+        cap = self.graphs.get(key)
+        if cap is None:
+            ctx = self._context(B)
+            sampled = torch.zeros((B,), dtype=torch.int32, device=self.model.device)
+            side = torch.cuda.Stream(device=self.model.device)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                kernels.argmax(self.model.forward(ctx, self.cache), out=sampled)
+            torch.cuda.current_stream().wait_stream(side)
+            graph = torch.cuda.CUDAGraph()
+            n0 = kernels.launch_count()
+            with torch.cuda.graph(graph):
+                kernels.argmax(self.model.forward(ctx, self.cache), out=sampled)
+                kernels.advance_decode(ctx.tokens, ctx.tok_pos, ctx.seq_start, sampled)
+            cap = self.graphs[key] = _Captured(graph, sampled)
+            cap.launches = kernels.launch_count() - n0
+            self.desc.upload(batch.pack())          # warm-up and capture did not advance anything, but be exact
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for i in range(steps):
+            cap.graph.replay()
+            out[i].copy_(cap.logits, non_blocking=True)
+        end.record()
+        self.replays += steps
+        self.cache.commit(slots, [steps] * B)
+        return out, start, end, cap.launches
+
     def run(self, slots, tokens, requests, draws, sampling) -> torch.Tensor:
         return self.sampler.sample(self.logits(slots, tokens), sampling, requests, draws)

@@ -18,8 +18,18 @@ _CODES = {-1: "bad argument", -2: "size not supported by this kernel",
           -3: "device error flag set by the kernel (a bounded wait ran out)"}
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many launcher calls of this package's CUDA modules succeeded so far in this process."""
+    return _launches
+
+
 def check(code: int, what: str) -> None:
+    global _launches
     if code == 0:
+        _launches += 1
         return
     if code < 0:
         raise KernelError(f"{what}: {_CODES.get(code, f'error {code}')}")

@@ -193,3 +193,13 @@ def sample(logits: torch.Tensor, temperature: float, top_p: float, top_k: int, s
     check(f(ptr(logits), R, V, logits.stride(0), float(temperature), float(top_p), int(top_k), ptr(seeds),
             ptr(draw_counter), ptr(out), stream()), "sample")
     return out
+
+
+def advance_decode(tokens, tok_pos, seq_start, sampled) -> None:
+    """tokens <- sampled; positions and starts += 1 (one token per sequence), all on the device."""
+    need_cuda(tokens, tok_pos, seq_start, sampled)
+    B = tokens.shape[0]
+    need(all(t.dtype == torch.int32 and t.shape == (B,) for t in (tokens, tok_pos, seq_start, sampled)),
+         "advance_decode: four int32 arrays of one length")
+    f = _f("sampling", "rf_advance_decode", c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p)
+    check(f(ptr(tokens), ptr(tok_pos), ptr(seq_start), ptr(sampled), B, stream()), "advance_decode")

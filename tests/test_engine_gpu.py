@@ -136,7 +136,7 @@ def test_long_decoding(folders, name, dtype):
 def test_first_tokens_of_a_sequence(folders, dtype):
     from rocmforge_b200 import StepRequest
     m, p = engine(folders, "A", dtype), plain(folders, "A", dtype)
-    cache = m.new_cache(max_tokens=128)
+    cache = m.new_cache(max_tokens=256)
     toks = random_tokens(256, 4, 5)
     ref = p.logits(toks)
     s = cache.alloc_slot()

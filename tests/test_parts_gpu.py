@@ -21,6 +21,16 @@ def tol(dt):
     return dict(atol=2e-5, rtol=1e-4) if dt == torch.float32 else dict(atol=3e-2, rtol=3e-2)
 
 
+def close(got, ref, dt):
+    """32-bit: element-wise; bfloat16: within 2 % of the largest reference value."""
+    if dt == torch.float32:
+        torch.testing.assert_close(got, ref, atol=2e-5, rtol=1e-4)
+    else:
+        bound = 2e-2 * float(ref.abs().max())
+        worst = float((got - ref).abs().max())
+        assert worst <= bound, f"largest difference {worst:.4g} exceeds {bound:.4g}"
+
+
 def rnd(*shape, dt=torch.float32, seed=0, scale=1.0):
     g = torch.Generator().manual_seed(seed)
     return (torch.randn(*shape, generator=g) * scale).to(dt).to(DEV)
@@ -110,7 +120,7 @@ def test_attention_part_over_its_cache(dt, window):
         out = stream.flush().double().cpu()
         off = 0
         for i, n in enumerate(chunk):
-            torch.testing.assert_close(out[off:off + n], refs[i][done[i]:done[i] + n], **tol(dt))
+            close(out[off:off + n], refs[i][done[i]:done[i] + n], dt)
             off += n
             done[i] += n
     assert done == lens
