@@ -32,6 +32,7 @@ MODULES: Dict[str, List[str]] = {
     "gemm_simt": ["gemm_simt.cu", "common.cuh"],
     "attention_generic": ["attention_generic.cu", "common.cuh"],
     "sampling": ["sampling.cu", "common.cuh"],
+    "gemm_tcgen05": ["gemm_tcgen05.cu", "common.cuh"],
 }
 
 _loaded: Dict[str, ctypes.CDLL] = {}

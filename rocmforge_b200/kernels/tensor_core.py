@@ -1,0 +1,110 @@
+"""Python face of the tcgen05 matrix products (bfloat16 in, 32-bit accumulate)."""
+from __future__ import annotations
+
+import functools
+from typing import Optional
+
+import torch
+
+from ._ffi import KernelError, c_int, c_ll, c_void_p, check, fn, need, need_cuda, ptr, stream
+
+STORE, F32, RESIDUAL, SWIGLU, PARTIAL = 0, 1, 2, 3, 4
+SKINNY_MAX_TOKENS = 64
+
+_status = {}
+
+
+def status_word(device) -> torch.Tensor:
+    """Device word that a kernel sets when one of its bounded waits runs out."""
+    key = str(device)
+    if key not in _status:
+        _status[key] = torch.zeros((1,), dtype=torch.int32, device=device)
+    return _status[key]
+
+
+def check_status(device) -> None:
+    """Raise if a tensor-core kernel gave up waiting since the last check (synchronises)."""
+    key = str(device)
+    if key in _status and int(_status[key].item()) != 0:
+        _status[key].zero_()
+        raise KernelError("a tensor-core kernel ran out of its wait limit (a copy or an MMA never completed); "
+                          "its results are invalid")
+
+
+@functools.lru_cache(None)
+def _f(name, *argtypes):
+    return fn("gemm_tcgen05", name, list(argtypes))
+
+
+def supported(M: int, N: int, K: int, mode: int = STORE) -> bool:
+    f = _f("rf_gemm_tc_supported", c_int, c_int, c_int, c_int)
+    return bool(f(M, N, K, mode))
+
+
+def _common(x, w, bias, out):
+    need_cuda(x, w, bias, out)
+    need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "tensor-core gemm: x and w must be bfloat16")
+    need(x.dim() == 2 and w.dim() == 2 and x.stride(1) == 1 and w.is_contiguous() and x.shape[1] == w.shape[1],
+         "tensor-core gemm: x [M,K] and w [N,K] must be row-major with equal K")
+    need(x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and (x.stride(0) * 2) % 16 == 0,
+         "tensor-core gemm: operands must be 16-byte aligned")
+    if bias is not None:
+        need(bias.shape == (w.shape[0],) and bias.dtype in (torch.float32, torch.bfloat16), "gemm: bias must be [N]")
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, *, mode: int = STORE,
+            out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Tokens as accumulator rows (any M).  STORE -> bf16 [M,N]; F32 -> f32 [M,N]; RESIDUAL: out (f32) += x w^T;
+    SWIGLU -> bf16 [M, N/2] from row-interleaved gate/up weights."""
+    _common(x, w, bias, out)
+    M, K = x.shape
+    N = w.shape[0]
+    need(supported(M, N, K, mode), f"tensor-core gemm: shape {M}x{N}x{K} is not supported")
+    cols = N // 2 if mode == SWIGLU else N
+    odt = torch.bfloat16 if mode in (STORE, SWIGLU) else torch.float32
+    if out is None:
+        need(mode != RESIDUAL, "gemm: RESIDUAL needs the tensor to add into")
+        out = torch.empty((M, cols), dtype=odt, device=x.device)
+    need(out.shape == (M, cols) and out.dtype == odt and out.stride(1) == 1, "gemm: output has the wrong shape or dtype")
+    f = _f("rf_gemm_tc", c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
+           c_void_p, c_void_p)
+    check(f(ptr(x), x.stride(0), ptr(w), ptr(bias), int(bias is not None and bias.dtype == torch.float32), ptr(out),
+            out.stride(0), M, N, K, mode, ptr(status_word(x.device)), stream()), f"gemm_tc ({M}x{N}x{K})")
+    return out
+
+
+def split_k_for(N: int, K: int, sm_count: int = 148) -> int:
+    """K splits of a skinny product, from N and K alone (never from the batch), so that about one
+    wave of CTAs streams the weight and every split keeps at least 8 blocks of 64."""
+    tiles = (N + 127) // 128
+    kb = (K + 63) // 64
+    if tiles >= sm_count or kb < 16:
+        return 1
+    want = max(1, sm_count // tiles)
+    splits = max(1, min(want, kb // 8))
+    per = (kb + splits - 1) // splits
+    return (kb + per - 1) // per                   # no empty split
+
+
+def gemm_tc_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, *, mode: int = STORE,
+                   splits: int = 1, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Weights as accumulator rows, for at most 64 tokens.  With ``splits`` > 1 the mode must be PARTIAL and
+    the result is the float32 stack [splits, M, N] of partial sums."""
+    _common(x, w, bias, out)
+    M, K = x.shape
+    N = w.shape[0]
+    need(M <= SKINNY_MAX_TOKENS, f"skinny gemm takes at most {SKINNY_MAX_TOKENS} tokens, got {M}")
+    need(supported(M, N, K, mode), f"tensor-core gemm: shape {M}x{N}x{K} is not supported")
+    need(splits == 1 or mode == PARTIAL, "skinny gemm: several K splits need mode PARTIAL")
+    cols = N // 2 if mode == SWIGLU else N
+    odt = torch.bfloat16 if mode in (STORE, SWIGLU) else torch.float32
+    shape = (splits, M, N) if mode == PARTIAL else (M, cols)
+    if out is None:
+        need(mode != RESIDUAL, "gemm: RESIDUAL needs the tensor to add into")
+        out = torch.empty(shape, dtype=odt, device=x.device)
+    need(tuple(out.shape) == shape and out.dtype == odt and out.is_contiguous(), "gemm: output has the wrong shape or dtype")
+    f = _f("rf_gemm_tc_skinny", c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
+           c_int, c_int, c_void_p, c_void_p)
+    check(f(ptr(x), x.stride(0), ptr(w), ptr(bias), int(bias is not None and bias.dtype == torch.float32), ptr(out),
+            cols, M, N, K, mode, splits, ptr(status_word(x.device)), stream()), f"gemm_tc_skinny ({M}x{N}x{K})")
+    return out

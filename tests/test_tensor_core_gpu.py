@@ -1,0 +1,91 @@
+"""The tcgen05 matrix products alone, against float64 references (needs a GPU)."""
+import pytest
+import torch
+
+from plain import qwen2_plain as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def rnd(*shape, seed=0, scale=1.0, dt=torch.bfloat16):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dt).to(DEV)
+
+
+def close(got, ref, what=""):
+    """bfloat16 operands, 32-bit sums: within 1 % of the largest value for bf16 outputs, 1e-3 for f32 ones."""
+    scale = float(ref.abs().max())
+    rel = 1e-2 if got.dtype == torch.bfloat16 else 1e-4
+    err = float((got.double() - ref).abs().max())
+    assert err <= rel * scale, f"{what}: largest difference {err:.4g}, allowed {rel * scale:.4g}"
+
+
+SHAPES = [(1, 128, 64), (5, 48, 72), (128, 256, 128), (130, 200, 264), (300, 520, 1000), (2048, 4608, 3584),
+          (77, 3584, 18944), (257, 1000, 3584)]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_tokens_as_rows(M, N, K):
+    from rocmforge_b200.kernels import tensor_core as tc
+    x, w, b = rnd(M, K, seed=1), rnd(N, K, seed=2, scale=0.05), rnd(N, seed=3, dt=torch.float32)
+    ref = x.double() @ w.double().t()
+    close(tc.gemm_tc(x, w), ref, "store")
+    close(tc.gemm_tc(x, w, b, mode=tc.F32), ref + b.double(), "f32 + bias")
+    close(tc.gemm_tc(x, w, b.bfloat16()), ref + b.bfloat16().double(), "bf16 bias")
+    acc = rnd(M, N, seed=4, dt=torch.float32)
+    want = acc.double() + ref
+    tc.gemm_tc(x, w, mode=tc.RESIDUAL, out=acc)
+    close(acc, want, "residual")
+    if N % 2 == 0:
+        g, u = ref[:, 0::2], ref[:, 1::2]
+        close(tc.gemm_tc(x, w, mode=tc.SWIGLU), P.silu(g) * u, "swiglu")
+    tc.check_status(DEV)
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 16, 17, 33, 64])
+@pytest.mark.parametrize("N,K", [(128, 64), (200, 136), (3584, 3584), (1000, 18944), (4608, 3584)])
+def test_weights_as_rows(M, N, K):
+    from rocmforge_b200.kernels import tensor_core as tc
+    x, w, b = rnd(M, K, seed=5), rnd(N, K, seed=6, scale=0.05), rnd(N, seed=7, dt=torch.float32)
+    ref = x.double() @ w.double().t()
+    close(tc.gemm_tc_skinny(x, w), ref, "store")
+    close(tc.gemm_tc_skinny(x, w, b, mode=tc.F32), ref + b.double(), "f32 + bias")
+    acc = rnd(M, N, seed=8, dt=torch.float32)
+    want = acc.double() + ref
+    tc.gemm_tc_skinny(x, w, mode=tc.RESIDUAL, out=acc)
+    close(acc, want, "residual")
+    if N % 2 == 0:
+        close(tc.gemm_tc_skinny(x, w, mode=tc.SWIGLU), P.silu(ref[:, 0::2]) * ref[:, 1::2], "swiglu")
+    splits = tc.split_k_for(N, K)
+    for s in {1, splits, min(3, (K + 63) // 64)}:
+        parts = tc.gemm_tc_skinny(x, w, mode=tc.PARTIAL, splits=s)
+        assert tuple(parts.shape) == (s, M, N)
+        close(parts.double().sum(0).float(), ref, f"{s} partial sums")
+    # a token's result does not depend on the others in the batch
+    if M > 1:
+        alone = tc.gemm_tc_skinny(x[M - 1:M], w, mode=tc.F32)
+        assert torch.equal(alone, tc.gemm_tc_skinny(x, w, mode=tc.F32)[M - 1:M])
+    tc.check_status(DEV)
+
+
+def test_split_rule_depends_on_the_weight_only():
+    from rocmforge_b200.kernels import tensor_core as tc
+    assert tc.split_k_for(3584, 3584) > 1 and tc.split_k_for(152064, 3584) == 1
+    for N, K in ((3584, 3584), (3584, 18944), (4608, 3584), (896, 4864), (128, 64)):
+        s = tc.split_k_for(N, K)
+        kb = (K + 63) // 64
+        per = (kb + s - 1) // s
+        assert s >= 1 and (s - 1) * per < kb
+
+
+def test_refusals():
+    from rocmforge_b200.kernels import tensor_core as tc
+    from rocmforge_b200.kernels import KernelError
+    assert not tc.supported(4, 8, 12)                  # K * 2 bytes is not a multiple of 16
+    with pytest.raises(KernelError):
+        tc.gemm_tc(rnd(4, 12), rnd(8, 12))
+    with pytest.raises(KernelError):
+        tc.gemm_tc_skinny(rnd(65, 64), rnd(128, 64))
+    with pytest.raises(KernelError):
+        tc.gemm_tc(rnd(4, 64, dt=torch.float32), rnd(8, 64, dt=torch.float32))
