@@ -33,6 +33,7 @@ MODULES: Dict[str, List[str]] = {
     "attention_generic": ["attention_generic.cu", "common.cuh"],
     "sampling": ["sampling.cu", "common.cuh"],
     "gemm_tcgen05": ["gemm_tcgen05.cu", "common.cuh"],
+    "attention_decode": ["attention_decode.cu", "common.cuh"],
 }
 
 _loaded: Dict[str, ctypes.CDLL] = {}

@@ -60,11 +60,15 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const void* __restrict
 }
 
 // ---------------------------------------------------------------- rotation + cache write
-// qkv: [T, (nh + 2*nkv) * hd] rows of q | k | v.  q is rotated in place; k is rotated and
-// v copied into the page of (slot, position): pages are [n_pages, nkv, RF_PAGE, hd].
+// Rows of q | k | v, [T, (nh + 2*nkv) * hd], come either in the compute dtype (src, one tensor)
+// or as n_partials 32-bit partial sums of a K-split product plus a bias (the sum is formed here,
+// in index order).  q is rotated and written to q_out (which may be the source itself); k is
+// rotated and v copied into the page of (slot, position): pages are [n_pages, nkv, RF_PAGE, hd].
 // The angle is float(pos) * inv_freq[i] in 32-bit; sincosf is the accurate one.
-template <typename T>
-__global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, int nh, int nkv, int hd,
+template <typename T, bool PARTIALS>
+__global__ void rope_kv_write_kernel(const void* __restrict__ src, int row_stride, int n_partials,
+                                     size_t partial_stride, const void* __restrict__ bias, int bias_is_f32,
+                                     T* __restrict__ q_out, int q_out_stride, int nh, int nkv, int hd,
                                      const float* __restrict__ inv_freq,
                                      const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                                      const int* __restrict__ seq_slot,
@@ -73,7 +77,15 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, int nh
     const int t = blockIdx.x;
     const int pos = tok_pos[t];
     const int half = hd >> 1;
-    T* row = qkv + (size_t)t * row_stride;
+    auto value = [&](int col) -> float {
+        if (PARTIALS) {
+            const float* p = reinterpret_cast<const float*>(src) + (size_t)t * row_stride + col;
+            float v = bias ? load_vec(bias, bias_is_f32, col) : 0.f;
+            for (int s = 0; s < n_partials; ++s) v += p[(size_t)s * partial_stride];
+            return v;
+        }
+        return Cvt<T>::to_f32(reinterpret_cast<const T*>(src)[(size_t)t * row_stride + col]);
+    };
     size_t page_base = 0;
     if (write_kv) {
         const int slot = seq_slot[tok_seq[t]];
@@ -83,26 +95,26 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, int nh
     const int n_rot = (nh + nkv) * half;
     for (int idx = threadIdx.x; idx < n_rot; idx += blockDim.x) {
         const int head = idx / half, i = idx - head * half;
+        if (head >= nh && !write_kv) break;
         const float angle = (float)pos * inv_freq[i];
         float s, c;
         sincosf(angle, &s, &c);
-        T* x = row + (size_t)head * hd;
-        const float x0 = Cvt<T>::to_f32(x[i]), x1 = Cvt<T>::to_f32(x[i + half]);
+        const float x0 = value(head * hd + i), x1 = value(head * hd + i + half);
         const float r0 = x0 * c - x1 * s, r1 = x0 * s + x1 * c;
         if (head < nh) {
+            T* x = q_out + (size_t)t * q_out_stride + (size_t)head * hd;
             x[i] = Cvt<T>::from_f32(r0);
             x[i + half] = Cvt<T>::from_f32(r1);
-        } else if (write_kv) {
+        } else {
             T* dst = k_pages + page_base + (size_t)(head - nh) * RF_PAGE * hd;
             dst[i] = Cvt<T>::from_f32(r0);
             dst[i + half] = Cvt<T>::from_f32(r1);
         }
     }
     if (write_kv) {
-        const T* vsrc = row + (size_t)(nh + nkv) * hd;
         for (int idx = threadIdx.x; idx < nkv * hd; idx += blockDim.x) {
             const int head = idx / hd, i = idx - head * hd;
-            v_pages[page_base + (size_t)head * RF_PAGE * hd + i] = vsrc[idx];
+            v_pages[page_base + (size_t)head * RF_PAGE * hd + i] = Cvt<T>::from_f32(value((nh + nkv) * hd + idx));
         }
     }
 }
@@ -150,16 +162,21 @@ static int launch_add_rmsnorm(float* h, const void* pending, int kind, int n_pen
 }
 
 template <typename T>
-static int launch_rope_kv_write(void* qkv, int row_stride, int nh, int nkv, int hd, const float* inv_freq,
-                                const int* tok_seq, const int* tok_pos, const int* seq_slot,
-                                const int* block_table, int max_pages, void* k_pages, void* v_pages,
-                                int write_kv, int T_, cudaStream_t st) {
+static int launch_rope_kv_write(const void* src, int row_stride, int n_partials, size_t partial_stride,
+                                const void* bias, int bias_is_f32, void* q_out, int q_out_stride, int nh, int nkv,
+                                int hd, const float* inv_freq, const int* tok_seq, const int* tok_pos,
+                                const int* seq_slot, const int* block_table, int max_pages, void* k_pages,
+                                void* v_pages, int write_kv, int T_, cudaStream_t st) {
     if (T_ <= 0) return 0;
     if (hd % 2) return RF_ERR_BAD_ARG;
-    rope_kv_write_kernel<T><<<T_, 256, 0, st>>>(reinterpret_cast<T*>(qkv), row_stride, nh, nkv, hd, inv_freq,
-                                                tok_seq, tok_pos, seq_slot, block_table, max_pages,
-                                                reinterpret_cast<T*>(k_pages), reinterpret_cast<T*>(v_pages),
-                                                write_kv);
+    if (n_partials > 0)
+        rope_kv_write_kernel<T, true><<<T_, 256, 0, st>>>(src, row_stride, n_partials, partial_stride, bias,
+            bias_is_f32, reinterpret_cast<T*>(q_out), q_out_stride, nh, nkv, hd, inv_freq, tok_seq, tok_pos, seq_slot,
+            block_table, max_pages, reinterpret_cast<T*>(k_pages), reinterpret_cast<T*>(v_pages), write_kv);
+    else
+        rope_kv_write_kernel<T, false><<<T_, 256, 0, st>>>(src, row_stride, 0, 0, nullptr, 0,
+            reinterpret_cast<T*>(q_out), q_out_stride, nh, nkv, hd, inv_freq, tok_seq, tok_pos, seq_slot,
+            block_table, max_pages, reinterpret_cast<T*>(k_pages), reinterpret_cast<T*>(v_pages), write_kv);
     RF_LAUNCH_CHECK();
     return 0;
 }
@@ -187,13 +204,17 @@ int rf_add_rmsnorm(int dtype, float* h, const void* pending, int kind, int n_pen
         ? launch_add_rmsnorm<float>(h, pending, kind, n_pending, (size_t)pstride, w, w_is_f32, eps, y, rows, n_rows, H, st)
         : launch_add_rmsnorm<__nv_bfloat16>(h, pending, kind, n_pending, (size_t)pstride, w, w_is_f32, eps, y, rows, n_rows, H, st);
 }
-int rf_rope_kv_write(int dtype, void* qkv, int row_stride, int nh, int nkv, int hd, const float* inv_freq,
-                     const int* tok_seq, const int* tok_pos, const int* seq_slot, const int* block_table,
-                     int max_pages, void* k_pages, void* v_pages, int write_kv, int T_, cudaStream_t st) {
+int rf_rope_kv_write(int dtype, const void* src, int row_stride, int n_partials, long long partial_stride,
+                     const void* bias, int bias_is_f32, void* q_out, int q_out_stride, int nh, int nkv, int hd,
+                     const float* inv_freq, const int* tok_seq, const int* tok_pos, const int* seq_slot,
+                     const int* block_table, int max_pages, void* k_pages, void* v_pages, int write_kv, int T_,
+                     cudaStream_t st) {
     return dtype == 0
-        ? launch_rope_kv_write<float>(qkv, row_stride, nh, nkv, hd, inv_freq, tok_seq, tok_pos, seq_slot,
-                                      block_table, max_pages, k_pages, v_pages, write_kv, T_, st)
-        : launch_rope_kv_write<__nv_bfloat16>(qkv, row_stride, nh, nkv, hd, inv_freq, tok_seq, tok_pos, seq_slot,
+        ? launch_rope_kv_write<float>(src, row_stride, n_partials, (size_t)partial_stride, bias, bias_is_f32, q_out,
+                                      q_out_stride, nh, nkv, hd, inv_freq, tok_seq, tok_pos, seq_slot, block_table,
+                                      max_pages, k_pages, v_pages, write_kv, T_, st)
+        : launch_rope_kv_write<__nv_bfloat16>(src, row_stride, n_partials, (size_t)partial_stride, bias, bias_is_f32,
+                                              q_out, q_out_stride, nh, nkv, hd, inv_freq, tok_seq, tok_pos, seq_slot,
                                               block_table, max_pages, k_pages, v_pages, write_kv, T_, st);
 }
 int rf_swiglu(int dtype, const void* gu, void* a, int T_, int I, cudaStream_t st) {

@@ -35,6 +35,7 @@ class StepContext:
         self.device = model.device
         self.T, self.B, self.R = T, B, R
         self.is_decode, self.max_new, self.max_end = is_decode, max_new, max_end
+        self.model_cache_limit = max_end     # inside a replayed graph: the longest sequence the cache holds
         self.host = host                     # the StepBatch (host arrays); None inside a replayed graph
         self.replayed = False                # True inside a CUDA graph: launch shapes must be fixed
         self.tokens = views["tokens"]
@@ -47,22 +48,93 @@ class StepContext:
         self.want_rows = views["want_rows"]
 
     # ---------------------------------------------------------------- matrix products
+    def _tensor_cores(self, x, w, mode) -> bool:
+        return (self.compute_dtype == torch.bfloat16 and self.options.tensor_core_gemm
+                and kernels.tensor_core.supported(x.shape[0], w.shape[0], w.shape[1], mode)
+                and x.data_ptr() % 16 == 0 and (x.stride(0) * 2) % 16 == 0)
+
     def matmul(self, x, w, bias=None, *, out_f32=False):
+        """x [M,K] @ w[N,K]^T (+ bias) -> [M,N] in the compute dtype, or in float32."""
+        tc = kernels.tensor_core
+        mode = tc.F32 if out_f32 else tc.STORE
+        if self._tensor_cores(x, w, mode):
+            if x.shape[0] <= tc.SKINNY_MAX_TOKENS:
+                return tc.gemm_tc_skinny(x, w, bias, mode=mode)
+            return tc.gemm_tc(x, w, bias, mode=mode)
         return kernels.gemm_simt(x, w, bias, out_f32=out_f32)
 
     def matmul_residual(self, x, w, bias, stream) -> None:
-        """stream.h += x w^T (+ bias), summed in 32-bit."""
+        """stream += x w^T (+ bias), summed in 32-bit: into ``h`` directly, or left pending as the
+        32-bit partial sums of a K-split product (the next norm adds them in index order)."""
+        tc = kernels.tensor_core
+        if self._tensor_cores(x, w, tc.RESIDUAL):
+            if x.shape[0] <= tc.SKINNY_MAX_TOKENS:
+                splits = tc.split_k_for(w.shape[0], w.shape[1]) if bias is None else 1
+                if splits > 1:
+                    stream.add_pending(tc.gemm_tc_skinny(x, w, mode=tc.PARTIAL, splits=splits))
+                    return
+                stream.flush()
+                tc.gemm_tc_skinny(x, w, bias, mode=tc.RESIDUAL, out=stream.h)
+                return
+            stream.flush()
+            tc.gemm_tc(x, w, bias, mode=tc.RESIDUAL, out=stream.h)
+            return
         stream.flush()
         kernels.gemm_simt(x, w, bias, out=stream.h, accumulate=True)
 
     def gated_activation(self, y, gate_up):
         """silu(gate) * up from the fused, row-interleaved gate/up matrix."""
-        gu = self.matmul(y, gate_up.weight, gate_up.bias)
+        tc = kernels.tensor_core
+        w = gate_up.weight
+        if gate_up.bias is None and self._tensor_cores(y, w, tc.SWIGLU):
+            if y.shape[0] <= tc.SKINNY_MAX_TOKENS:
+                return tc.gemm_tc_skinny(y, w, mode=tc.SWIGLU)
+            return tc.gemm_tc(y, w, mode=tc.SWIGLU)
+        gu = self.matmul(y, w, gate_up.bias)
         return kernels.swiglu(gu)
 
     # ---------------------------------------------------------------- attention
-    def attention(self, qkv, mixer, view):
-        """Attention of the step's tokens over the cache; q is the first heads*head_dim columns of ``qkv``."""
-        return kernels.attention_generic(qkv, mixer.n_heads, mixer.n_kv_heads, mixer.head_dim,
-                                         view.k_pages, view.v_pages, self.tok_seq, self.tok_pos,
+    def project_qkv_into_cache(self, y, mixer, view):
+        """q/k/v projection (+ bias), rotation, cache write; returns rotated q [T, >= heads*head_dim].
+
+        With few tokens on the tensor-core path the product is K-split for parallelism and the
+        rotation kernel sums the 32-bit partial sums (and the bias) itself, so q/k/v never
+        exist as an intermediate bfloat16 tensor.
+        """
+        tc = kernels.tensor_core
+        w, bias = mixer.qkv.weight, mixer.qkv.bias
+        rope = dict(tok_seq=self.tok_seq, tok_pos=self.tok_pos, seq_slot=self.seq_slot,
+                    block_table=view.block_table, k_pages=view.k_pages, v_pages=view.v_pages, write_kv=view.writes)
+        if y.shape[0] <= tc.SKINNY_MAX_TOKENS and self._tensor_cores(y, w, tc.PARTIAL):
+            splits = tc.split_k_for(w.shape[0], w.shape[1])
+            if splits > 1:
+                parts = tc.gemm_tc_skinny(y, w, mode=tc.PARTIAL, splits=splits)
+                return kernels.rope_kv_write(parts, mixer.n_heads, mixer.n_kv_heads, mixer.head_dim,
+                                             mixer.position.inv_freq, bias=bias, compute_dtype=self.compute_dtype,
+                                             **rope)
+        qkv = self.matmul(y, w, bias)
+        return kernels.rope_kv_write(qkv, mixer.n_heads, mixer.n_kv_heads, mixer.head_dim,
+                                     mixer.position.inv_freq, **rope)
+
+    def attention(self, q, mixer, view):
+        """Attention of the step's tokens over the cache; q is the first heads*head_dim columns of ``q``."""
+        nh, nkv, hd = mixer.n_heads, mixer.n_kv_heads, mixer.head_dim
+        if (self.is_decode and self.compute_dtype == torch.bfloat16 and self.options.tuned_attention
+                and kernels.attention_decode_supported(nh, nkv, hd)):
+            longest = self.model_cache_limit if self.replayed else self.max_end
+            need = max(1, (longest + kernels.DECODE_CHUNK - 1) // kernels.DECODE_CHUNK)
+            max_chunks = 1
+            while max_chunks < need:                   # powers of two: few distinct scratch sizes
+                max_chunks *= 2
+            cap = 1
+            while cap < self.B:
+                cap *= 2
+            n_o, n_ml, n_c = kernels.attention_decode_scratch(cap, nh, nkv, hd, max_chunks)
+            scratch = self.model.scratch
+            return kernels.attention_decode(
+                q, nh, nkv, hd, view.k_pages, view.v_pages, self.tok_seq, self.tok_pos, self.seq_slot,
+                view.block_table, mixer.scale, view.window, max_chunks,
+                scratch("attn_decode_o", n_o, torch.float32), scratch("attn_decode_ml", n_ml, torch.float32),
+                scratch("attn_decode_counters", n_c, torch.int32))
+        return kernels.attention_generic(q, nh, nkv, hd, view.k_pages, view.v_pages, self.tok_seq, self.tok_pos,
                                          self.seq_slot, view.block_table, mixer.scale, view.window)

@@ -81,6 +81,8 @@ class ModelSpec:
 
     def cuda_modules(self, compute_dtype) -> List[str]:
         mods: List[str] = ["gemm_simt", "sampling"]
+        if compute_dtype == torch.bfloat16:
+            mods.append("gemm_tcgen05")
         for part in self.named_parts().values():
             mods += part.cuda_modules(compute_dtype)
         return list(dict.fromkeys(mods))
@@ -105,6 +107,7 @@ class Model:
                      if name.startswith(prefix) and name[len(prefix):] in part.param_specs()}
             part.bind(local, compute_dtype)
         self._desc = DeviceDescriptor(self.device)
+        self._scratch: Dict[tuple, torch.Tensor] = {}
         self.weight_bytes = sum(t.numel() * t.element_size()
                                 for t in {t.data_ptr(): t for t in params.values()}.values())
 
@@ -131,6 +134,14 @@ class Model:
             if name not in params:
                 params[name] = params[s.tied_to]
         return cls(spec, params, dtype, device, options)
+
+    def scratch(self, name: str, n: int, dtype: torch.dtype) -> torch.Tensor:
+        """Zero-initialised scratch memory that kernels share from launch to launch.  A buffer, once handed
+        out, is never freed or moved (captured graphs keep its address); a larger request gets a new one."""
+        key = (name, n, dtype)
+        if key not in self._scratch:
+            self._scratch[key] = torch.zeros((max(n, 1),), dtype=dtype, device=self.device)
+        return self._scratch[key]
 
     # ---------------------------------------------------------------- cache
     def new_cache(self, max_tokens: int, max_slots: Optional[int] = None) -> SequenceCache:

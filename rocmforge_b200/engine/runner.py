@@ -5,6 +5,7 @@ from typing import List, Optional, Sequence
 
 import torch
 
+from .. import kernels
 from ..cache import pages_for
 from ..sampling import DeviceSampler, SamplingParams
 from .batch import StepRequest
@@ -49,4 +50,6 @@ class ModelEngine(StepEngine):
             reqs = [StepRequest(s, t, [len(t) - 1]) for s, t in zip(slots, tokens)]
             logits = self.model.step(self.cache, reqs)
             out = self.sampler.sample(logits, sampling, requests, draws)
-        return out.cpu().tolist()
+        ids = out.cpu().tolist()
+        kernels.tensor_core.check_status(self.model.device)
+        return ids

@@ -21,6 +21,7 @@ from typing import Dict, IO
 import numpy as np
 import torch
 
+from .. import kernels
 from .batch import StepRequest
 
 
@@ -64,6 +65,7 @@ def replay(model, cache, lines: IO[str], out_dir: str, reply: IO[str] = sys.stdo
                 arr.tofile(os.path.join(out_dir, f"{step}.f32"))
             else:
                 torch.cuda.synchronize(model.device)
+            kernels.tensor_core.check_status(model.device)
         for rid in msg.get("end", []):
             rid = str(rid)
             if rid not in slot_of:

@@ -1,4 +1,5 @@
 from ._ffi import KernelError
-from .basic import (PAGE, embed, add_rmsnorm, rope_kv_write, swiglu, gemm_simt, attention_generic, argmax, sample, advance_decode)
+from .basic import (PAGE, embed, add_rmsnorm, rope_kv_write, swiglu, gemm_simt, attention_generic, argmax, sample, advance_decode,
+                    attention_decode, attention_decode_supported, attention_decode_scratch, DECODE_CHUNK)
 from ._ffi import launch_count
 from . import tensor_core

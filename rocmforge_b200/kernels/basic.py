@@ -79,24 +79,49 @@ def add_rmsnorm(h: torch.Tensor, weight: torch.Tensor, eps: float, compute_dtype
 
 def rope_kv_write(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, inv_freq: torch.Tensor,
                   tok_seq, tok_pos, seq_slot, block_table: torch.Tensor,
-                  k_pages: torch.Tensor | None, v_pages: torch.Tensor | None, write_kv: bool = True) -> None:
-    """Rotate q (in place) and k by position; write rotated k and v into their cache pages."""
-    need_cuda(qkv, inv_freq, tok_seq, tok_pos, seq_slot, block_table, k_pages, v_pages)
-    T = qkv.shape[0]
-    need(qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] == (n_heads + 2 * n_kv_heads) * head_dim,
-         "rope_kv_write: qkv must be [T, (heads + 2 kv_heads) * head_dim]")
+                  k_pages: torch.Tensor | None, v_pages: torch.Tensor | None, write_kv: bool = True, *,
+                  bias: torch.Tensor | None = None, compute_dtype: torch.dtype | None = None,
+                  q_out: torch.Tensor | None = None) -> torch.Tensor:
+    """Rotate q and k by position; write rotated k and v into their cache pages; return q.
+
+    ``qkv`` is [T, (heads + 2 kv_heads) * head_dim] in the compute dtype (q is then rotated in place and
+    the returned q is a view of it), or a float32 stack [S, T, ...] of partial sums of a K-split product,
+    to which ``bias`` is added (q then goes to a new [T, heads * head_dim] tensor of ``compute_dtype``).
+    """
+    need_cuda(qkv, inv_freq, tok_seq, tok_pos, seq_slot, block_table, k_pages, v_pages, bias)
+    width = (n_heads + 2 * n_kv_heads) * head_dim
+    partials = qkv.dim() == 3
+    if partials:
+        need(qkv.dtype == torch.float32 and qkv.is_contiguous() and qkv.shape[2] == width,
+             "rope_kv_write: partial sums must be a contiguous float32 [S, T, width] stack")
+        need(compute_dtype is not None, "rope_kv_write: partial sums need the compute dtype")
+        S, T = qkv.shape[0], qkv.shape[1]
+        dt = compute_dtype
+        if q_out is None:
+            q_out = torch.empty((T, n_heads * head_dim), dtype=dt, device=qkv.device)
+        row_stride, pstride = width, T * width
+    else:
+        need(qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] == width,
+             "rope_kv_write: qkv must be [T, (heads + 2 kv_heads) * head_dim]")
+        need(bias is None, "rope_kv_write: a bias goes with partial sums only")
+        S, T, dt = 0, qkv.shape[0], qkv.dtype
+        q_out = qkv
+        row_stride, pstride = qkv.stride(0), 0
     need(inv_freq.dtype == torch.float32 and inv_freq.numel() == head_dim // 2,
          "rope_kv_write: inv_freq must hold head_dim/2 float32 frequencies")
     if write_kv:
         for p in (k_pages, v_pages):
-            need(p is not None and p.dtype == qkv.dtype and p.is_contiguous()
+            need(p is not None and p.dtype == dt and p.is_contiguous()
                  and tuple(p.shape[1:]) == (n_kv_heads, PAGE, head_dim),
                  "rope_kv_write: pages must be [n_pages, kv_heads, 64, head_dim] of the compute dtype")
-    f = _f("elementwise", "rf_rope_kv_write", c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
-           c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p)
-    check(f(dtype_code(qkv.dtype), ptr(qkv), qkv.stride(0), n_heads, n_kv_heads, head_dim, ptr(inv_freq),
-            ptr(tok_seq), ptr(tok_pos), ptr(seq_slot), ptr(block_table), block_table.shape[1],
-            ptr(k_pages), ptr(v_pages), int(write_kv), T, stream()), "rope_kv_write")
+    f = _f("elementwise", "rf_rope_kv_write", c_int, c_void_p, c_int, c_int, c_ll, c_void_p, c_int, c_void_p, c_int,
+           c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
+           c_int, c_void_p)
+    check(f(dtype_code(dt), ptr(qkv), row_stride, S, pstride, ptr(bias),
+            int(bias is not None and bias.dtype == torch.float32), ptr(q_out), q_out.stride(0), n_heads, n_kv_heads,
+            head_dim, ptr(inv_freq), ptr(tok_seq), ptr(tok_pos), ptr(seq_slot), ptr(block_table),
+            block_table.shape[1], ptr(k_pages), ptr(v_pages), int(write_kv), T, stream()), "rope_kv_write")
+    return q_out
 
 
 def swiglu(gu: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
@@ -203,3 +228,51 @@ def advance_decode(tokens, tok_pos, seq_start, sampled) -> None:
          "advance_decode: four int32 arrays of one length")
     f = _f("sampling", "rf_advance_decode", c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p)
     check(f(ptr(tokens), ptr(tok_pos), ptr(seq_start), ptr(sampled), B, stream()), "advance_decode")
+
+
+def attention_decode_supported(n_heads: int, n_kv_heads: int, head_dim: int) -> bool:
+    f = _f("attention_decode", "rf_attention_decode_supported", c_int, c_int, c_int)
+    return bool(f(n_heads, n_kv_heads, head_dim))
+
+
+DECODE_CHUNK = 256
+
+
+def attention_decode_scratch(B: int, n_heads: int, n_kv_heads: int, head_dim: int, max_chunks: int):
+    """Element counts (partial outputs, partial max/sum, counters) the decode attention needs for B sequences."""
+    return (B * n_heads * max_chunks * head_dim, B * n_heads * max_chunks * 2, B * n_kv_heads)
+
+
+def attention_decode(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, k_pages, v_pages,
+                     tok_seq, tok_pos, seq_slot, block_table, scale: float, window: int | None, max_chunks: int,
+                     part_o: torch.Tensor, part_ml: torch.Tensor, counters: torch.Tensor,
+                     out: torch.Tensor | None = None) -> torch.Tensor:
+    """One new token per sequence over the bfloat16 paged cache, keys in chunks of 256.
+
+    ``max_chunks`` must cover the longest sequence (ceil(length / 256)); ``part_o``, ``part_ml`` (float32)
+    and ``counters`` (int32, zero before the first call; the kernel leaves them zero) are scratch of at
+    least ``attention_decode_scratch`` elements.
+    """
+    need_cuda(q, k_pages, v_pages, tok_seq, tok_pos, seq_slot, block_table, part_o, part_ml, counters)
+    B = q.shape[0]
+    need(q.dtype == torch.bfloat16 and q.dim() == 2 and q.stride(1) == 1, "attention_decode: q must be bfloat16 [B, ...]")
+    need(k_pages.dtype == torch.bfloat16 and tuple(k_pages.shape[1:]) == (n_kv_heads, PAGE, head_dim)
+         and k_pages.is_contiguous() and v_pages.shape == k_pages.shape and v_pages.is_contiguous(),
+         "attention_decode: bad cache page shape or dtype")
+    need(attention_decode_supported(n_heads, n_kv_heads, head_dim),
+         f"attention_decode: heads={n_heads}, kv_heads={n_kv_heads}, head_dim={head_dim} is not supported")
+    n_o, n_ml, n_c = attention_decode_scratch(B, n_heads, n_kv_heads, head_dim, max_chunks)
+    need(part_o.dtype == torch.float32 and part_o.numel() >= n_o and part_ml.dtype == torch.float32
+         and part_ml.numel() >= n_ml and counters.dtype == torch.int32 and counters.numel() >= n_c,
+         "attention_decode: scratch tensors are too small")
+    need(q.data_ptr() % 4 == 0, "attention_decode: q must be 4-byte aligned")
+    if out is None:
+        out = torch.empty((B, n_heads * head_dim), dtype=torch.bfloat16, device=q.device)
+    f = _f("attention_decode", "rf_attention_decode", c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+           c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p,
+           c_void_p, c_void_p)
+    check(f(ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(k_pages), ptr(v_pages), ptr(tok_seq), ptr(tok_pos),
+            ptr(seq_slot), ptr(block_table), block_table.shape[1], n_heads, n_kv_heads, head_dim, float(scale),
+            int(window or 0), B, max_chunks, ptr(part_o), ptr(part_ml), ptr(counters), stream()),
+          f"attention_decode (heads={n_heads}, kv_heads={n_kv_heads}, head_dim={head_dim})")
+    return out

@@ -68,15 +68,15 @@ class GQAAttention(Mixer):
             self.position.prepare(w.device)
 
     def cuda_modules(self, compute_dtype):
-        return ["elementwise", "attention_generic"]
+        mods = ["elementwise", "attention_generic"]
+        if compute_dtype == torch.bfloat16:
+            mods.append("attention_decode")
+        return mods
 
     def cache_request(self):
         return KVRequest(self.n_kv_heads, self.head_dim, self.window)
 
     def forward(self, ctx, y, cache_view, stream):
-        qkv = self.qkv(ctx, y)                                              # [T, q + 2 kv]
-        kernels.rope_kv_write(qkv, self.n_heads, self.n_kv_heads, self.head_dim, self.position.inv_freq,
-                              ctx.tok_seq, ctx.tok_pos, ctx.seq_slot, cache_view.block_table,
-                              cache_view.k_pages, cache_view.v_pages, write_kv=cache_view.writes)
-        o = ctx.attention(qkv, self, cache_view)
+        q = ctx.project_qkv_into_cache(y, self, cache_view)                 # rotated q; k, v are in the cache
+        o = ctx.attention(q, self, cache_view)
         self.o.add_to_stream(ctx, o, stream)

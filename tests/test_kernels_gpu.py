@@ -232,6 +232,96 @@ def test_rope_kv_write(dt, nh, nkv, hd):
     assert torch.equal(qkv2, qkv) and float(k2.abs().sum()) == 0
 
 
+@pytest.mark.parametrize("nh,nkv,hd,window", [(28, 4, 128, None), (14, 2, 64, None), (4, 4, 32, 300), (16, 1, 16, None),
+                                              (3, 3, 256, None), (12, 4, 128, 1000), (8, 2, 64, 64)])
+def test_attention_decode(nh, nkv, hd, window):
+    """One new token per sequence over contexts that end inside, at and beyond chunk borders."""
+    from rocmforge_b200 import kernels
+    dt = torch.bfloat16
+    lens = [1, 255, 256, 257, 700, 1500, 64]
+    B = len(lens)
+    ks, vs, k_pages, v_pages, table = paged(lens, nkv, hd, dt, n_pages=64, seed=nh + hd)
+    g = torch.Generator().manual_seed(2)
+    q = torch.randn(B, nh * hd, generator=g).to(dt)
+    tok_seq = torch.arange(B, dtype=torch.int32, device=DEV)
+    tok_pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV)
+    seq_slot = torch.arange(1, B + 1, dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(hd)
+    refs = [attention_reference(q[b].view(nh, hd), ks[b], vs[b], lens[b] - 1, scale, window) for b in range(B)]
+    for max_chunks in (6, 16):                             # exactly enough, and a replayed graph's fixed shape
+        n_o, n_ml, n_c = kernels.attention_decode_scratch(B, nh, nkv, hd, max_chunks)
+        part_o = torch.full((n_o,), float("nan"), device=DEV)
+        part_ml = torch.full((n_ml,), float("nan"), device=DEV)
+        counters = torch.zeros(n_c, dtype=torch.int32, device=DEV)
+        for rep in range(2):                               # the second launch finds the counters as the first left them
+            out = kernels.attention_decode(q.to(DEV), nh, nkv, hd, k_pages, v_pages, tok_seq, tok_pos, seq_slot,
+                                           table, scale, window, max_chunks, part_o, part_ml, counters)
+            assert torch.isfinite(out.float()).all()
+            assert int(counters.abs().sum()) == 0
+            for b in range(B):
+                torch.testing.assert_close(out[b].cpu().double().view(nh, hd), refs[b], atol=2e-2, rtol=2e-2)
+    gen = kernels.attention_generic(q.to(DEV), nh, nkv, hd, k_pages, v_pages, tok_seq, tok_pos, seq_slot, table,
+                                    scale, window)
+    torch.testing.assert_close(out.float(), gen.float(), atol=2e-2, rtol=2e-2)
+
+
+def test_attention_decode_finds_far_keys_and_the_window_edge():
+    from rocmforge_b200 import kernels
+    dt, nh, nkv, hd, n = torch.bfloat16, 2, 1, 64, 900
+    ks, vs, k_pages, v_pages, table = paged([n], nkv, hd, dt, n_pages=20, seed=5)
+    q = torch.zeros(1, nh * hd); q[0, 0] = 8.0; q[0, hd + 1] = 8.0      # head 0 looks along dim 0, head 1 along dim 1
+    zero = torch.zeros(1, dtype=torch.int32, device=DEV)
+    n_o, n_ml, n_c = kernels.attention_decode_scratch(1, nh, nkv, hd, 4)
+    scratch = (torch.zeros(n_o, device=DEV), torch.zeros(n_ml, device=DEV), torch.zeros(n_c, dtype=torch.int32, device=DEV))
+
+    def run(t0, t1, window):
+        kp = k_pages.clone()
+        for dim, t in ((0, t0), (1, t1)):
+            page = int(table[1, t // 64])
+            kp[page, 0, t % 64, dim] = 60.0
+        return kernels.attention_decode(q.to(dt).to(DEV), nh, nkv, hd, kp, v_pages, zero,
+                                        torch.tensor([n - 1], dtype=torch.int32, device=DEV),
+                                        torch.tensor([1], dtype=torch.int32, device=DEV), table, 1.0 / math.sqrt(hd),
+                                        window, 4, *scratch)[0].float().cpu().view(nh, hd)
+
+    for t0, t1 in ((0, 899), (255, 256), (511, 512), (63, 64), (700, 3)):
+        out = run(t0, t1, None)
+        torch.testing.assert_close(out[0], vs[0][t0, 0].float(), atol=2e-2, rtol=2e-2)
+        torch.testing.assert_close(out[1], vs[0][t1, 0].float(), atol=2e-2, rtol=2e-2)
+    out = run(500, 499, 400)                             # the query at 899 sees 500..899: 500 is in, 499 is out
+    torch.testing.assert_close(out[0], vs[0][500, 0].float(), atol=2e-2, rtol=2e-2)
+    assert (out[1] - vs[0][499, 0].float()).abs().max() > 0.1
+
+
+def test_rope_kv_write_from_partial_sums():
+    """The rotation kernel adds the 32-bit partial sums of a K-split product and the bias itself."""
+    from rocmforge_b200 import kernels
+    from rocmforge_b200.parts import NeoxRope
+    nh, nkv, hd, T, S = 6, 2, 32, 5, 3
+    width = (nh + 2 * nkv) * hd
+    rope = NeoxRope(hd, 1e4); rope.prepare(DEV)
+    parts = rnd(S, T, width, seed=1)
+    bias = rnd(width, seed=2)
+    pos = torch.tensor([0, 5, 64, 130, 9], dtype=torch.int32, device=DEV)
+    seq = torch.arange(T, dtype=torch.int32, device=DEV)
+    slots = torch.arange(T, dtype=torch.int32, device=DEV)
+    table = (torch.arange(T * 4, dtype=torch.int32).view(T, 4)).to(DEV)
+    total = (parts.sum(0) + bias)
+    for dt in DTS:
+        kp = torch.zeros(T * 4, nkv, 64, hd, dtype=dt, device=DEV)
+        vp = torch.zeros_like(kp)
+        q = kernels.rope_kv_write(parts, nh, nkv, hd, rope.inv_freq, seq, pos, slots, table, kp, vp, bias=bias,
+                                  compute_dtype=dt)
+        kp2, vp2 = torch.zeros_like(kp), torch.zeros_like(vp)
+        whole = total.to(dt).clone()
+        q2 = kernels.rope_kv_write(whole, nh, nkv, hd, rope.inv_freq, seq, pos, slots, table, kp2, vp2)
+        t = dict(atol=1e-5, rtol=1e-5) if dt == torch.float32 else dict(atol=4e-2, rtol=2e-2)
+        torch.testing.assert_close(q.float(), q2[:, :nh * hd].float(), **t)
+        torch.testing.assert_close(kp.float(), kp2.float(), **t)
+        torch.testing.assert_close(vp.float(), vp2.float(), **t)
+        assert tuple(q.shape) == (T, nh * hd) and q.dtype == dt
+
+
 def test_argmax_ties_and_sizes():
     from rocmforge_b200 import kernels
     x = rnd(5, 152064, seed=9)

@@ -40,7 +40,11 @@ def context(dt, requests, starts, vocab=1 << 20):
     """A StepContext for parts tested outside a model."""
     from rocmforge_b200.engine import Options, StepBatch, StepContext, StepRequest
     from rocmforge_b200.engine.batch import DeviceDescriptor
-    fake_model = SimpleNamespace(options=Options(), compute_dtype=dt, device=torch.device(DEV))
+    pool = {}
+
+    def scratch(name, n, dtype):
+        return pool.setdefault((name, n, dtype), torch.zeros((max(n, 1),), dtype=dtype, device=DEV))
+    fake_model = SimpleNamespace(options=Options(), compute_dtype=dt, device=torch.device(DEV), scratch=scratch)
     batch = StepBatch([StepRequest(*r) for r in requests], starts, vocab)
     desc = DeviceDescriptor(DEV)
     desc.upload(batch.pack())
