@@ -1,37 +1,51 @@
 // Decode attention over the paged cache: one new token per sequence, bfloat16 cache.
 //
-// The context is cut into chunks of 256 keys; a CTA owns (chunk, kv head, sequence) and
-// serves ALL query heads of that kv head's group from one pass over the chunk's keys and
-// values (maeddesg/ROCmForge's flash_attn_decode_gqa_kernel has the same idea with 32-key
-// tiles in LDS and one block per kv head, hip_kernels/attention.hip:633-798; its dispatched
-// decode kernel keeps all scores of a head in LDS, :148-213).  Scores, softmax and the
-// output sums are 32-bit.  Each CTA writes its chunk's (max, sum, unnormalised output) to
-// scratch memory; the CTA that finishes last for a (sequence, kv head) merges the chunks in
-// index order, so the result does not depend on which CTA that was.  The grid may be larger
-// than the context needs (a replayed CUDA graph keeps its launch shape): CTAs beyond the
-// sequence's last chunk, or wholly before its window, leave at once.
+// The context is cut into chunks of 128 keys (two cache pages); a CTA owns (chunk, kv head,
+// sequence) and serves ALL query heads of that kv head's group from one pass over the
+// chunk's keys and values (maeddesg/ROCmForge's flash_attn_decode_gqa_kernel has the same idea
+// with 32-key tiles in LDS and one block per kv head, hip_kernels/attention.hip:633-798; its
+// dispatched decode kernel keeps all scores of a head in LDS, :148-213).  A page's keys (or
+// values) of one kv head are one contiguous slab, so the whole chunk is brought into shared
+// memory by four bulk async copies that are all in flight at once.  Both products run on the
+// tensor cores (mma.sync m16n8k16, bf16 in, 32-bit accumulate) with the group's query heads
+// as the 16 rows: Q K^T into 32-bit scores, the softmax in 32-bit, the weights rounded to
+// bfloat16 as the operand of P V (as maeddesg/ROCmForge's WMMA attention rounds them to FP16,
+// hip_kernels/wmma/wmma_attention_prefill.hip:574).  Each CTA writes its chunk's (max, sum, unnormalised
+// output) to scratch memory; the CTA that finishes last for a (sequence, kv head) merges
+// the chunks in index order, so the result does not depend on which CTA that was.  The grid
+// may be larger than the context needs (a replayed CUDA graph keeps its launch shape): CTAs
+// beyond the sequence's last chunk, or wholly before its window, leave at once.
 #include "common.cuh"
 
-#define DEC_THREADS 256
-#define DEC_CHUNK 256
+#define DEC_THREADS 128
+#define DEC_WARPS 4
+#define DEC_CHUNK 128
+#define DEC_GP 8                      // query heads per kv head, padded
+#define DEC_WAIT_LIMIT_NS 2000000000ULL
 
-template <int GP>
+__device__ __forceinline__ uint32_t dec_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+template <int EPL>
 __global__ void __launch_bounds__(DEC_THREADS)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* __restrict__ out,
                         int out_stride, const __nv_bfloat16* __restrict__ k_pages,
                         const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ tok_seq,
                         const int* __restrict__ tok_pos, const int* __restrict__ seq_slot,
-                        const int* __restrict__ block_table, int max_pages, int nh, int nkv, int hd, float scale,
+                        const int* __restrict__ block_table, int max_pages, int nh, int nkv, float scale,
                         int window, int max_chunks, float* __restrict__ part_o, float* __restrict__ part_ml,
-                        int* __restrict__ counters) {
-    extern __shared__ float sm[];
-    const int G = nh / nkv;
-    float* q_s = sm;                                   // [GP][hd]
-    float* p_s = q_s + GP * hd;                        // [GP][DEC_CHUNK]
-    float* wred = p_s + GP * DEC_CHUNK;                // [8 warps][GP]
-    float* o_red = wred + 8 * GP;                      // [n_ks][GP][hd]
-    __shared__ int is_last;
+                        int* __restrict__ counters, int* __restrict__ status) {
+    constexpr int HD = EPL * 32;
+    constexpr uint32_t SLAB = RF_PAGE * HD * 2;                 // bytes of one page's keys of one kv head
+    extern __shared__ __align__(128) uint8_t dec_smem[];
+    __nv_bfloat16* k_s = reinterpret_cast<__nv_bfloat16*>(dec_smem);                   // [128][HD]
+    __nv_bfloat16* v_s = k_s + DEC_CHUNK * HD;                                          // [128][HD]
+    float* p_s = reinterpret_cast<float*>(v_s + DEC_CHUNK * HD);                        // [GP][128] scores, then weights
+    float* wred = p_s + DEC_GP * DEC_CHUNK;                                             // [4 warps][GP]
+    uint64_t* bar = reinterpret_cast<uint64_t*>(wred + DEC_WARPS * DEC_GP);
+    float* o_red = reinterpret_cast<float*>(dec_smem);                                 // [4][GP][HD], over k_s when done
+    __shared__ int is_last, gave_up;
 
+    const int G = nh / nkv;
     const int c = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z, tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
     const int pos = tok_pos[b];
@@ -41,131 +55,178 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
     const int n_act = c_hi - c_lo + 1;
     const int slot = seq_slot[tok_seq[b]];
     const int* bt = block_table + (size_t)slot * max_pages;
-
-    const __nv_bfloat16* qrow = q + (size_t)b * q_stride + (size_t)kvh * G * hd;
-    for (int i = tid; i < G * hd; i += DEC_THREADS) q_s[i] = __bfloat162float(qrow[i]) * scale;
-    __syncthreads();
-
-    // ---- scores: one key per thread, all heads of the group
-    const int j = c * DEC_CHUNK + tid;
-    const bool valid = j >= lo && j <= pos;
-    float s[GP];
-#pragma unroll
-    for (int g = 0; g < GP; ++g) s[g] = 0.f;
-    if (valid) {
-        const int page = bt[j / RF_PAGE];
-        const uint4* kr = reinterpret_cast<const uint4*>(
-            k_pages + ((size_t)page * nkv + kvh) * RF_PAGE * hd + (size_t)(j % RF_PAGE) * hd);
-        for (int v8 = 0; v8 < hd / 8; ++v8) {
-            const uint4 raw = kr[v8];
-            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
-            float kf[8];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float2 f = __bfloat1622float2(h2[i]);
-                kf[2 * i] = f.x; kf[2 * i + 1] = f.y;
-            }
-#pragma unroll
-            for (int g = 0; g < GP; ++g) {
-                if (g < G) {
-                    const float4 qa = *reinterpret_cast<const float4*>(q_s + g * hd + v8 * 8);
-                    const float4 qb = *reinterpret_cast<const float4*>(q_s + g * hd + v8 * 8 + 4);
-                    s[g] += kf[0] * qa.x + kf[1] * qa.y + kf[2] * qa.z + kf[3] * qa.w
-                          + kf[4] * qb.x + kf[5] * qb.y + kf[6] * qb.z + kf[7] * qb.w;
-                }
-            }
-        }
-    }
-    // ---- chunk maximum per head
-    float m[GP], l[GP];
-#pragma unroll
-    for (int g = 0; g < GP; ++g) {
-        float v = valid ? s[g] : -INFINITY;
-        v = warp_max(v);
-        if (lane == 0) wred[warp * GP + g] = v;
-    }
-    __syncthreads();
-#pragma unroll
-    for (int g = 0; g < GP; ++g) {
-        float v = wred[g];
-#pragma unroll
-        for (int w = 1; w < 8; ++w) v = fmaxf(v, wred[w * GP + g]);
-        m[g] = v;
-    }
-    __syncthreads();
-#pragma unroll
-    for (int g = 0; g < GP; ++g) {
-        const float p = valid ? expf(s[g] - m[g]) : 0.f;
-        p_s[g * DEC_CHUNK + tid] = p;
-        const float v = warp_sum(p);
-        if (lane == 0) wred[warp * GP + g] = v;
-    }
-    __syncthreads();
-#pragma unroll
-    for (int g = 0; g < GP; ++g) {
-        float v = wred[g];
-#pragma unroll
-        for (int w = 1; w < 8; ++w) v += wred[w * GP + g];
-        l[g] = v;
-    }
-
-    // ---- values: thread = (pair of dimensions, subset of keys), all heads of the group
-    const int half = hd >> 1, n_ks = DEC_THREADS / half;
-    const int dp = tid % half, ks = tid / half;
-    float acc[GP][2];
-#pragma unroll
-    for (int g = 0; g < GP; ++g) acc[g][0] = acc[g][1] = 0.f;
     const int k_first = c * DEC_CHUNK;
-    int k_last = pos - k_first;                         // last valid key of the chunk, chunk-relative
-    if (k_last > DEC_CHUNK - 1) k_last = DEC_CHUNK - 1;
-    int k_begin = lo - k_first;
-    if (k_begin < 0) k_begin = 0;
-    for (int kk = k_begin + ks; kk <= k_last; kk += n_ks) {
-        const int jj = k_first + kk;
-        const int page = bt[jj / RF_PAGE];
-        const __nv_bfloat162 v2 = *reinterpret_cast<const __nv_bfloat162*>(
-            v_pages + ((size_t)page * nkv + kvh) * RF_PAGE * hd + (size_t)(jj % RF_PAGE) * hd + 2 * dp);
-        const float2 vf = __bfloat1622float2(v2);
+    int k_begin = lo - k_first; if (k_begin < 0) k_begin = 0;                  // chunk-relative valid range
+    int k_last = pos - k_first; if (k_last > DEC_CHUNK - 1) k_last = DEC_CHUNK - 1;
+
+    // ---- bring the chunk's pages in: all copies in flight at once
+    const uint32_t bar_a = dec_smem_u32(bar);
+    if (tid == 0) {
+        gave_up = 0;
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_a));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        uint32_t bytes = 0;
+        for (int pg = 0; pg < DEC_CHUNK / RF_PAGE; ++pg)
+            if (pg * RF_PAGE <= k_last && pg * RF_PAGE + RF_PAGE - 1 >= k_begin) bytes += 2 * SLAB;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_a), "r"(bytes) : "memory");
+        for (int pg = 0; pg < DEC_CHUNK / RF_PAGE; ++pg) {
+            if (!(pg * RF_PAGE <= k_last && pg * RF_PAGE + RF_PAGE - 1 >= k_begin)) continue;
+            const int page = bt[k_first / RF_PAGE + pg];
+            const size_t off = ((size_t)page * nkv + kvh) * RF_PAGE * HD;
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         ::"r"(dec_smem_u32(k_s + pg * RF_PAGE * HD)), "l"(k_pages + off), "r"(SLAB), "r"(bar_a) : "memory");
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         ::"r"(dec_smem_u32(v_s + pg * RF_PAGE * HD)), "l"(v_pages + off), "r"(SLAB), "r"(bar_a) : "memory");
+        }
+    }
+    // the group's queries as the A operand of mma.m16n8k16 (row = query head of the group, rows >= G are
+    // zero; with at most 8 heads per group the upper 8 rows are always zero): two registers per 16 dims
+    const int gid = lane >> 2, tig = lane & 3;
+    uint32_t qa[HD / 16][2];
 #pragma unroll
-        for (int g = 0; g < GP; ++g) {
-            if (g < G) {
-                const float p = p_s[g * DEC_CHUNK + kk];
-                acc[g][0] = fmaf(p, vf.x, acc[g][0]);
-                acc[g][1] = fmaf(p, vf.y, acc[g][1]);
+    for (int ks = 0; ks < HD / 16; ++ks) {
+        qa[ks][0] = qa[ks][1] = 0u;
+        if (gid < G) {
+            const __nv_bfloat16* qrow = q + (size_t)b * q_stride + (size_t)(kvh * G + gid) * HD + ks * 16 + tig * 2;
+            qa[ks][0] = *reinterpret_cast<const uint32_t*>(qrow);
+            qa[ks][1] = *reinterpret_cast<const uint32_t*>(qrow + 8);
+        }
+    }
+    __syncthreads();                                   // the barrier is initialised for everyone
+    {   // bounded wait for the copies
+        uint32_t ok = 0;
+        unsigned long long t0 = 0;
+        for (long long it = 0; !ok; ++it) {
+            asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n\t"
+                         "selp.u32 %0, 1, 0, p;\n\t}" : "=r"(ok) : "r"(bar_a) : "memory");
+            if (ok) break;
+            if ((it & 63) == 63) {
+                unsigned long long now;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+                if (t0 == 0) t0 = now;
+                if (now - t0 > DEC_WAIT_LIMIT_NS || gave_up) { gave_up = 1; break; }
             }
         }
     }
+    __syncthreads();
+    if (gave_up) {                                      // record it and leave; the output stays unwritten
+        if (tid == 0 && status) atomicExch(status, 2);
+        return;
+    }
+
+    // value rows outside the sequence (the rest of a half-filled page) get weight zero below, but
+    // 0 * (whatever bits lie there) must be 0: clear those rows
+    for (int i = tid; i < DEC_CHUNK * (HD / 8); i += DEC_THREADS) {
+        const int row = i / (HD / 8);
+        if (row < k_begin || row > k_last) reinterpret_cast<uint4*>(v_s)[i] = make_uint4(0u, 0u, 0u, 0u);
+    }
+
+    // ---- scores on the tensor cores: a warp owns 32 keys = 4 tiles of 8; S[head][key] = q . k
+    const int kbase = warp * 32;
+    const bool warp_active = kbase <= k_last && kbase + 31 >= k_begin;
+    float sc[4][4];
 #pragma unroll
-    for (int g = 0; g < GP; ++g) {
-        if (g < G) {
-            o_red[(ks * GP + g) * hd + 2 * dp] = acc[g][0];
-            o_red[(ks * GP + g) * hd + 2 * dp + 1] = acc[g][1];
+    for (int nt = 0; nt < 4; ++nt) sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+    if (warp_active) {
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt) {
+                const __nv_bfloat16* kr = k_s + (kbase + nt * 8 + gid) * HD + ks * 16 + tig * 2;
+                const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kr);
+                const uint32_t b1 = *reinterpret_cast<const uint32_t*>(kr + 8);
+                asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                             : "+f"(sc[nt][0]), "+f"(sc[nt][1]), "+f"(sc[nt][2]), "+f"(sc[nt][3])
+                             : "r"(qa[ks][0]), "r"(0u), "r"(qa[ks][1]), "r"(0u), "r"(b0), "r"(b1));
+            }
         }
+    }
+    // this thread: head gid, keys kbase + nt*8 + tig*2 + {0,1}; 32-bit from here on
+    float mloc = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int kk = kbase + nt * 8 + tig * 2 + e;
+            const bool ok = warp_active && kk >= k_begin && kk <= k_last;     // garbage beyond the sequence is masked here
+            sc[nt][e] = ok ? sc[nt][e] * scale : -INFINITY;
+            mloc = fmaxf(mloc, sc[nt][e]);
+        }
+    mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, 1));
+    mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, 2));
+    if (tig == 0) wred[warp * DEC_GP + gid] = mloc;
+    __syncthreads();
+    const float mrow = fmaxf(fmaxf(wred[gid], wred[DEC_GP + gid]), fmaxf(wred[2 * DEC_GP + gid], wred[3 * DEC_GP + gid]));
+    __syncthreads();
+    float lloc = 0.f;
+    uint32_t pa[2][2];                                  // P as the A operand of the second product, two 16-key steps
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+        const float p0 = sc[nt][0] == -INFINITY ? 0.f : expf(sc[nt][0] - mrow);
+        const float p1 = sc[nt][1] == -INFINITY ? 0.f : expf(sc[nt][1] - mrow);
+        lloc += p0 + p1;
+        const __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+        pa[nt >> 1][nt & 1] = *reinterpret_cast<const uint32_t*>(&pk);
+    }
+    lloc += __shfl_xor_sync(0xffffffffu, lloc, 1);
+    lloc += __shfl_xor_sync(0xffffffffu, lloc, 2);
+    if (tig == 0) wred[warp * DEC_GP + gid] = lloc;
+    __syncthreads();
+    const float lrow = (wred[gid] + wred[DEC_GP + gid]) + (wred[2 * DEC_GP + gid] + wred[3 * DEC_GP + gid]);
+    // every thread needs m and l of the heads it writes later: park them in shared memory
+    if (warp == 0 && tig == 0) { p_s[gid] = mrow; p_s[DEC_GP + gid] = lrow; }
+
+    // ---- values on the tensor cores: O[head][dim] += P[head][key] * V[key][dim]
+    float oc[HD / 8][4];
+#pragma unroll
+    for (int nt = 0; nt < HD / 8; ++nt) oc[nt][0] = oc[nt][1] = oc[nt][2] = oc[nt][3] = 0.f;
+    if (warp_active) {
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks) {
+            // a tile of 16 keys wholly outside the sequence holds garbage: skip it (its weights are zero, but 0 * NaN is not)
+            const int t0 = kbase + ks * 16;
+            if (t0 > k_last || t0 + 15 < k_begin) continue;
+#pragma unroll
+            for (int nt = 0; nt < HD / 8; nt += 2) {
+                const int mi = lane >> 3, r = lane & 7;
+                const __nv_bfloat16* vr = v_s + (t0 + (mi & 1) * 8 + r) * HD + (nt + (mi >> 1)) * 8;
+                uint32_t v0, v1, v2, v3;
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3) : "r"(dec_smem_u32(vr)));
+                asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                             : "+f"(oc[nt][0]), "+f"(oc[nt][1]), "+f"(oc[nt][2]), "+f"(oc[nt][3])
+                             : "r"(pa[ks][0]), "r"(0u), "r"(pa[ks][1]), "r"(0u), "r"(v0), "r"(v1));
+                asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                             : "+f"(oc[nt + 1][0]), "+f"(oc[nt + 1][1]), "+f"(oc[nt + 1][2]), "+f"(oc[nt + 1][3])
+                             : "r"(pa[ks][0]), "r"(0u), "r"(pa[ks][1]), "r"(0u), "r"(v2), "r"(v3));
+            }
+        }
+    }
+    __syncthreads();                                   // everyone is done with k_s / v_s
+#pragma unroll
+    for (int nt = 0; nt < HD / 8; ++nt) {
+        o_red[(warp * DEC_GP + gid) * HD + nt * 8 + tig * 2] = oc[nt][0];
+        o_red[(warp * DEC_GP + gid) * HD + nt * 8 + tig * 2 + 1] = oc[nt][1];
     }
     __syncthreads();
 
     // ---- this chunk's result: final if it is the only chunk, else a partial in scratch memory
-    for (int i = tid; i < G * hd; i += DEC_THREADS) {
-        const int g = i / hd, d = i - g * hd;
-        float o = 0.f;
-        for (int k2 = 0; k2 < n_ks; ++k2) o += o_red[(k2 * GP + g) * hd + d];     // fixed order
+    for (int i = tid; i < G * HD; i += DEC_THREADS) {
+        const int g = i / HD, d = i - g * HD;
+        const float o = (o_red[g * HD + d] + o_red[(DEC_GP + g) * HD + d])
+                      + (o_red[(2 * DEC_GP + g) * HD + d] + o_red[(3 * DEC_GP + g) * HD + d]);
         const int head = kvh * G + g;
         if (n_act == 1) {
-            float lg = 0.f;                              // l[g] lives in registers indexed at compile time
-#pragma unroll
-            for (int gg = 0; gg < GP; ++gg) if (gg == g) lg = l[gg];
-            out[(size_t)b * out_stride + (size_t)head * hd + d] = __float2bfloat16_rn(lg > 0.f ? o / lg : 0.f);
+            const float lg = p_s[DEC_GP + g];
+            out[(size_t)b * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(lg > 0.f ? o / lg : 0.f);
         } else {
-            part_o[(((size_t)b * nh + head) * max_chunks + c) * hd + d] = o;
+            part_o[(((size_t)b * nh + head) * max_chunks + c) * HD + d] = o;
         }
     }
     if (n_act == 1) return;
     if (tid < G) {
-        float mg = 0.f, lg = 0.f;
-#pragma unroll
-        for (int gg = 0; gg < GP; ++gg) if (gg == tid) { mg = m[gg]; lg = l[gg]; }
         float* ml = part_ml + (((size_t)b * nh + kvh * G + tid) * max_chunks + c) * 2;
-        ml[0] = mg; ml[1] = lg;
+        ml[0] = p_s[tid]; ml[1] = p_s[DEC_GP + tid];
     }
     __threadfence();
     __syncthreads();
@@ -176,56 +237,72 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    for (int i = tid; i < G * hd; i += DEC_THREADS) {
-        const int g = i / hd, d = i - g * hd;
-        const int head = kvh * G + g;
-        const size_t base = ((size_t)b * nh + head) * max_chunks;
+    // weights of the chunks, once per head: w[g][cc] = exp(m_cc - M) / L   (p_s is free by now)
+    float* w_s = p_s;                                    // [GP][n_act], n_act <= DEC_CHUNK
+    for (int i = tid; i < G * n_act; i += DEC_THREADS) {
+        const int g = i / n_act, cc = i - g * n_act;
+        w_s[g * DEC_CHUNK + cc] = __ldcg(part_ml + (((size_t)b * nh + kvh * G + g) * max_chunks + c_lo + cc) * 2);
+    }
+    __syncthreads();
+    if (tid < G) {
+        const size_t base = ((size_t)b * nh + kvh * G + tid) * max_chunks;
         float M = -INFINITY;
-        for (int cc = c_lo; cc <= c_hi; ++cc) M = fmaxf(M, __ldcg(part_ml + (base + cc) * 2));
-        float L = 0.f, O = 0.f;
-        for (int cc = c_lo; cc <= c_hi; ++cc) {          // chunks in index order
-            const float w = expf(__ldcg(part_ml + (base + cc) * 2) - M);
-            L += w * __ldcg(part_ml + (base + cc) * 2 + 1);
-            O += w * __ldcg(part_o + (base + cc) * hd + d);
+        for (int cc = 0; cc < n_act; ++cc) M = fmaxf(M, w_s[tid * DEC_CHUNK + cc]);
+        float L = 0.f;
+        for (int cc = 0; cc < n_act; ++cc) {             // chunks in index order
+            const float w = expf(w_s[tid * DEC_CHUNK + cc] - M);
+            L += w * __ldcg(part_ml + (base + c_lo + cc) * 2 + 1);
+            w_s[tid * DEC_CHUNK + cc] = w;
         }
-        out[(size_t)b * out_stride + (size_t)head * hd + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+        const float inv = L > 0.f ? 1.f / L : 0.f;
+        for (int cc = 0; cc < n_act; ++cc) w_s[tid * DEC_CHUNK + cc] *= inv;
+    }
+    __syncthreads();
+    for (int i = tid; i < G * HD; i += DEC_THREADS) {
+        const int g = i / HD, d = i - g * HD;
+        const int head = kvh * G + g;
+        const float* po = part_o + (((size_t)b * nh + head) * max_chunks + c_lo) * HD + d;
+        float O = 0.f;
+#pragma unroll 4
+        for (int cc = 0; cc < n_act; ++cc) O = fmaf(w_s[g * DEC_CHUNK + cc], __ldcg(po + (size_t)cc * HD), O);
+        out[(size_t)b * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(O);
     }
     if (tid == 0) counters[b * nkv + kvh] = 0;          // ready for the next launch
 }
 
-static size_t smem_bytes(int gp, int hd) {
-    const int n_ks = DEC_THREADS / (hd / 2);
-    return (size_t)(gp * hd + gp * DEC_CHUNK + 8 * gp + n_ks * gp * hd) * sizeof(float);
-}
-
-template <int GP>
+template <int EPL>
 static int launch(const void* q, int q_stride, void* out, int out_stride, const void* k_pages, const void* v_pages,
                   const int* tok_seq, const int* tok_pos, const int* seq_slot, const int* block_table,
-                  int max_pages, int nh, int nkv, int hd, float scale, int window, int B, int max_chunks,
-                  float* part_o, float* part_ml, int* counters, cudaStream_t st) {
-    const size_t smem = smem_bytes(GP, hd);
-    if (smem > 200 * 1024) return RF_ERR_UNSUPPORTED;
-    if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<GP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                  int max_pages, int nh, int nkv, float scale, int window, int B, int max_chunks,
+                  float* part_o, float* part_ml, int* counters, int* status, cudaStream_t st) {
+    constexpr int HD = EPL * 32;
+    const size_t smem = (size_t)2 * DEC_CHUNK * HD * 2 + (DEC_GP * DEC_CHUNK + DEC_WARPS * DEC_GP) * sizeof(float) + 16;
+    static bool configured = false;
+    if (!configured && smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<EPL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)smem);
         if (e != cudaSuccess) return (int)e;
+        configured = true;
     }
     dim3 grid(max_chunks, nkv, B);
-    attention_decode_kernel<GP><<<grid, DEC_THREADS, smem, st>>>(
+    attention_decode_kernel<EPL><<<grid, DEC_THREADS, smem, st>>>(
         reinterpret_cast<const __nv_bfloat16*>(q), q_stride, reinterpret_cast<__nv_bfloat16*>(out), out_stride,
         reinterpret_cast<const __nv_bfloat16*>(k_pages), reinterpret_cast<const __nv_bfloat16*>(v_pages), tok_seq,
-        tok_pos, seq_slot, block_table, max_pages, nh, nkv, hd, scale, window, max_chunks, part_o, part_ml, counters);
+        tok_pos, seq_slot, block_table, max_pages, nh, nkv, scale, window, max_chunks, part_o, part_ml, counters, status);
     RF_LAUNCH_CHECK();
     return 0;
 }
 
 extern "C" {
 
-// head sizes this kernel takes: hd/2 must divide the 256 threads, rows must allow 16-byte loads
+// What this kernel takes: head sizes whose rows split evenly over 32 lanes, up to 8 query heads per kv head,
+// and at most DEC_CHUNK chunks (16,384 keys) per sequence: the merge keeps one weight per chunk in shared memory.
 int rf_attention_decode_supported(int nh, int nkv, int hd) {
-    if (nkv <= 0 || nh % nkv || nh / nkv > 16) return 0;
-    return hd == 16 || hd == 32 || hd == 64 || hd == 128 || hd == 256;
+    if (nkv <= 0 || nh % nkv || nh / nkv > DEC_GP) return 0;
+    return hd == 64 || hd == 128 || hd == 256;
 }
+
+int rf_attention_decode_chunk() { return DEC_CHUNK; }
 
 // Scratch sizes in elements for B sequences: part_o, part_ml (floats), counters (ints, zero before the first launch).
 void rf_attention_decode_scratch(int B, int nh, int nkv, int hd, int max_chunks, long long* n_part_o,
@@ -238,18 +315,18 @@ void rf_attention_decode_scratch(int B, int nh, int nkv, int hd, int max_chunks,
 int rf_attention_decode(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                         const void* v_pages, const int* tok_seq, const int* tok_pos, const int* seq_slot,
                         const int* block_table, int max_pages, int nh, int nkv, int hd, float scale, int window,
-                        int B, int max_chunks, float* part_o, float* part_ml, int* counters, cudaStream_t st) {
+                        int B, int max_chunks, float* part_o, float* part_ml, int* counters, int* status,
+                        cudaStream_t st) {
     if (B <= 0) return 0;
-    if (!rf_attention_decode_supported(nh, nkv, hd) || max_chunks <= 0 || B > 65535) return RF_ERR_UNSUPPORTED;
-    const int G = nh / nkv;
-#define GO(GP) return launch<GP>(q, q_stride, out, out_stride, k_pages, v_pages, tok_seq, tok_pos, seq_slot, \
-                                 block_table, max_pages, nh, nkv, hd, scale, window, B, max_chunks, part_o, part_ml, \
-                                 counters, st)
-    if (G <= 1) GO(1);
-    if (G <= 2) GO(2);
-    if (G <= 4) GO(4);
-    if (G <= 8) GO(8);
-    GO(16);
+    if (!rf_attention_decode_supported(nh, nkv, hd) || max_chunks <= 0 || max_chunks > DEC_CHUNK || B > 65535)
+        return RF_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(q) & 15) || (q_stride * 2) % 16) return RF_ERR_BAD_ARG;
+#define GO(EPL) return launch<EPL>(q, q_stride, out, out_stride, k_pages, v_pages, tok_seq, tok_pos, seq_slot, \
+                                   block_table, max_pages, nh, nkv, scale, window, B, max_chunks, part_o, part_ml, \
+                                   counters, status, st)
+    if (hd == 64) GO(2);
+    if (hd == 128) GO(4);
+    GO(8);
 #undef GO
 }
 

@@ -59,6 +59,59 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const void* __restrict
     }
 }
 
+// The same for rows whose length is a multiple of 4: the row lives in registers (at most NV float4 per
+// thread), every load is 16 bytes wide and independent of the others, so a short row costs a few
+// memory round trips instead of a chain of them.  Sums are formed in the same order as above
+// (h first, then the partial sums in index order), element by element.
+template <typename T, int NV>
+__global__ void __launch_bounds__(1024)
+add_rmsnorm_vec_kernel(float* __restrict__ h, const void* __restrict__ pending, int pending_kind, int n_pending,
+                       size_t pending_stride, const void* __restrict__ w, int w_is_f32, float eps,
+                       T* __restrict__ y, const int* __restrict__ rows, int H) {
+    __shared__ float red[34];
+    const int r = blockIdx.x;
+    const int t = rows ? rows[r] : r;
+    const int nvec = H >> 2;
+    float4* hrow = reinterpret_cast<float4*>(h + (size_t)t * H);
+    float4 v[NV];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < nvec) {
+            float4 a = hrow[c];
+            if (pending_kind == 1) {
+                const float4* p = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(pending) + (size_t)t * H) + c;
+                for (int s2 = 0; s2 < n_pending; ++s2) {
+                    const float4 b = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + (size_t)s2 * pending_stride);
+                    a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+                }
+            } else if (pending_kind == 2) {
+                const T* p = reinterpret_cast<const T*>(pending) + (size_t)t * H + 4 * c;
+                a.x += Cvt<T>::to_f32(p[0]); a.y += Cvt<T>::to_f32(p[1]);
+                a.z += Cvt<T>::to_f32(p[2]); a.w += Cvt<T>::to_f32(p[3]);
+            }
+            v[i] = a;
+            ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+        }
+    }
+    const float total = block_sum(ss, red);
+    const float inv = rsqrtf(total / (float)H + eps);
+    T* yrow = y + (size_t)r * H;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < nvec) {
+            if (!rows && pending_kind != 0) hrow[c] = v[i];
+            const float o0 = v[i].x * inv * load_vec(w, w_is_f32, 4 * c), o1 = v[i].y * inv * load_vec(w, w_is_f32, 4 * c + 1);
+            const float o2 = v[i].z * inv * load_vec(w, w_is_f32, 4 * c + 2), o3 = v[i].w * inv * load_vec(w, w_is_f32, 4 * c + 3);
+            T* o = yrow + 4 * c;
+            o[0] = Cvt<T>::from_f32(o0); o[1] = Cvt<T>::from_f32(o1);
+            o[2] = Cvt<T>::from_f32(o2); o[3] = Cvt<T>::from_f32(o3);
+        }
+    }
+}
+
 // ---------------------------------------------------------------- rotation + cache write
 // Rows of q | k | v, [T, (nh + 2*nkv) * hd], come either in the compute dtype (src, one tensor)
 // or as n_partials 32-bit partial sums of a K-split product plus a bias (the sum is formed here,
@@ -74,9 +127,16 @@ __global__ void rope_kv_write_kernel(const void* __restrict__ src, int row_strid
                                      const int* __restrict__ seq_slot,
                                      const int* __restrict__ block_table, int max_pages,
                                      T* __restrict__ k_pages, T* __restrict__ v_pages, int write_kv) {
+    // grid: (token, block of pairs).  Pair index space: nh + nkv rotated heads, then nkv value heads,
+    // hd/2 pairs each (a value "pair" is two neighbouring elements, copied).
     const int t = blockIdx.x;
-    const int pos = tok_pos[t];
     const int half = hd >> 1;
+    const int idx = blockIdx.y * blockDim.x + threadIdx.x;
+    const int n_pairs = (nh + 2 * nkv) * half;
+    if (idx >= n_pairs) return;
+    const int head = idx / half, i = idx - head * half;
+    if (head >= nh && !write_kv) return;
+    const int pos = tok_pos[t];
     auto value = [&](int col) -> float {
         if (PARTIALS) {
             const float* p = reinterpret_cast<const float*>(src) + (size_t)t * row_stride + col;
@@ -87,35 +147,26 @@ __global__ void rope_kv_write_kernel(const void* __restrict__ src, int row_strid
         return Cvt<T>::to_f32(reinterpret_cast<const T*>(src)[(size_t)t * row_stride + col]);
     };
     size_t page_base = 0;
-    if (write_kv) {
+    if (head >= nh) {
         const int slot = seq_slot[tok_seq[t]];
         const int page = block_table[(size_t)slot * max_pages + pos / RF_PAGE];
         page_base = (size_t)page * nkv * RF_PAGE * hd + (size_t)(pos % RF_PAGE) * hd;
     }
-    const int n_rot = (nh + nkv) * half;
-    for (int idx = threadIdx.x; idx < n_rot; idx += blockDim.x) {
-        const int head = idx / half, i = idx - head * half;
-        if (head >= nh && !write_kv) break;
+    if (head < nh + nkv) {
         const float angle = (float)pos * inv_freq[i];
         float s, c;
         sincosf(angle, &s, &c);
         const float x0 = value(head * hd + i), x1 = value(head * hd + i + half);
         const float r0 = x0 * c - x1 * s, r1 = x0 * s + x1 * c;
-        if (head < nh) {
-            T* x = q_out + (size_t)t * q_out_stride + (size_t)head * hd;
-            x[i] = Cvt<T>::from_f32(r0);
-            x[i + half] = Cvt<T>::from_f32(r1);
-        } else {
-            T* dst = k_pages + page_base + (size_t)(head - nh) * RF_PAGE * hd;
-            dst[i] = Cvt<T>::from_f32(r0);
-            dst[i + half] = Cvt<T>::from_f32(r1);
-        }
-    }
-    if (write_kv) {
-        for (int idx = threadIdx.x; idx < nkv * hd; idx += blockDim.x) {
-            const int head = idx / hd, i = idx - head * hd;
-            v_pages[page_base + (size_t)head * RF_PAGE * hd + i] = Cvt<T>::from_f32(value((nh + nkv) * hd + idx));
-        }
+        T* dst = head < nh ? q_out + (size_t)t * q_out_stride + (size_t)head * hd
+                           : k_pages + page_base + (size_t)(head - nh) * RF_PAGE * hd;
+        dst[i] = Cvt<T>::from_f32(r0);
+        dst[i + half] = Cvt<T>::from_f32(r1);
+    } else {
+        const int vh = head - nh - nkv;
+        T* dst = v_pages + page_base + (size_t)vh * RF_PAGE * hd;
+        dst[2 * i] = Cvt<T>::from_f32(value(head * hd + 2 * i));
+        dst[2 * i + 1] = Cvt<T>::from_f32(value(head * hd + 2 * i + 1));
     }
 }
 
@@ -147,6 +198,19 @@ static int launch_add_rmsnorm(float* h, const void* pending, int kind, int n_pen
                               const void* w, int w_is_f32, float eps, void* y, const int* rows,
                               int n_rows, int H, cudaStream_t st) {
     if (n_rows <= 0) return 0;
+    if (H % 4 == 0 && H <= 4 * 4 * 1024 && (pstride % 4) == 0 &&
+        !(reinterpret_cast<uintptr_t>(h) & 15) && !(kind == 1 && (reinterpret_cast<uintptr_t>(pending) & 15))) {
+        const int nvec = H / 4;
+        int threads = ((nvec + 31) / 32) * 32;            // one 16-byte vector per thread where the row allows
+        if (threads > 1024) threads = 1024;
+        const int per = (nvec + threads - 1) / threads;
+        T* yy = reinterpret_cast<T*>(y);
+        if (per <= 1) add_rmsnorm_vec_kernel<T, 1><<<n_rows, threads, 0, st>>>(h, pending, kind, n_pending, pstride, w, w_is_f32, eps, yy, rows, H);
+        else if (per <= 2) add_rmsnorm_vec_kernel<T, 2><<<n_rows, threads, 0, st>>>(h, pending, kind, n_pending, pstride, w, w_is_f32, eps, yy, rows, H);
+        else add_rmsnorm_vec_kernel<T, 4><<<n_rows, threads, 0, st>>>(h, pending, kind, n_pending, pstride, w, w_is_f32, eps, yy, rows, H);
+        RF_LAUNCH_CHECK();
+        return 0;
+    }
     const size_t smem = (size_t)(H + 33) * sizeof(float);
     if (smem > 200 * 1024) return RF_ERR_UNSUPPORTED;
     if (smem > 48 * 1024) {
@@ -169,12 +233,15 @@ static int launch_rope_kv_write(const void* src, int row_stride, int n_partials,
                                 void* v_pages, int write_kv, int T_, cudaStream_t st) {
     if (T_ <= 0) return 0;
     if (hd % 2) return RF_ERR_BAD_ARG;
+    const int n_pairs = (nh + 2 * nkv) * (hd / 2);
+    const dim3 grid(T_, (n_pairs + 255) / 256);
+    if (T_ > 2147483647 || grid.y > 65535) return RF_ERR_UNSUPPORTED;
     if (n_partials > 0)
-        rope_kv_write_kernel<T, true><<<T_, 256, 0, st>>>(src, row_stride, n_partials, partial_stride, bias,
+        rope_kv_write_kernel<T, true><<<grid, 256, 0, st>>>(src, row_stride, n_partials, partial_stride, bias,
             bias_is_f32, reinterpret_cast<T*>(q_out), q_out_stride, nh, nkv, hd, inv_freq, tok_seq, tok_pos, seq_slot,
             block_table, max_pages, reinterpret_cast<T*>(k_pages), reinterpret_cast<T*>(v_pages), write_kv);
     else
-        rope_kv_write_kernel<T, false><<<T_, 256, 0, st>>>(src, row_stride, 0, 0, nullptr, 0,
+        rope_kv_write_kernel<T, false><<<grid, 256, 0, st>>>(src, row_stride, 0, 0, nullptr, 0,
             reinterpret_cast<T*>(q_out), q_out_stride, nh, nkv, hd, inv_freq, tok_seq, tok_pos, seq_slot,
             block_table, max_pages, reinterpret_cast<T*>(k_pages), reinterpret_cast<T*>(v_pages), write_kv);
     RF_LAUNCH_CHECK();

@@ -145,7 +145,7 @@ __host__ __device__ constexpr uint32_t make_idesc(int n) {
 // ---------------------------------------------------------------- the kernel
 // SWAP = false: map A = X (rows are tokens), map B = W;  SWAP = true: map A = W, map B = X.
 template <int BN, bool SWAP, int STAGES>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(TC_THREADS, SWAP ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p) {
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2;
     constexpr uint32_t B_BYTES = BN * TC_BK * 2;
@@ -385,9 +385,11 @@ int rf_gemm_tc_skinny(const void* X, int ldx, const void* W, const void* bias, i
     const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
     if ((e = make_map(&ma, W, N, K, K, TC_BM)) || (e = make_map(&mb, X, M, K, ldx, bn))) return e;
     dim3 grid(1, (N + TC_BM - 1) / TC_BM, splits);
-    if (bn == 16) return launch_cfg<16, true, 8>(ma, mb, p, grid, st);
-    if (bn == 32) return launch_cfg<32, true, 8>(ma, mb, p, grid, st);
-    return launch_cfg<64, true, 8>(ma, mb, p, grid, st);
+    // stage counts chosen so that two CTAs share an SM: their pipelines overlap each other's
+    // start-up and epilogue, and 2 x stages x 16 KB of weight bytes are in flight per SM
+    if (bn == 16) return launch_cfg<16, true, 6>(ma, mb, p, grid, st);
+    if (bn == 32) return launch_cfg<32, true, 5>(ma, mb, p, grid, st);
+    return launch_cfg<64, true, 4>(ma, mb, p, grid, st);
 }
 
 }

@@ -119,9 +119,10 @@ class StepContext:
     def attention(self, q, mixer, view):
         """Attention of the step's tokens over the cache; q is the first heads*head_dim columns of ``q``."""
         nh, nkv, hd = mixer.n_heads, mixer.n_kv_heads, mixer.head_dim
+        longest = self.model_cache_limit if self.replayed else self.max_end
         if (self.is_decode and self.compute_dtype == torch.bfloat16 and self.options.tuned_attention
-                and kernels.attention_decode_supported(nh, nkv, hd)):
-            longest = self.model_cache_limit if self.replayed else self.max_end
+                and kernels.attention_decode_supported(nh, nkv, hd)
+                and longest <= kernels.DECODE_CHUNK * kernels.DECODE_CHUNK):
             need = max(1, (longest + kernels.DECODE_CHUNK - 1) // kernels.DECODE_CHUNK)
             max_chunks = 1
             while max_chunks < need:                   # powers of two: few distinct scratch sizes

@@ -235,7 +235,7 @@ def attention_decode_supported(n_heads: int, n_kv_heads: int, head_dim: int) -> 
     return bool(f(n_heads, n_kv_heads, head_dim))
 
 
-DECODE_CHUNK = 256
+DECODE_CHUNK = 128
 
 
 def attention_decode_scratch(B: int, n_heads: int, n_kv_heads: int, head_dim: int, max_chunks: int):
@@ -247,9 +247,9 @@ def attention_decode(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: i
                      tok_seq, tok_pos, seq_slot, block_table, scale: float, window: int | None, max_chunks: int,
                      part_o: torch.Tensor, part_ml: torch.Tensor, counters: torch.Tensor,
                      out: torch.Tensor | None = None) -> torch.Tensor:
-    """One new token per sequence over the bfloat16 paged cache, keys in chunks of 256.
+    """One new token per sequence over the bfloat16 paged cache, keys in chunks of 128.
 
-    ``max_chunks`` must cover the longest sequence (ceil(length / 256)); ``part_o``, ``part_ml`` (float32)
+    ``max_chunks`` must cover the longest sequence (ceil(length / 128)); ``part_o``, ``part_ml`` (float32)
     and ``counters`` (int32, zero before the first call; the kernel leaves them zero) are scratch of at
     least ``attention_decode_scratch`` elements.
     """
@@ -265,14 +265,16 @@ def attention_decode(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: i
     need(part_o.dtype == torch.float32 and part_o.numel() >= n_o and part_ml.dtype == torch.float32
          and part_ml.numel() >= n_ml and counters.dtype == torch.int32 and counters.numel() >= n_c,
          "attention_decode: scratch tensors are too small")
-    need(q.data_ptr() % 4 == 0, "attention_decode: q must be 4-byte aligned")
+    need(q.data_ptr() % 16 == 0 and (q.stride(0) * 2) % 16 == 0, "attention_decode: q rows must be 16-byte aligned")
     if out is None:
         out = torch.empty((B, n_heads * head_dim), dtype=torch.bfloat16, device=q.device)
     f = _f("attention_decode", "rf_attention_decode", c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
            c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p,
-           c_void_p, c_void_p)
+           c_void_p, c_void_p, c_void_p)
+    from .tensor_core import status_word
     check(f(ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(k_pages), ptr(v_pages), ptr(tok_seq), ptr(tok_pos),
             ptr(seq_slot), ptr(block_table), block_table.shape[1], n_heads, n_kv_heads, head_dim, float(scale),
-            int(window or 0), B, max_chunks, ptr(part_o), ptr(part_ml), ptr(counters), stream()),
+            int(window or 0), B, max_chunks, ptr(part_o), ptr(part_ml), ptr(counters), ptr(status_word(q.device)),
+            stream()),
           f"attention_decode (heads={n_heads}, kv_heads={n_kv_heads}, head_dim={head_dim})")
     return out

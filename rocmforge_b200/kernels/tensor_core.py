@@ -74,14 +74,14 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = Non
 
 
 def split_k_for(N: int, K: int, sm_count: int = 148) -> int:
-    """K splits of a skinny product, from N and K alone (never from the batch), so that about one
-    wave of CTAs streams the weight and every split keeps at least 8 blocks of 64."""
+    """K splits of a skinny product, from N and K alone (never from the batch), so that about two
+    CTAs per SM stream the weight and every split keeps at least 4 blocks of 64."""
     tiles = (N + 127) // 128
     kb = (K + 63) // 64
-    if tiles >= sm_count or kb < 16:
+    if tiles >= 2 * sm_count or kb < 8:
         return 1
-    want = max(1, sm_count // tiles)
-    splits = max(1, min(want, kb // 8))
+    want = max(1, (2 * sm_count) // tiles)
+    splits = max(1, min(want, kb // 4))
     per = (kb + splits - 1) // splits
     return (kb + per - 1) // per                   # no empty split
 
