@@ -237,35 +237,45 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    // weights of the chunks, once per head: w[g][cc] = exp(m_cc - M) / L   (p_s is free by now)
-    float* w_s = p_s;                                    // [GP][n_act], n_act <= DEC_CHUNK
+    // weights of the chunks, once per head: w[g][cc] = exp(m_cc - M) / L.  All loads of this phase are
+    // independent of one another (p_s and o_red are free by now).
+    float* w_s = p_s;                                    // [GP][DEC_CHUNK]: max, then weight, of chunk cc
+    float* l_s = o_red;                                  // [GP][DEC_CHUNK]: sum of chunk cc
     for (int i = tid; i < G * n_act; i += DEC_THREADS) {
         const int g = i / n_act, cc = i - g * n_act;
-        w_s[g * DEC_CHUNK + cc] = __ldcg(part_ml + (((size_t)b * nh + kvh * G + g) * max_chunks + c_lo + cc) * 2);
+        const float2 ml = __ldcg(reinterpret_cast<const float2*>(
+            part_ml + (((size_t)b * nh + kvh * G + g) * max_chunks + c_lo + cc) * 2));
+        w_s[g * DEC_CHUNK + cc] = ml.x;
+        l_s[g * DEC_CHUNK + cc] = ml.y;
     }
     __syncthreads();
     if (tid < G) {
-        const size_t base = ((size_t)b * nh + kvh * G + tid) * max_chunks;
         float M = -INFINITY;
         for (int cc = 0; cc < n_act; ++cc) M = fmaxf(M, w_s[tid * DEC_CHUNK + cc]);
         float L = 0.f;
         for (int cc = 0; cc < n_act; ++cc) {             // chunks in index order
             const float w = expf(w_s[tid * DEC_CHUNK + cc] - M);
-            L += w * __ldcg(part_ml + (base + c_lo + cc) * 2 + 1);
+            L += w * l_s[tid * DEC_CHUNK + cc];
             w_s[tid * DEC_CHUNK + cc] = w;
         }
         const float inv = L > 0.f ? 1.f / L : 0.f;
         for (int cc = 0; cc < n_act; ++cc) w_s[tid * DEC_CHUNK + cc] *= inv;
     }
     __syncthreads();
-    for (int i = tid; i < G * HD; i += DEC_THREADS) {
-        const int g = i / HD, d = i - g * HD;
+    for (int i = tid; i < G * (HD / 4); i += DEC_THREADS) {
+        const int g = i / (HD / 4), d4 = i - g * (HD / 4);
         const int head = kvh * G + g;
-        const float* po = part_o + (((size_t)b * nh + head) * max_chunks + c_lo) * HD + d;
-        float O = 0.f;
-#pragma unroll 4
-        for (int cc = 0; cc < n_act; ++cc) O = fmaf(w_s[g * DEC_CHUNK + cc], __ldcg(po + (size_t)cc * HD), O);
-        out[(size_t)b * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(O);
+        const float4* po = reinterpret_cast<const float4*>(part_o + (((size_t)b * nh + head) * max_chunks + c_lo) * HD) + d4;
+        float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+        for (int cc = 0; cc < n_act; ++cc) {
+            const float w = w_s[g * DEC_CHUNK + cc];
+            const float4 v = __ldcg(po + (size_t)cc * (HD / 4));
+            O.x = fmaf(w, v.x, O.x); O.y = fmaf(w, v.y, O.y); O.z = fmaf(w, v.z, O.z); O.w = fmaf(w, v.w, O.w);
+        }
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(out + (size_t)b * out_stride + (size_t)head * HD + 4 * d4);
+        o2[0] = __floats2bfloat162_rn(O.x, O.y);
+        o2[1] = __floats2bfloat162_rn(O.z, O.w);
     }
     if (tid == 0) counters[b * nkv + kvh] = 0;          // ready for the next launch
 }
