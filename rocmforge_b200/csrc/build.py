@@ -34,6 +34,7 @@ MODULES: Dict[str, List[str]] = {
     "sampling": ["sampling.cu", "common.cuh"],
     "gemm_tcgen05": ["gemm_tcgen05.cu", "common.cuh"],
     "attention_decode": ["attention_decode.cu", "common.cuh"],
+    "attention_prefill": ["attention_prefill.cu", "common.cuh"],
     "attention_decode_noalloc": ["attention_decode_noalloc.cu", "attention_decode_noalloc.h", "attention_decode.cu",
                                  "common.cuh"],
 }

@@ -27,6 +27,9 @@ class StepRequest:
     want: Sequence[int] = ()          # indices among ``tokens`` whose logits are wanted
 
 
+Q_TILE = 64           # rows of a prefill attention tile (PF_BM in csrc/attention_prefill.cu)
+
+
 class StepBatch:
     """Host side of a step: flat int32 arrays, packed into one buffer for a single copy."""
 
@@ -59,15 +62,20 @@ class StepBatch:
                 rows.append(int(self.cu_q[i]) + int(w))
         self.want_rows = np.asarray(rows, dtype=np.int32)
         self.R = len(rows)
+        # 64-row tiles of the new tokens, (sequence, first row), for the tiled attention: decided here so
+        # that the device never searches
+        tiles = [(i, q0) for i in range(self.B) for q0 in range(0, int(self.n_new[i]), Q_TILE)]
+        self.q_tiles = np.asarray(tiles, dtype=np.int32).reshape(-1)
+        self.n_tiles = len(tiles)
         self.is_decode = bool((self.n_new == 1).all())
         self.max_new = int(self.n_new.max())
         self.max_end = int((self.starts + self.n_new).max())
 
     # layout of the packed descriptor, in int32 elements
     @staticmethod
-    def layout(T: int, B: int, R: int):
+    def layout(T: int, B: int, R: int, n_tiles: int = 0):
         names = [("tokens", T), ("tok_seq", T), ("tok_pos", T), ("seq_slot", B), ("seq_start", B),
-                 ("seq_nnew", B), ("cu_q", B + 1), ("want_rows", R)]
+                 ("seq_nnew", B), ("cu_q", B + 1), ("want_rows", R), ("q_tiles", 2 * n_tiles)]
         off, out = 0, {}
         for name, n in names:
             out[name] = (off, n)
@@ -75,11 +83,12 @@ class StepBatch:
         return out, off
 
     def pack(self) -> np.ndarray:
-        lay, total = self.layout(self.T, self.B, self.R)
+        lay, total = self.layout(self.T, self.B, self.R, self.n_tiles)
         buf = np.zeros((total,), dtype=np.int32)
         for name, arr in (("tokens", self.tokens), ("tok_seq", self.tok_seq), ("tok_pos", self.tok_pos),
                           ("seq_slot", np.asarray(self.slots, dtype=np.int32)), ("seq_start", self.starts),
-                          ("seq_nnew", self.n_new), ("cu_q", self.cu_q), ("want_rows", self.want_rows)):
+                          ("seq_nnew", self.n_new), ("cu_q", self.cu_q), ("want_rows", self.want_rows),
+                          ("q_tiles", self.q_tiles)):
             o, n = lay[name]
             buf[o:o + n] = arr
         return buf
@@ -117,6 +126,6 @@ class DeviceDescriptor:
             self._done = torch.cuda.Event()
             self._done.record()
 
-    def views(self, T: int, B: int, R: int):
-        lay, _ = StepBatch.layout(T, B, R)
+    def views(self, T: int, B: int, R: int, n_tiles: int = 0):
+        lay, _ = StepBatch.layout(T, B, R, n_tiles)
         return {name: self.dev[o:o + n] for name, (o, n) in lay.items()}

@@ -46,6 +46,7 @@ class StepContext:
         self.seq_nnew = views["seq_nnew"]
         self.cu_q = views["cu_q"]
         self.want_rows = views["want_rows"]
+        self.q_tiles = views["q_tiles"]
 
     # ---------------------------------------------------------------- matrix products
     def _tensor_cores(self, x, w, mode) -> bool:
@@ -137,5 +138,11 @@ class StepContext:
                 view.block_table, mixer.scale, view.window, max_chunks,
                 scratch("attn_decode_o", n_o, torch.float32), scratch("attn_decode_ml", n_ml, torch.float32),
                 scratch("attn_decode_counters", n_c, torch.int32))
+        if (not self.is_decode and self.compute_dtype == torch.bfloat16 and self.options.tuned_attention
+                and self.q_tiles.numel() > 0 and kernels.attention_prefill_supported(nh, nkv, hd)
+                and q.data_ptr() % 4 == 0 and q.stride(0) % 2 == 0):
+            return kernels.attention_prefill(q, nh, nkv, hd, view.k_pages, view.v_pages, self.q_tiles, self.seq_slot,
+                                             self.seq_start, self.seq_nnew, self.cu_q, view.block_table, mixer.scale,
+                                             view.window)
         return kernels.attention_generic(q, nh, nkv, hd, view.k_pages, view.v_pages, self.tok_seq, self.tok_pos,
                                          self.seq_slot, view.block_table, mixer.scale, view.window)

@@ -278,3 +278,42 @@ def attention_decode(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: i
             stream()),
           f"attention_decode (heads={n_heads}, kv_heads={n_kv_heads}, head_dim={head_dim})")
     return out
+
+
+PREFILL_TILE = 64
+
+
+def attention_prefill_supported(n_heads: int, n_kv_heads: int, head_dim: int) -> bool:
+    f = _f("attention_prefill", "rf_attention_prefill_supported", c_int, c_int, c_int)
+    return bool(f(n_heads, n_kv_heads, head_dim))
+
+
+def attention_prefill(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, k_pages, v_pages,
+                      q_tiles: torch.Tensor, seq_slot, seq_start, seq_nnew, cu_q, block_table, scale: float,
+                      window: int | None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Tiled causal attention of the new tokens over the bfloat16 paged cache (head_dim 64 or 128).
+
+    ``q_tiles`` is an int32 array of (sequence index, first row within the sequence's new tokens) pairs,
+    one per 64-row tile, built on the host.
+    """
+    need_cuda(q, k_pages, v_pages, q_tiles, seq_slot, seq_start, seq_nnew, cu_q, block_table)
+    T = q.shape[0]
+    need(q.dtype == torch.bfloat16 and q.dim() == 2 and q.stride(1) == 1, "attention_prefill: q must be bfloat16 [T, ...]")
+    need(k_pages.dtype == torch.bfloat16 and tuple(k_pages.shape[1:]) == (n_kv_heads, PAGE, head_dim)
+         and k_pages.is_contiguous() and v_pages.shape == k_pages.shape and v_pages.is_contiguous(),
+         "attention_prefill: bad cache page shape or dtype")
+    need(attention_prefill_supported(n_heads, n_kv_heads, head_dim),
+         f"attention_prefill: heads={n_heads}, kv_heads={n_kv_heads}, head_dim={head_dim} is not supported")
+    need(q_tiles.dtype == torch.int32 and q_tiles.numel() % 2 == 0, "attention_prefill: q_tiles must be int32 pairs")
+    if out is None:
+        out = torch.empty((T, n_heads * head_dim), dtype=torch.bfloat16, device=q.device)
+    from .tensor_core import status_word
+    f = _f("attention_prefill", "rf_attention_prefill", c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_ll,
+           c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int,
+           c_void_p, c_void_p)
+    check(f(ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(k_pages), ptr(v_pages), k_pages.shape[0], ptr(q_tiles),
+            q_tiles.numel() // 2, ptr(seq_slot), ptr(seq_start), ptr(seq_nnew), ptr(cu_q), ptr(block_table),
+            block_table.shape[1], n_heads, n_kv_heads, head_dim, float(scale), int(window or 0),
+            ptr(status_word(q.device)), stream()),
+          f"attention_prefill (heads={n_heads}, kv_heads={n_kv_heads}, head_dim={head_dim})")
+    return out

@@ -293,6 +293,64 @@ def test_attention_decode_finds_far_keys_and_the_window_edge():
     assert (out[1] - vs[0][499, 0].float()).abs().max() > 0.1
 
 
+@pytest.mark.parametrize("nh,nkv,hd,window", [(28, 4, 128, None), (14, 2, 64, None), (4, 4, 64, 100), (6, 1, 128, 70),
+                                              (2, 2, 128, 64), (3, 1, 64, 1)])
+def test_attention_prefill(nh, nkv, hd, window):
+    """Tiled attention: a whole prompt, a chunk appended to a context, tiny and page-straddling pieces."""
+    from rocmforge_b200 import kernels
+    dt = torch.bfloat16
+    lens = [300, 333, 65, 1, 64, 130]
+    new = [300, 50, 65, 1, 3, 129]
+    ks, vs, k_pages, v_pages, table = paged(lens, nkv, hd, dt, n_pages=48, seed=nh * hd)
+    g = torch.Generator().manual_seed(3)
+    T = sum(new)
+    q = torch.randn(T, nh * hd, generator=g).to(dt)
+    cu = [0]
+    for n in new:
+        cu.append(cu[-1] + n)
+    tiles = [(i, q0) for i, n in enumerate(new) for q0 in range(0, n, 64)]
+    dev = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(hd)
+    out = kernels.attention_prefill(q.to(DEV), nh, nkv, hd, k_pages, v_pages, dev(tiles).view(-1),
+                                    dev(list(range(1, len(lens) + 1))), dev([L - n for L, n in zip(lens, new)]),
+                                    dev(new), dev(cu), table, scale, window)
+    assert torch.isfinite(out.float()).all()
+    t = 0
+    for s, (L, n) in enumerate(zip(lens, new)):
+        for r in range(n):
+            ref = attention_reference(q[t].view(nh, hd), ks[s], vs[s], L - n + r, scale, window)
+            torch.testing.assert_close(out[t].cpu().double().view(nh, hd), ref, atol=2e-2, rtol=2e-2)
+            t += 1
+
+
+def test_attention_prefill_finds_far_keys_and_the_window_edge():
+    from rocmforge_b200 import kernels
+    dt, nh, nkv, hd, n = torch.bfloat16, 1, 1, 64, 700
+    ks, vs, k_pages, v_pages, table = paged([n], nkv, hd, dt, n_pages=16, seed=9)
+    # the last two rows are the queries; both look along dim 0
+    q = torch.zeros(2, hd); q[:, 0] = 8.0
+    dev = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+
+    def run(target, window):
+        kp = k_pages.clone()
+        page = int(table[1, target // 64])
+        kp[page, 0, target % 64] = 0
+        kp[page, 0, target % 64, 0] = 60.0
+        return kernels.attention_prefill(q.to(dt).to(DEV), nh, nkv, hd, kp, v_pages, dev([0, 0]), dev([1]), dev([n - 2]),
+                                         dev([2]), dev([0, 2]), table, 1.0 / math.sqrt(hd), window).float().cpu()
+
+    for target in (0, 63, 64, 320, 697):
+        out = run(target, None)
+        for row in range(2):
+            torch.testing.assert_close(out[row], vs[0][target, 0].float(), atol=2e-2, rtol=2e-2)
+    out = run(599, 100)            # rows at 698 and 699 with a window of 100: 599 is inside for the first row only
+    torch.testing.assert_close(out[0], vs[0][599, 0].float(), atol=2e-2, rtol=2e-2)
+    assert (out[1] - vs[0][599, 0].float()).abs().max() > 0.1
+    out = run(699, None)           # the last key belongs to the second row alone (causal)
+    torch.testing.assert_close(out[1], vs[0][699, 0].float(), atol=2e-2, rtol=2e-2)
+    assert (out[0] - vs[0][699, 0].float()).abs().max() > 0.1
+
+
 def test_rope_kv_write_from_partial_sums():
     """The rotation kernel adds the 32-bit partial sums of a K-split product and the bias itself."""
     from rocmforge_b200 import kernels
