@@ -32,7 +32,10 @@ MODULES: Dict[str, List[str]] = {
     "gemm_simt": ["gemm_simt.cu", "common.cuh"],
     "attention_generic": ["attention_generic.cu", "common.cuh"],
     "sampling": ["sampling.cu", "common.cuh"],
-    "gemm_tcgen05": ["gemm_tcgen05.cu", "common.cuh"],
+    "gemm_tcgen05": ["gemm_tcgen05.cu", "tcgen05_common.cuh", "common.cuh"],
+    # uses TMA multicast inside a cluster (this GPU's memory only): a file of its own, left out of
+    # multi-GPU runs; the package works without it
+    "gemm_tcgen05_cluster": ["gemm_tcgen05_cluster.cu", "tcgen05_common.cuh", "common.cuh"],
     "attention_decode": ["attention_decode.cu", "common.cuh"],
     "attention_prefill": ["attention_prefill.cu", "common.cuh"],
     "attention_decode_noalloc": ["attention_decode_noalloc.cu", "attention_decode_noalloc.h", "attention_decode.cu",
@@ -150,5 +153,10 @@ def load(name: str) -> ctypes.CDLL:
         return lib
 
 
+def available(name: str) -> bool:
+    """Whether the module's sources are present (an optional module may have been left out)."""
+    return name in MODULES and all(os.path.exists(os.path.join(HERE, src)) for src in MODULES[name])
+
+
 def build_all() -> None:
-    ensure_built(MODULES.keys())
+    ensure_built([n for n in MODULES if available(n)])

@@ -1,0 +1,235 @@
+// The large-M bfloat16 matrix product: persistent, clustered, with a double-buffered accumulator.
+//
+//   D[m, n] = sum_k X[m, k] * W[n, k]      tokens as accumulator rows, 128 x 256 tiles per CTA
+//
+// What it adds to gemm_tcgen05.cu, and why (B200: 148 SMs, ~2.25 PFLOP/s dense bf16, one L2):
+//   * A 128 x 256 x 64 step needs 48 KB of operands for 4.2 MFLOP; 148 SMs at full tensor rate would
+//     pull more from L2 than it delivers.  CTAs are therefore launched as clusters of CL along M:
+//     the CL CTAs of a cluster work on the same 256 weight rows, each loads 256/CL of them and
+//     multicasts its part into every CTA of the cluster, so a weight tile crosses L2 -> SM once per
+//     cluster instead of once per CTA.  (This GPU's own memory only; this file is used by
+//     single-GPU runs alone.)
+//   * CTAs are persistent: each cluster walks a list of (row group, column tile) work items, rows
+//     fastest, so that neighbouring clusters share a weight tile in L2.
+//   * The accumulator has two buffers in tensor memory (2 x 256 columns): while the four epilogue
+//     warps drain tile i, the MMA thread is already accumulating tile i + 1, and the TMA ring runs
+//     ahead across tile borders.
+// A stage of a CTA's ring is written by its own loads and by its peers' multicasts, so it may be
+// refilled only when every CTA of the cluster has finished reading it: the "empty" barrier of a
+// stage counts CL arrivals, and each CTA's MMA thread signals all of them with one multicast
+// tcgen05.commit.  Waits are bounded as everywhere; a cluster-wide barrier at both ends keeps a
+// CTA's shared memory alive while peers can still write to it.
+//
+// Counterpart in maeddesg/ROCmForge: the prefill GEMMs of hip_kernels/wmma/ (64x64x16 tiles, one
+// tile per block, single-buffered LDS, wmma_gemm_tiled.hip:57-195).
+#include "tcgen05_common.cuh"
+
+#define CG_BN 256
+#define CG_STAGES 4
+#define CG_THREADS 192
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_2d_multicast(uint32_t dst, const CUtensorMap* map, int c0, int c1,
+                                                      uint32_t bar, uint16_t mask) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.multicast::cluster"
+        " [%0], [%1, {%2, %3}], [%4], %5;"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar), "h"(mask) : "memory");
+}
+__device__ __forceinline__ void tcgen05_commit_multicast(uint32_t bar, uint16_t mask) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(mask) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// grid.x = n_clusters * CL (cluster dimension CL along x).  Work item w -> row group w % groups_m,
+// column tile w / groups_m; CTA `rank` of the cluster owns row tile group * CL + rank.
+template <int CL>
+__global__ void __launch_bounds__(CG_THREADS, 1)
+gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p,
+                       int groups_m, int tiles_n) {
+    constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2;
+    constexpr uint32_t B_BYTES = CG_BN * TC_BK * 2;
+    constexpr uint32_t B_PART = B_BYTES / CL;
+    constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr int S = CG_STAGES;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * STAGE_BYTES);
+    // full[S], empty[S], acc_full[2], acc_empty[2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 4);
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int cluster_id = blockIdx.x / CL, n_clusters = gridDim.x / CL;
+    const int n_work = groups_m * tiles_n;
+    const int kb_total = (p.K + TC_BK - 1) / TC_BK;
+    const uint16_t all = (uint16_t)((1u << CL) - 1);
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < S; ++s) {
+            mbar_init(smem_u32(&bars[s]), 1);
+            mbar_init(smem_u32(&bars[S + s]), CL);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&bars[2 * S + b]), 1);
+            mbar_init(smem_u32(&bars[2 * S + 2 + b]), 128);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+    }
+    if (warp == 1) {
+        tcgen05_alloc(smem_u32(tmem_slot), 512);
+        tcgen05_relinquish();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                  // every CTA's barriers exist before anyone signals them
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;                                  // running k-block count across work items
+            for (int w = cluster_id; w < n_work && !abort_flag; w += n_clusters) {
+                const int tile_m = (w % groups_m) * CL + (int)rank, tile_n = w / groups_m;
+                for (int kb = 0; kb < kb_total; ++kb, ++it) {
+                    const int s = it % S;
+                    if (!mbar_wait(smem_u32(&bars[S + s]), ((it / S) & 1) ^ 1, &abort_flag)) break;
+                    const uint32_t full = smem_u32(&bars[s]);
+                    mbar_expect_tx(full, STAGE_BYTES);
+                    const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+                    tma_load_2d(sa, &map_a, kb * TC_BK, tile_m * TC_BM, full);
+                    tma_load_2d_multicast(sa + A_BYTES + rank * B_PART, &map_b, kb * TC_BK,
+                                          tile_n * CG_BN + (int)rank * (CG_BN / CL), full, all);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(CG_BN);
+            int it = 0, local = 0;
+            for (int w = cluster_id; w < n_work && !abort_flag; w += n_clusters, ++local) {
+                const int buf = local & 1;
+                if (!mbar_wait(smem_u32(&bars[2 * S + 2 + buf]), ((local >> 1) & 1) ^ 1, &abort_flag)) break;
+                tcgen05_fence_after();
+                const uint32_t acc = tmem_base + buf * CG_BN;
+                bool ok = true;
+                for (int kb = 0; kb < kb_total; ++kb, ++it) {
+                    const int s = it % S;
+                    ok = mbar_wait(smem_u32(&bars[s]), (it / S) & 1, &abort_flag);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+                    const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+                    const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < TC_BK / 16; ++k)
+                        tcgen05_mma_bf16(acc, da + 2 * k, db + 2 * k, idesc, (kb | k) ? 1u : 0u);
+                    tcgen05_commit_multicast(smem_u32(&bars[S + s]), all);   // the stage is free in every CTA that fed it
+                }
+                if (!ok) break;
+                tcgen05_commit(smem_u32(&bars[2 * S + buf]));                // this accumulator is complete
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        int local = 0;
+        for (int w = cluster_id; w < n_work; w += n_clusters, ++local) {
+            const int buf = local & 1;
+            const int tile_m = (w % groups_m) * CL + (int)rank, tile_n = w / groups_m;
+            if (!mbar_wait(smem_u32(&bars[2 * S + buf]), (local >> 1) & 1, &abort_flag)) break;
+            tcgen05_fence_after();
+            const int m = tile_m * TC_BM + quarter * 32 + lane;
+            const uint32_t taddr = tmem_base + buf * CG_BN + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+            for (int c0 = 0; c0 < CG_BN; c0 += 32) {
+                uint32_t r[32];
+                tcgen05_ld32(taddr + c0, r);
+                tcgen05_wait_ld();
+                epilogue_rows<32>(p, r, m, tile_n * CG_BN + c0);
+            }
+            tcgen05_fence_before();
+            mbar_arrive(smem_u32(&bars[2 * S + 2 + buf]));                   // 128 arrivals hand the buffer back
+        }
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                  // no peer may still write here or signal our barriers
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tcgen05_dealloc(tmem_base, 512);
+    }
+    if (threadIdx.x == 0 && abort_flag && p.status) atomicExch(p.status, 4);
+}
+
+template <int CL>
+static int launch_cluster(const void* X, int ldx, const void* W, TcParams p, cudaStream_t st) {
+    constexpr size_t smem = (size_t)CG_STAGES * (TC_BM * TC_BK * 2 + CG_BN * TC_BK * 2) + (2 * CG_STAGES + 4) * 8 + 16 + 1024;
+    static int max_clusters = -1;
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CL; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.blockDim = dim3(CG_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (max_clusters < 0) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_cluster_kernel<CL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        cfg.gridDim = dim3(CL);
+        int n = 0;
+        e = cudaOccupancyMaxActiveClusters(&n, gemm_tc_cluster_kernel<CL>, &cfg);
+        if (e != cudaSuccess) return (int)e;
+        if (n <= 0) return RF_ERR_UNSUPPORTED;
+        max_clusters = n;
+    }
+    CUtensorMap ma, mb;
+    int e;
+    if ((e = make_map(&ma, X, p.M, p.K, ldx, TC_BM)) || (e = make_map(&mb, W, p.N, p.K, p.K, CG_BN / CL))) return e;
+    const int tiles_m = (p.M + TC_BM - 1) / TC_BM, groups_m = (tiles_m + CL - 1) / CL, tiles_n = (p.N + CG_BN - 1) / CG_BN;
+    int n_clusters = groups_m * tiles_n;
+    if (n_clusters > max_clusters) n_clusters = max_clusters;
+    cfg.gridDim = dim3(n_clusters * CL);
+    cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_tc_cluster_kernel<CL>, ma, mb, p, groups_m, tiles_n);
+    if (le != cudaSuccess) return (int)le;
+    RF_LAUNCH_CHECK();
+    return 0;
+}
+
+extern "C" {
+
+int rf_gemm_tc_cluster_supported(int M, int N, int K, int mode) {
+    if (M < 2 * TC_BM || N < CG_BN || K <= 0 || K % 8) return 0;
+    if (mode == EPI_SWIGLU && (N % 2)) return 0;
+    if (mode == EPI_PARTIAL) return 0;
+    return encode_fn() != nullptr;
+}
+
+// Same contract as rf_gemm_tc (tokens as rows), for M >= 256 and N >= 256.  cluster = 2 or 4 CTAs along M.
+int rf_gemm_tc_cluster(const void* X, int ldx, const void* W, const void* bias, int bias_is_f32, void* out, int ldo,
+                       int M, int N, int K, int mode, int cluster, int* status, cudaStream_t st) {
+    if (!rf_gemm_tc_cluster_supported(M, N, K, mode)) return RF_ERR_UNSUPPORTED;
+    TcParams p{out, bias, bias_is_f32, M, N, K, ldo, mode, (K + TC_BK - 1) / TC_BK, 0, status};
+    if (cluster == 2) return launch_cluster<2>(X, ldx, W, p, st);
+    if (cluster == 4) return launch_cluster<4>(X, ldx, W, p, st);
+    return RF_ERR_BAD_ARG;
+}
+
+}

@@ -83,6 +83,9 @@ class ModelSpec:
         mods: List[str] = ["gemm_simt", "sampling"]
         if compute_dtype == torch.bfloat16:
             mods.append("gemm_tcgen05")
+            from ..csrc import build
+            if build.available("gemm_tcgen05_cluster"):
+                mods.append("gemm_tcgen05_cluster")
         for part in self.named_parts().values():
             mods += part.cuda_modules(compute_dtype)
         return list(dict.fromkeys(mods))

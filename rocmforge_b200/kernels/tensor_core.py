@@ -52,8 +52,27 @@ def _common(x, w, bias, out):
         need(bias.shape == (w.shape[0],) and bias.dtype in (torch.float32, torch.bfloat16), "gemm: bias must be [N]")
 
 
+_cluster_ok = None
+
+
+def cluster_available() -> bool:
+    """The clustered kernel lives in an optional module (it uses TMA multicast, which multi-GPU runs exclude)."""
+    global _cluster_ok
+    if _cluster_ok is None:
+        from ..csrc import build
+        _cluster_ok = build.available("gemm_tcgen05_cluster")
+    return _cluster_ok
+
+
+def cluster_supported(M: int, N: int, K: int, mode: int = STORE) -> bool:
+    if not cluster_available():
+        return False
+    f = fn("gemm_tcgen05_cluster", "rf_gemm_tc_cluster_supported", [c_int, c_int, c_int, c_int])
+    return bool(f(M, N, K, mode))
+
+
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, *, mode: int = STORE,
-            out: Optional[torch.Tensor] = None) -> torch.Tensor:
+            out: Optional[torch.Tensor] = None, cluster: Optional[int] = None) -> torch.Tensor:
     """Tokens as accumulator rows (any M).  STORE -> bf16 [M,N]; F32 -> f32 [M,N]; RESIDUAL: out (f32) += x w^T;
     SWIGLU -> bf16 [M, N/2] from row-interleaved gate/up weights."""
     _common(x, w, bias, out)
@@ -66,6 +85,16 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = Non
         need(mode != RESIDUAL, "gemm: RESIDUAL needs the tensor to add into")
         out = torch.empty((M, cols), dtype=odt, device=x.device)
     need(out.shape == (M, cols) and out.dtype == odt and out.stride(1) == 1, "gemm: output has the wrong shape or dtype")
+    if cluster is None:
+        cluster = (4 if (M + 127) // 128 >= 4 else 2) if cluster_supported(M, N, K, mode) else 0
+    if cluster:
+        f = fn("gemm_tcgen05_cluster", "rf_gemm_tc_cluster",
+               [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                c_void_p, c_void_p])
+        check(f(ptr(x), x.stride(0), ptr(w), ptr(bias), int(bias is not None and bias.dtype == torch.float32),
+                ptr(out), out.stride(0), M, N, K, mode, cluster, ptr(status_word(x.device)), stream()),
+              f"gemm_tc_cluster ({M}x{N}x{K}, cluster {cluster})")
+        return out
     f = _f("rf_gemm_tc", c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
            c_void_p, c_void_p)
     check(f(ptr(x), x.stride(0), ptr(w), ptr(bias), int(bias is not None and bias.dtype == torch.float32), ptr(out),

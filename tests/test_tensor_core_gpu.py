@@ -43,6 +43,26 @@ def test_tokens_as_rows(M, N, K):
     tc.check_status(DEV)
 
 
+@pytest.mark.parametrize("cluster", [2, 4])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (300, 520, 1000), (2048, 4608, 3584), (1100, 3584, 18944),
+                                   (257, 1000, 3584), (640, 37888, 3584)])
+def test_clustered_persistent_kernel(M, N, K, cluster):
+    from rocmforge_b200.kernels import tensor_core as tc
+    if not tc.cluster_available():
+        pytest.skip("the clustered module is not part of this checkout")
+    x, w, b = rnd(M, K, seed=1), rnd(N, K, seed=2, scale=0.05), rnd(N, seed=3, dt=torch.float32)
+    ref = x.double() @ w.double().t()
+    close(tc.gemm_tc(x, w, cluster=cluster), ref, "store")
+    close(tc.gemm_tc(x, w, b, mode=tc.F32, cluster=cluster), ref + b.double(), "f32 + bias")
+    acc = rnd(M, N, seed=4, dt=torch.float32)
+    want = acc.double() + ref
+    tc.gemm_tc(x, w, mode=tc.RESIDUAL, out=acc, cluster=cluster)
+    close(acc, want, "residual")
+    close(tc.gemm_tc(x, w, mode=tc.SWIGLU, cluster=cluster), P.silu(ref[:, 0::2]) * ref[:, 1::2], "swiglu")
+    assert torch.equal(tc.gemm_tc(x, w, cluster=cluster), tc.gemm_tc(x, w, cluster=0)), "both kernels sum in the same order"
+    tc.check_status(DEV)
+
+
 @pytest.mark.parametrize("M", [1, 3, 8, 16, 17, 33, 64])
 @pytest.mark.parametrize("N,K", [(128, 64), (200, 136), (3584, 3584), (1000, 18944), (4608, 3584)])
 def test_weights_as_rows(M, N, K):
