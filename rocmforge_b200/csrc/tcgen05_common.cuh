@@ -124,32 +124,83 @@ __host__ __device__ constexpr uint32_t make_idesc(int n) {
 
 
 // Epilogue of one 32-column (or 16-column) chunk in the "tokens as rows" orientation: lane = token m,
-// registers = CH consecutive weight rows starting at n0.
+// registers = CH consecutive weight rows starting at n0.  A thread owns a contiguous piece of its
+// output row, so it writes 16 bytes at a time wherever the row and the chunk are aligned for it
+// (scalar stores of 2 bytes from 32 lanes to 32 different rows would make the epilogue, not the
+// tensor cores, the limit of the kernel).
+__device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// silu for a bfloat16 result: the hardware exponential and reciprocal are 32-bit with a relative
+// error near 1e-6, three orders below the rounding of the output
+__device__ __forceinline__ float silu_fast(float g) { return __fdividef(g, 1.f + __expf(-g)); }
+
 template <int CH>
 __device__ __forceinline__ void epilogue_rows(const TcParams& p, const uint32_t* r, int m, int n0) {
     if (m >= p.M) return;
+    const bool whole = n0 + CH <= p.N;
     if (p.mode == EPI_SWIGLU) {
         __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.ldo + (n0 >> 1);
+        if (whole && !(reinterpret_cast<uintptr_t>(o) & 15)) {
+#pragma unroll
+            for (int j = 0; j < CH; j += 16) {
+                uint32_t w[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float g0 = __uint_as_float(r[j + 4 * q]), u0 = __uint_as_float(r[j + 4 * q + 1]);
+                    const float g1 = __uint_as_float(r[j + 4 * q + 2]), u1 = __uint_as_float(r[j + 4 * q + 3]);
+                    w[q] = pack_bf16x2(silu_fast(g0) * u0, silu_fast(g1) * u1);
+                }
+                *reinterpret_cast<uint4*>(o + (j >> 1)) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+            return;
+        }
 #pragma unroll
         for (int j = 0; j < CH; j += 2)
             if (n0 + j + 1 < p.N) {
                 const float g = __uint_as_float(r[j]), u = __uint_as_float(r[j + 1]);
                 o[j >> 1] = __float2bfloat16_rn(g / (1.f + expf(-g)) * u);
             }
-    } else {
-#pragma unroll
-        for (int j = 0; j < CH; ++j) {
-            const int n = n0 + j;
-            if (n < p.N) {
-                float v = __uint_as_float(r[j]);
-                if (p.bias) v += load_vec(p.bias, p.bias_is_f32, n);
-                const size_t o = (size_t)m * p.ldo + n;
-                if (p.mode == EPI_STORE) reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(v);
-                else if (p.mode == EPI_F32) reinterpret_cast<float*>(p.out)[o] = v;
-                else reinterpret_cast<float*>(p.out)[o] += v;
-            }
-        }
+        return;
     }
+    float v[CH];
+#pragma unroll
+    for (int j = 0; j < CH; ++j) {
+        v[j] = __uint_as_float(r[j]);
+        if (p.bias && n0 + j < p.N) v[j] += load_vec(p.bias, p.bias_is_f32, n0 + j);
+    }
+    const size_t o = (size_t)m * p.ldo + n0;
+    if (p.mode == EPI_STORE) {
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + o;
+        if (whole && !(reinterpret_cast<uintptr_t>(dst) & 15)) {
+#pragma unroll
+            for (int j = 0; j < CH; j += 8)
+                *reinterpret_cast<uint4*>(dst + j) = make_uint4(pack_bf16x2(v[j], v[j + 1]), pack_bf16x2(v[j + 2], v[j + 3]),
+                                                                 pack_bf16x2(v[j + 4], v[j + 5]), pack_bf16x2(v[j + 6], v[j + 7]));
+            return;
+        }
+#pragma unroll
+        for (int j = 0; j < CH; ++j) if (n0 + j < p.N) dst[j] = __float2bfloat16_rn(v[j]);
+        return;
+    }
+    float* dst = reinterpret_cast<float*>(p.out) + o;
+    if (whole && !(reinterpret_cast<uintptr_t>(dst) & 15)) {
+#pragma unroll
+        for (int j = 0; j < CH; j += 4) {
+            float4 t = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            if (p.mode == EPI_RESIDUAL) {
+                const float4 old = *reinterpret_cast<const float4*>(dst + j);
+                t.x += old.x; t.y += old.y; t.z += old.z; t.w += old.w;
+            }
+            *reinterpret_cast<float4*>(dst + j) = t;
+        }
+        return;
+    }
+#pragma unroll
+    for (int j = 0; j < CH; ++j)
+        if (n0 + j < p.N) dst[j] = (p.mode == EPI_RESIDUAL ? dst[j] : 0.f) + v[j];
 }
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda).
