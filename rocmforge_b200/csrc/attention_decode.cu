@@ -45,6 +45,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
     float* o_red = reinterpret_cast<float*>(dec_smem);                                 // [4][GP][HD], over k_s when done
     __shared__ int is_last, gave_up;
 
+    pdl_trigger();
     const int G = nh / nkv;
     const int c = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z, tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
@@ -59,6 +60,9 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
     int k_begin = lo - k_first; if (k_begin < 0) k_begin = 0;                  // chunk-relative valid range
     int k_last = pos - k_first; if (k_last > DEC_CHUNK - 1) k_last = DEC_CHUNK - 1;
 
+    // positions, slots and block tables are not written by any kernel of the step; the queries and the
+    // newest keys and values are: wait for the kernel before us
+    pdl_wait();
     // ---- bring the chunk's pages in: all copies in flight at once
     const uint32_t bar_a = dec_smem_u32(bar);
     if (tid == 0) {
@@ -295,7 +299,7 @@ static int launch(const void* q, int q_stride, void* out, int out_stride, const 
         configured = true;
     }
     dim3 grid(max_chunks, nkv, B);
-    attention_decode_kernel<EPL><<<grid, DEC_THREADS, smem, st>>>(
+    rf_launch(attention_decode_kernel<EPL>, grid, dim3(DEC_THREADS), smem, st,
         reinterpret_cast<const __nv_bfloat16*>(q), q_stride, reinterpret_cast<__nv_bfloat16*>(out), out_stride,
         reinterpret_cast<const __nv_bfloat16*>(k_pages), reinterpret_cast<const __nv_bfloat16*>(v_pages), tok_seq,
         tok_pos, seq_slot, block_table, max_pages, nh, nkv, scale, window, max_chunks, part_o, part_ml, counters, status);

@@ -23,6 +23,8 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
                          const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                          const int* __restrict__ seq_slot, const int* __restrict__ block_table,
                          int max_pages, int nh, int nkv, int hd, float scale, int window) {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ float smem[];
     float* qs = smem;                               // hd
     float* probs = qs + hd;                         // ATT_THREADS
@@ -100,7 +102,7 @@ static int launch(const void* q, int q_stride, void* out, int out_stride, const 
     const size_t smem = (size_t)(hd_pad + ATT_THREADS + 34) * sizeof(float) + ATT_THREADS * sizeof(long long);
     if (hd & 1) return RF_ERR_UNSUPPORTED;
     dim3 grid(nh, T_);
-    attention_generic_kernel<T><<<grid, ATT_THREADS, smem, st>>>(
+    rf_launch(attention_generic_kernel<T>, grid, dim3(ATT_THREADS), smem, st,
         reinterpret_cast<const T*>(q), q_stride, reinterpret_cast<T*>(out), out_stride,
         reinterpret_cast<const T*>(k_pages), reinterpret_cast<const T*>(v_pages), tok_seq, tok_pos, seq_slot,
         block_table, max_pages, nh, nkv, hd, scale, window);

@@ -54,6 +54,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2 * STAGE_BYTES);
     __shared__ int gave_up;
 
+    pdl_trigger();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int gid = lane >> 2, tig = lane & 3;
     const int seq = tiles[2 * blockIdx.x], q0 = tiles[2 * blockIdx.x + 1];
@@ -75,6 +76,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
     }
     __syncthreads();
+    pdl_wait();                                        // queries, keys and values come from the kernel before us
 
     auto issue = [&](int it) {                          // thread 0: bring page kt_lo + it into stage it & 1
         const int stage = it & 1;
@@ -299,7 +301,7 @@ static int pf_launch(const CUtensorMap& mk, const CUtensorMap& mv, const void* q
         configured = true;
     }
     dim3 grid(n_tiles, nh);
-    attention_prefill_kernel<HD><<<grid, PF_THREADS, smem, st>>>(
+    rf_launch(attention_prefill_kernel<HD>, grid, dim3(PF_THREADS), smem, st,
         mk, mv, reinterpret_cast<const __nv_bfloat16*>(q), q_stride, reinterpret_cast<__nv_bfloat16*>(out), out_stride,
         tiles, seq_slot, seq_start, seq_nnew, cu_q, block_table, max_pages, nh, nkv, scale, window, status);
     RF_LAUNCH_CHECK();

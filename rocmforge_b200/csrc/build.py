@@ -149,6 +149,8 @@ def load(name: str) -> ctypes.CDLL:
             lib = ctypes.CDLL(lib_path(name))
         except OSError as e:
             raise BuildError(f"CUDA module {name} was built but cannot be loaded: {e}") from None
+        if hasattr(lib, "rf_set_pdl"):
+            lib.rf_set_pdl(ctypes.c_int(0 if os.environ.get("ROCMFORGE_B200_PDL", "1") == "0" else 1))
         _loaded[name] = lib
         return lib
 

@@ -10,6 +10,38 @@
 #define RF_ERR_BAD_ARG (-1)
 #define RF_ERR_UNSUPPORTED (-2)
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// Kernels of a step run back to back on one stream.  With the launch attribute below a kernel may be
+// scheduled while its predecessor is still running: it executes its set-up (and whatever does not
+// depend on the predecessor, above all streaming weights into shared memory) and then blocks in
+// pdl_wait() until the predecessor has completed and its writes are visible.  Every kernel of this
+// library calls pdl_wait() before it reads anything another kernel of the step wrote and before it
+// writes anything at all; what it touches earlier is only weights, the step descriptor and block
+// tables, which no kernel of a step writes.  Launched without the attribute, both calls do nothing.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+static int g_rf_pdl = 0;
+extern "C" void rf_set_pdl(int on) { g_rf_pdl = on; }
+
+template <typename... KArgs, typename... Args>
+static cudaError_t rf_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                             Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    if (g_rf_pdl) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 #define RF_LAUNCH_CHECK()                         \
     do {                                          \
         cudaError_t e__ = cudaGetLastError();     \

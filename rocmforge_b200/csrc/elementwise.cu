@@ -13,6 +13,8 @@
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                              float* __restrict__ out, int H, int V) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     int id = ids[t];
     id = id < 0 ? 0 : (id >= V ? V - 1 : id);   // ids are validated on the host; never read outside
@@ -32,6 +34,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const void* __restrict
                                    int pending_kind, int n_pending, size_t pending_stride,
                                    const void* __restrict__ w, int w_is_f32, float eps,
                                    T* __restrict__ y, const int* __restrict__ rows, int H) {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ float row_buf[];          // H floats + 33 for the reduction
     float* red = row_buf + H;
     const int r = blockIdx.x;
@@ -68,10 +72,12 @@ __global__ void __launch_bounds__(1024)
 add_rmsnorm_vec_kernel(float* __restrict__ h, const void* __restrict__ pending, int pending_kind, int n_pending,
                        size_t pending_stride, const void* __restrict__ w, int w_is_f32, float eps,
                        T* __restrict__ y, const int* __restrict__ rows, int H) {
+    pdl_trigger();
     __shared__ float red[34];
     const int r = blockIdx.x;
     const int t = rows ? rows[r] : r;
     const int nvec = H >> 2;
+    pdl_wait();
     float4* hrow = reinterpret_cast<float4*>(h + (size_t)t * H);
     float4 v[NV];
     float ss = 0.f;
@@ -129,6 +135,8 @@ __global__ void rope_kv_write_kernel(const void* __restrict__ src, int row_strid
                                      T* __restrict__ k_pages, T* __restrict__ v_pages, int write_kv) {
     // grid: (token, block of pairs).  Pair index space: nh + nkv rotated heads, then nkv value heads,
     // hd/2 pairs each (a value "pair" is two neighbouring elements, copied).
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     const int half = hd >> 1;
     const int idx = blockIdx.y * blockDim.x + threadIdx.x;
@@ -175,6 +183,8 @@ __global__ void rope_kv_write_kernel(const void* __restrict__ src, int row_strid
 // interleaved row by row at load time); a[t, j] = silu(gate) * up, evaluated in 32-bit.
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ a, size_t n_out, int I) {
+    pdl_trigger();
+    pdl_wait();
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n_out;
          idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / I, j = idx - t * I;
@@ -188,7 +198,7 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ a, size_
 template <typename T>
 static int launch_embed(const void* table, const int* ids, float* out, int T_, int H, int V, cudaStream_t st) {
     if (T_ <= 0) return 0;
-    embed_kernel<T><<<T_, 256, 0, st>>>(reinterpret_cast<const T*>(table), ids, out, H, V);
+    rf_launch(embed_kernel<T>, dim3(T_), dim3(256), 0, st, reinterpret_cast<const T*>(table), ids, out, H, V);
     RF_LAUNCH_CHECK();
     return 0;
 }
@@ -205,9 +215,9 @@ static int launch_add_rmsnorm(float* h, const void* pending, int kind, int n_pen
         if (threads > 1024) threads = 1024;
         const int per = (nvec + threads - 1) / threads;
         T* yy = reinterpret_cast<T*>(y);
-        if (per <= 1) add_rmsnorm_vec_kernel<T, 1><<<n_rows, threads, 0, st>>>(h, pending, kind, n_pending, pstride, w, w_is_f32, eps, yy, rows, H);
-        else if (per <= 2) add_rmsnorm_vec_kernel<T, 2><<<n_rows, threads, 0, st>>>(h, pending, kind, n_pending, pstride, w, w_is_f32, eps, yy, rows, H);
-        else add_rmsnorm_vec_kernel<T, 4><<<n_rows, threads, 0, st>>>(h, pending, kind, n_pending, pstride, w, w_is_f32, eps, yy, rows, H);
+        if (per <= 1) rf_launch(add_rmsnorm_vec_kernel<T, 1>, dim3(n_rows), dim3(threads), 0, st, h, pending, kind, n_pending, pstride, w, w_is_f32, eps, yy, rows, H);
+        else if (per <= 2) rf_launch(add_rmsnorm_vec_kernel<T, 2>, dim3(n_rows), dim3(threads), 0, st, h, pending, kind, n_pending, pstride, w, w_is_f32, eps, yy, rows, H);
+        else rf_launch(add_rmsnorm_vec_kernel<T, 4>, dim3(n_rows), dim3(threads), 0, st, h, pending, kind, n_pending, pstride, w, w_is_f32, eps, yy, rows, H);
         RF_LAUNCH_CHECK();
         return 0;
     }
@@ -219,8 +229,8 @@ static int launch_add_rmsnorm(float* h, const void* pending, int kind, int n_pen
         if (e != cudaSuccess) return (int)e;
     }
     const int threads = H >= 2048 ? 512 : 256;
-    add_rmsnorm_kernel<T><<<n_rows, threads, smem, st>>>(h, pending, kind, n_pending, pstride, w, w_is_f32,
-                                                         eps, reinterpret_cast<T*>(y), rows, H);
+    rf_launch(add_rmsnorm_kernel<T>, dim3(n_rows), dim3(threads), smem, st, h, pending, kind, n_pending, pstride, w,
+              w_is_f32, eps, reinterpret_cast<T*>(y), rows, H);
     RF_LAUNCH_CHECK();
     return 0;
 }
@@ -237,11 +247,11 @@ static int launch_rope_kv_write(const void* src, int row_stride, int n_partials,
     const dim3 grid(T_, (n_pairs + 255) / 256);
     if (T_ > 2147483647 || grid.y > 65535) return RF_ERR_UNSUPPORTED;
     if (n_partials > 0)
-        rope_kv_write_kernel<T, true><<<grid, 256, 0, st>>>(src, row_stride, n_partials, partial_stride, bias,
+        rf_launch(rope_kv_write_kernel<T, true>, grid, dim3(256), 0, st, src, row_stride, n_partials, partial_stride, bias,
             bias_is_f32, reinterpret_cast<T*>(q_out), q_out_stride, nh, nkv, hd, inv_freq, tok_seq, tok_pos, seq_slot,
             block_table, max_pages, reinterpret_cast<T*>(k_pages), reinterpret_cast<T*>(v_pages), write_kv);
     else
-        rope_kv_write_kernel<T, false><<<grid, 256, 0, st>>>(src, row_stride, 0, 0, nullptr, 0,
+        rf_launch(rope_kv_write_kernel<T, false>, grid, dim3(256), 0, st, src, row_stride, 0, (size_t)0, (const void*)nullptr, 0,
             reinterpret_cast<T*>(q_out), q_out_stride, nh, nkv, hd, inv_freq, tok_seq, tok_pos, seq_slot,
             block_table, max_pages, reinterpret_cast<T*>(k_pages), reinterpret_cast<T*>(v_pages), write_kv);
     RF_LAUNCH_CHECK();
@@ -253,7 +263,7 @@ static int launch_swiglu(const void* gu, void* a, int T_, int I, cudaStream_t st
     const size_t n = (size_t)T_ * I;
     if (n == 0) return 0;
     const int blocks = (int)((n + 255) / 256 > 148 * 16 ? 148 * 16 : (n + 255) / 256);
-    swiglu_kernel<T><<<blocks, 256, 0, st>>>(reinterpret_cast<const T*>(gu), reinterpret_cast<T*>(a), n, I);
+    rf_launch(swiglu_kernel<T>, dim3(blocks), dim3(256), 0, st, reinterpret_cast<const T*>(gu), reinterpret_cast<T*>(a), n, I);
     RF_LAUNCH_CHECK();
     return 0;
 }

@@ -18,6 +18,8 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const T* __restrict__ X, const T* __restrict__ W, const void* __restrict__ bias,
                  int bias_is_f32, void* __restrict__ Y, int M, int N, int K, int ldx, int ldy, int mode) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float Xs[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
@@ -70,8 +72,8 @@ static int launch(const void* X, const void* W, const void* bias, int bias_is_f3
     if (K <= 0 || mode < 0 || mode > 2) return RF_ERR_BAD_ARG;
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     if (grid.y > 65535) return RF_ERR_UNSUPPORTED;
-    gemm_simt_kernel<T><<<grid, 256, 0, st>>>(reinterpret_cast<const T*>(X), reinterpret_cast<const T*>(W), bias,
-                                              bias_is_f32, Y, M, N, K, ldx, ldy, mode);
+    rf_launch(gemm_simt_kernel<T>, grid, dim3(256), 0, st, reinterpret_cast<const T*>(X), reinterpret_cast<const T*>(W), bias,
+              bias_is_f32, Y, M, N, K, ldx, ldy, mode);
     RF_LAUNCH_CHECK();
     return 0;
 }

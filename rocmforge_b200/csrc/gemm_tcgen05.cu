@@ -40,6 +40,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
     __shared__ int abort_flag;
 
+    pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile_a = blockIdx.y, tile_b = blockIdx.x, split = blockIdx.z;
     const int kb_total = (p.K + TC_BK - 1) / TC_BK;
@@ -71,7 +72,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (warp == 0) {
         // ---------------- producer: one thread feeds the ring of stages
         if (lane == 0) {
-            for (int i = 0; i < n_kb; ++i) {
+            // The weight operand does not depend on the kernel before this one: fill the ring with it at
+            // once, wait for that kernel, then add the activation operand to the same stages.
+            const int pre = n_kb < STAGES ? n_kb : STAGES;
+            for (int i = 0; i < pre; ++i) {
+                const uint32_t full = smem_u32(&bars[i]);
+                mbar_expect_tx(full, STAGE_BYTES);
+                const uint32_t sa = smem_u32(smem + i * STAGE_BYTES);
+                const int k0 = (kb_begin + i) * TC_BK;
+                if (SWAP) tma_load_2d(sa, &map_a, k0, tile_a * TC_BM, full);
+                else tma_load_2d(sa + A_BYTES, &map_b, k0, tile_b * BN, full);
+            }
+            pdl_wait();
+            for (int i = 0; i < pre; ++i) {
+                const uint32_t full = smem_u32(&bars[i]);
+                const uint32_t sa = smem_u32(smem + i * STAGE_BYTES);
+                const int k0 = (kb_begin + i) * TC_BK;
+                if (SWAP) tma_load_2d(sa + A_BYTES, &map_b, k0, tile_b * BN, full);
+                else tma_load_2d(sa, &map_a, k0, tile_a * TC_BM, full);
+            }
+            for (int i = pre; i < n_kb; ++i) {
                 const int s = i % STAGES;
                 const uint32_t parity = ((i / STAGES) & 1) ^ 1;
                 if (!mbar_wait(smem_u32(&bars[STAGES + s]), parity, &abort_flag)) break;
@@ -105,6 +125,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     } else {
         // ---------------- epilogue: four warps, one quarter of the 128 lanes each
         const int quarter = warp & 3;
+        pdl_wait();                                      // the output may still be read by the kernel before us
         const bool ok = mbar_wait(smem_u32(&bars[2 * STAGES]), 0, &abort_flag);
         tcgen05_fence_after();
         if (ok && n_kb > 0) {
@@ -165,7 +186,7 @@ static int launch_cfg(const CUtensorMap& ma, const CUtensorMap& mb, const TcPara
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    gemm_tc_kernel<BN, SWAP, STAGES><<<grid, TC_THREADS, smem, st>>>(ma, mb, p);
+    rf_launch(gemm_tc_kernel<BN, SWAP, STAGES>, grid, dim3(TC_THREADS), smem, st, ma, mb, p);
     RF_LAUNCH_CHECK();
     return 0;
 }

@@ -71,6 +71,7 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 4);
     __shared__ int abort_flag;
 
+    pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
     const int cluster_id = blockIdx.x / CL, n_clusters = gridDim.x / CL;
@@ -101,6 +102,7 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     cluster_sync_all();                                  // every CTA's barriers exist before anyone signals them
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();                                          // activations in, outputs out: both belong to the step's chain
 
     if (warp == 0) {
         if (lane == 0) {
@@ -181,9 +183,11 @@ static int launch_cluster(const void* X, int ldx, const void* W, TcParams p, cud
     constexpr size_t smem = (size_t)CG_STAGES * (TC_BM * TC_BK * 2 + CG_BN * TC_BK * 2) + (2 * CG_STAGES + 4) * 8 + 16 + 1024;
     static int max_clusters = -1;
     cudaLaunchConfig_t cfg = {};
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = CL; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.blockDim = dim3(CG_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
@@ -207,6 +211,7 @@ static int launch_cluster(const void* X, int ldx, const void* W, TcParams p, cud
     int n_clusters = groups_m * tiles_n;
     if (n_clusters > max_clusters) n_clusters = max_clusters;
     cfg.gridDim = dim3(n_clusters * CL);
+    cfg.numAttrs = g_rf_pdl ? 2 : 1;
     cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_tc_cluster_kernel<CL>, ma, mb, p, groups_m, tiles_n);
     if (le != cudaSuccess) return (int)le;
     RF_LAUNCH_CHECK();

@@ -14,6 +14,8 @@
 // ---------------------------------------------------------------- argmax
 __global__ void __launch_bounds__(1024)
 argmax_kernel(const float* __restrict__ logits, int V, long long row_stride, int* __restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float sval[32];
     __shared__ int sidx[32];
     const float* x = logits + (size_t)blockIdx.x * row_stride;
@@ -50,7 +52,7 @@ argmax_kernel(const float* __restrict__ logits, int V, long long row_stride, int
 extern "C" int rf_argmax(const float* logits, int rows, int V, long long row_stride, int* out, cudaStream_t st) {
     if (rows <= 0) return 0;
     if (V <= 0) return RF_ERR_BAD_ARG;
-    argmax_kernel<<<rows, 1024, 0, st>>>(logits, V, row_stride, out);
+    rf_launch(argmax_kernel, dim3(rows), dim3(1024), 0, st, logits, V, row_stride, out);
     RF_LAUNCH_CHECK();
     return 0;
 }
@@ -142,6 +144,8 @@ __global__ void __launch_bounds__(SMP_THREADS)
 sample_kernel(const float* __restrict__ logits, int V, long long row_stride, float temperature, float top_p,
               int top_k, const unsigned long long* __restrict__ seeds, const int* __restrict__ draw_counter,
               int* __restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ SampleShared s;
     const float* x = logits + (size_t)blockIdx.x * row_stride;
     const int tid = threadIdx.x;
@@ -288,8 +292,8 @@ extern "C" int rf_sample(const float* logits, int rows, int V, long long row_str
                          int* out, cudaStream_t st) {
     if (rows <= 0) return 0;
     if (V <= 0 || !seeds) return RF_ERR_BAD_ARG;
-    sample_kernel<<<rows, SMP_THREADS, 0, st>>>(logits, V, row_stride, temperature, top_p, top_k, seeds,
-                                                draw_counter, out);
+    rf_launch(sample_kernel, dim3(rows), dim3(SMP_THREADS), 0, st, logits, V, row_stride, temperature, top_p, top_k, seeds,
+              draw_counter, out);
     RF_LAUNCH_CHECK();
     return 0;
 }
@@ -299,6 +303,8 @@ extern "C" int rf_sample(const float* logits, int rows, int V, long long row_str
 // step's tokens and every sequence moves one position on (the reference's
 // increment_decode_state_kernel, hip_kernels/elementwise.hip:721-753).
 __global__ void advance_decode_kernel(int* tokens, int* tok_pos, int* seq_start, const int* sampled, int B) {
+    pdl_trigger();
+    pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < B) {
         tokens[i] = sampled[i];
@@ -310,7 +316,7 @@ __global__ void advance_decode_kernel(int* tokens, int* tok_pos, int* seq_start,
 extern "C" int rf_advance_decode(int* tokens, int* tok_pos, int* seq_start, const int* sampled, int B,
                                  cudaStream_t st) {
     if (B <= 0) return 0;
-    advance_decode_kernel<<<(B + 127) / 128, 128, 0, st>>>(tokens, tok_pos, seq_start, sampled, B);
+    rf_launch(advance_decode_kernel, dim3((B + 127) / 128), dim3(128), 0, st, tokens, tok_pos, seq_start, sampled, B);
     RF_LAUNCH_CHECK();
     return 0;
 }
