@@ -284,6 +284,328 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
     if (tid == 0) counters[b * nkv + kvh] = 0;          // ready for the next launch
 }
 
+// ---------------------------------------------------------------- the clustered variant
+// For contexts of ordinary length the merge through global memory above costs more than the attention
+// itself (write partials, fence, count arrivals, fence, read them back: five trips to L2).  Here the
+// CTAs that share a (sequence, kv head) form a thread-block cluster of `splits` CTAs instead.  CTA r
+// walks the pages r, r + splits, r + 2*splits, ... of the context with a three-stage ring of bulk
+// copies; each warp owns 16 of a page's 64 keys and keeps its own running maximum, sum and output
+// across pages (the online softmax, as in the prefill kernel), so a page costs one mbarrier wait and
+// one CTA barrier.  At the end the four warps' states are merged in shared memory, and CTA 0 reads its
+// peers' states through distributed shared memory, in rank order, and writes the result.  No scratch
+// memory, no atomics; the launch shape depends on the batch alone, so a captured graph stays valid
+// while the context grows.
+#define DCL_STAGES 3
+
+__device__ __forceinline__ uint32_t dcl_cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void dcl_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float dcl_ld_remote(const float* local, uint32_t rank) {
+    uint32_t raddr;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr) : "r"(dec_smem_u32(local)), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(raddr) : "memory");
+    return v;
+}
+
+template <int EPL>
+__global__ void __launch_bounds__(DEC_THREADS)
+attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* __restrict__ out,
+                                int out_stride, const __nv_bfloat16* __restrict__ k_pages,
+                                const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ tok_seq,
+                                const int* __restrict__ tok_pos, const int* __restrict__ seq_slot,
+                                const int* __restrict__ block_table, int max_pages, int nh, int nkv, float scale,
+                                int window, int splits, int* __restrict__ status) {
+    constexpr int HD = EPL * 32;
+    constexpr uint32_t SLAB = RF_PAGE * HD * 2;                 // one page's keys (or values) of one kv head
+    extern __shared__ __align__(128) uint8_t dec_smem[];
+    __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(dec_smem);                  // [stage][K | V][64][HD]
+    float* w_m = reinterpret_cast<float*>(dec_smem);                                   // [4 warps][GP]: over the ring,
+    float* w_l = w_m + DEC_WARPS * DEC_GP;                                              // [4][GP]        once the last
+    float* w_o = w_l + DEC_WARPS * DEC_GP;                                              // [4][GP][HD]    page is done
+    float* c_m = reinterpret_cast<float*>(dec_smem + DCL_STAGES * 2 * SLAB);           // this CTA: [GP]
+    float* c_l = c_m + DEC_GP;                                                          // [GP]
+    float* c_o = c_l + DEC_GP;                                                          // [GP][HD]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(c_o + DEC_GP * HD);                   // [stages]
+    __shared__ int gave_up;
+
+    pdl_trigger();
+    const int G = nh / nkv;
+    const int kvh = blockIdx.y, b = blockIdx.z, tid = threadIdx.x;
+    const int lane = tid & 31, warp = tid >> 5, gid = lane >> 2, tig = lane & 3;
+    const int rank = splits > 1 ? (int)dcl_cluster_rank() : 0;
+    const int pos = tok_pos[b];
+    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int p_lo = lo / RF_PAGE, p_hi = pos / RF_PAGE;
+    const int n_my = (p_hi - p_lo - rank) >= 0 ? (p_hi - p_lo - rank) / splits + 1 : 0;     // pages of this CTA
+    const int* bt = block_table + (size_t)seq_slot[tok_seq[b]] * max_pages;
+
+    if (tid == 0) {
+        gave_up = 0;
+        for (int s = 0; s < DCL_STAGES; ++s)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(dec_smem_u32(&bars[s])));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    pdl_wait();                                         // queries and the newest keys/values come from the kernel before us
+
+    auto issue = [&](int k) {                           // thread 0: page p_lo + rank + k*splits into stage k % stages
+        const int stage = k % DCL_STAGES;
+        const uint32_t bar = dec_smem_u32(&bars[stage]);
+        const int page = bt[p_lo + rank + k * splits];
+        const size_t off = ((size_t)page * nkv + kvh) * RF_PAGE * HD;
+        __nv_bfloat16* dst = ring + (size_t)stage * 2 * RF_PAGE * HD;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(2 * SLAB) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     ::"r"(dec_smem_u32(dst)), "l"(k_pages + off), "r"(SLAB), "r"(bar) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     ::"r"(dec_smem_u32(dst + RF_PAGE * HD)), "l"(v_pages + off), "r"(SLAB), "r"(bar) : "memory");
+    };
+    if (tid == 0)
+        for (int k = 0; k < n_my && k < DCL_STAGES - 1; ++k) issue(k);
+
+    uint32_t qa[HD / 16][2];
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+        qa[ks][0] = qa[ks][1] = 0u;
+        if (gid < G) {
+            const __nv_bfloat16* qrow = q + (size_t)b * q_stride + (size_t)(kvh * G + gid) * HD + ks * 16 + tig * 2;
+            qa[ks][0] = *reinterpret_cast<const uint32_t*>(qrow);
+            qa[ks][1] = *reinterpret_cast<const uint32_t*>(qrow + 8);
+        }
+    }
+    float oc[HD / 8][2];                                 // this thread: head gid, dims nt*8 + tig*2 + {0,1}
+#pragma unroll
+    for (int nt = 0; nt < HD / 8; ++nt) oc[nt][0] = oc[nt][1] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;
+
+    for (int k = 0; k < n_my; ++k) {
+        const int stage = k % DCL_STAGES;
+        if (tid == 0 && k + DCL_STAGES - 1 < n_my) issue(k + DCL_STAGES - 1);      // its stage was released by the last sync
+        {
+            const uint32_t bar = dec_smem_u32(&bars[stage]);
+            const uint32_t parity = (k / DCL_STAGES) & 1;
+            uint32_t ok = 0;
+            unsigned long long t0 = 0;
+            for (long long it = 0; !ok; ++it) {
+                asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                             "selp.u32 %0, 1, 0, p;\n\t}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+                if (ok) break;
+                if ((it & 63) == 63) {
+                    unsigned long long now;
+                    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+                    if (t0 == 0) t0 = now;
+                    if (now - t0 > DEC_WAIT_LIMIT_NS || gave_up) { gave_up = 1; break; }
+                }
+            }
+        }
+        __syncthreads();                                 // one verdict for everyone
+        if (gave_up) break;
+        const __nv_bfloat16* k_s = ring + (size_t)stage * 2 * RF_PAGE * HD;
+        __nv_bfloat16* v_s = ring + (size_t)stage * 2 * RF_PAGE * HD + RF_PAGE * HD;
+        const int key0 = (p_lo + rank + k * splits) * RF_PAGE;
+        int k_begin = lo - key0; if (k_begin < 0) k_begin = 0;                    // valid rows of this page
+        int k_last = pos - key0; if (k_last > RF_PAGE - 1) k_last = RF_PAGE - 1;
+        if (k_begin > 0 || k_last < RF_PAGE - 1) {
+            // rows outside the sequence get weight zero, but 0 * (whatever bits lie there) must be 0
+            for (int i = tid; i < RF_PAGE * (HD / 8); i += DEC_THREADS) {
+                const int row = i / (HD / 8);
+                if (row < k_begin || row > k_last) reinterpret_cast<uint4*>(v_s)[i] = make_uint4(0u, 0u, 0u, 0u);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncthreads();
+        }
+        // ---- scores of this warp's 16 keys: two tiles of 8
+        const int kb = warp * 16;
+        float sc[2][4];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+        const bool warp_active = kb <= k_last && kb + 15 >= k_begin;
+        if (warp_active) {
+#pragma unroll
+            for (int ks = 0; ks < HD / 16; ++ks)
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt) {
+                    const __nv_bfloat16* kr = k_s + (kb + nt * 8 + gid) * HD + ks * 16 + tig * 2;
+                    const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kr);
+                    const uint32_t b1 = *reinterpret_cast<const uint32_t*>(kr + 8);
+                    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                                 : "+f"(sc[nt][0]), "+f"(sc[nt][1]), "+f"(sc[nt][2]), "+f"(sc[nt][3])
+                                 : "r"(qa[ks][0]), "r"(0u), "r"(qa[ks][1]), "r"(0u), "r"(b0), "r"(b1));
+                }
+        }
+        float mx = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int kk = kb + nt * 8 + tig * 2 + e;
+                const bool ok = warp_active && kk >= k_begin && kk <= k_last;
+                sc[nt][e] = ok ? sc[nt][e] * scale : -INFINITY;
+                mx = fmaxf(mx, sc[nt][e]);
+            }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run, mx);
+        const float corr = (m_run == -INFINITY) ? 0.f : expf(m_run - m_new);
+        float psum = 0.f;
+        uint32_t pa[2];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            const float p0 = sc[nt][0] == -INFINITY ? 0.f : expf(sc[nt][0] - m_new);
+            const float p1 = sc[nt][1] == -INFINITY ? 0.f : expf(sc[nt][1] - m_new);
+            psum += p0 + p1;
+            const __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+            pa[nt] = *reinterpret_cast<const uint32_t*>(&pk);
+        }
+        psum += __shfl_xor_sync(0xffffffffu, psum, 1);
+        psum += __shfl_xor_sync(0xffffffffu, psum, 2);
+        l_run = l_run * corr + psum;
+        m_run = m_new;
+#pragma unroll
+        for (int nt = 0; nt < HD / 8; ++nt) { oc[nt][0] *= corr; oc[nt][1] *= corr; }
+        if (warp_active) {
+#pragma unroll
+            for (int nt = 0; nt < HD / 8; nt += 2) {
+                const int mi = lane >> 3, r = lane & 7;
+                const __nv_bfloat16* vr = v_s + (kb + (mi & 1) * 8 + r) * HD + (nt + (mi >> 1)) * 8;
+                uint32_t v0, v1, v2, v3;
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3) : "r"(dec_smem_u32(vr)));
+                float d0[4] = {oc[nt][0], oc[nt][1], 0.f, 0.f}, d1[4] = {oc[nt + 1][0], oc[nt + 1][1], 0.f, 0.f};
+                asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                             : "+f"(d0[0]), "+f"(d0[1]), "+f"(d0[2]), "+f"(d0[3])
+                             : "r"(pa[0]), "r"(0u), "r"(pa[1]), "r"(0u), "r"(v0), "r"(v1));
+                asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                             : "+f"(d1[0]), "+f"(d1[1]), "+f"(d1[2]), "+f"(d1[3])
+                             : "r"(pa[0]), "r"(0u), "r"(pa[1]), "r"(0u), "r"(v2), "r"(v3));
+                oc[nt][0] = d0[0]; oc[nt][1] = d0[1]; oc[nt + 1][0] = d1[0]; oc[nt + 1][1] = d1[1];
+            }
+        }
+        __syncthreads();                                 // the stage may be refilled
+    }
+
+    // ---- the four warps' states -> this CTA's state
+    if (tig == 0) { w_m[warp * DEC_GP + gid] = m_run; w_l[warp * DEC_GP + gid] = l_run; }
+#pragma unroll
+    for (int nt = 0; nt < HD / 8; ++nt) {
+        w_o[(warp * DEC_GP + gid) * HD + nt * 8 + tig * 2] = oc[nt][0];
+        w_o[(warp * DEC_GP + gid) * HD + nt * 8 + tig * 2 + 1] = oc[nt][1];
+    }
+    __syncthreads();
+    for (int i = tid; i < DEC_GP * HD; i += DEC_THREADS) {
+        const int g = i / HD, d = i - g * HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, w_m[w * DEC_GP + g]);
+        float L = 0.f, O = 0.f;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) {            // warps in index order
+            const float mw = w_m[w * DEC_GP + g];
+            const float f = mw == -INFINITY ? 0.f : expf(mw - M);
+            L += f * w_l[w * DEC_GP + g];
+            O += f * w_o[(w * DEC_GP + g) * HD + d];
+        }
+        c_o[g * HD + d] = O;
+        if (d == 0) { c_m[g] = M; c_l[g] = L; }
+    }
+    __syncthreads();
+    if (splits > 1) dcl_cluster_sync();                  // every CTA's state is complete and visible in the cluster
+    if (rank == 0 && !gave_up) {
+        // Bring the peers' states (max | sum | output, contiguous) into this CTA's memory first: batches of
+        // independent 16-byte remote loads, so that their latencies overlap instead of adding up.
+        constexpr int STATE4 = (2 * DEC_GP + DEC_GP * HD) / 4;            // float4 per CTA state
+        float4* stage = reinterpret_cast<float4*>(dec_smem);                // [splits - 1][STATE4], over the ring
+        const int total = (splits - 1) * STATE4;
+        for (int i0 = tid; i0 < total; i0 += DEC_THREADS * 4) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + u * DEC_THREADS;
+                if (i < total) {
+                    const int r = 1 + i / STATE4, j = i - (r - 1) * STATE4;
+                    uint32_t raddr;
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr) : "r"(dec_smem_u32(c_m) + 16 * j), "r"(r));
+                    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                 : "=f"(v[u].x), "=f"(v[u].y), "=f"(v[u].z), "=f"(v[u].w) : "r"(raddr) : "memory");
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + u * DEC_THREADS;
+                if (i < total) stage[i] = v[u];
+            }
+        }
+        __syncthreads();
+        const float* st = reinterpret_cast<const float*>(stage);
+        for (int i = tid; i < G * HD; i += DEC_THREADS) {
+            const int g = i / HD, d = i - g * HD;
+            float M = c_m[g];
+            for (int r = 1; r < splits; ++r) M = fmaxf(M, st[(r - 1) * STATE4 * 4 + g]);
+            float L = 0.f, O = 0.f;
+            for (int r = 0; r < splits; ++r) {           // CTAs in rank order
+                const float* base = st + (r - 1) * STATE4 * 4;
+                const float mr = r ? base[g] : c_m[g];
+                const float f = mr == -INFINITY ? 0.f : expf(mr - M);
+                L += f * (r ? base[DEC_GP + g] : c_l[g]);
+                O += f * (r ? base[2 * DEC_GP + g * HD + d] : c_o[g * HD + d]);
+            }
+            out[(size_t)b * out_stride + (size_t)(kvh * G + g) * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+        }
+    }
+    if (splits > 1) dcl_cluster_sync();                  // peers stay until their state has been read
+    if (gave_up && tid == 0 && status) atomicExch(status, 5);
+}
+
+template <int EPL>
+static int launch_cluster(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                          const void* v_pages, const int* tok_seq, const int* tok_pos, const int* seq_slot,
+                          const int* block_table, int max_pages, int nh, int nkv, float scale, int window, int B,
+                          int splits, int* status, cudaStream_t st) {
+    constexpr int HD = EPL * 32;
+    const size_t smem = (size_t)DCL_STAGES * 2 * RF_PAGE * HD * 2 +
+                        (size_t)(2 * DEC_GP + DEC_GP * HD) * sizeof(float) + DCL_STAGES * 8 + 16;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_cluster_kernel<EPL>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(splits, nkv, B);
+    cfg.blockDim = dim3(DEC_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (splits > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = splits; attr[n].val.clusterDim.y = 1; attr[n].val.clusterDim.z = 1;
+        ++n;
+    }
+    if (g_rf_pdl) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, attention_decode_cluster_kernel<EPL>,
+        reinterpret_cast<const __nv_bfloat16*>(q), q_stride, reinterpret_cast<__nv_bfloat16*>(out), out_stride,
+        reinterpret_cast<const __nv_bfloat16*>(k_pages), reinterpret_cast<const __nv_bfloat16*>(v_pages), tok_seq,
+        tok_pos, seq_slot, block_table, max_pages, nh, nkv, scale, window, splits, status);
+    if (e != cudaSuccess) return (int)e;
+    RF_LAUNCH_CHECK();
+    return 0;
+}
+
 template <int EPL>
 static int launch(const void* q, int q_stride, void* out, int out_stride, const void* k_pages, const void* v_pages,
                   const int* tok_seq, const int* tok_pos, const int* seq_slot, const int* block_table,
@@ -324,6 +646,23 @@ void rf_attention_decode_scratch(int B, int nh, int nkv, int hd, int max_chunks,
     *n_part_o = (long long)B * nh * max_chunks * hd;
     *n_part_ml = (long long)B * nh * max_chunks * 2;
     *n_counters = (long long)B * nkv;
+}
+
+// The clustered variant: `splits` (1, 2, 4 or 8) CTAs share a (sequence, kv head); no scratch memory.
+int rf_attention_decode_cluster(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                                const void* v_pages, const int* tok_seq, const int* tok_pos, const int* seq_slot,
+                                const int* block_table, int max_pages, int nh, int nkv, int hd, float scale,
+                                int window, int B, int splits, int* status, cudaStream_t st) {
+    if (B <= 0) return 0;
+    if (!rf_attention_decode_supported(nh, nkv, hd) || B > 65535) return RF_ERR_UNSUPPORTED;
+    if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return RF_ERR_BAD_ARG;
+    if ((reinterpret_cast<uintptr_t>(q) & 15) || (q_stride * 2) % 16) return RF_ERR_BAD_ARG;
+#define GOC(EPL) return launch_cluster<EPL>(q, q_stride, out, out_stride, k_pages, v_pages, tok_seq, tok_pos, seq_slot, \
+                                            block_table, max_pages, nh, nkv, scale, window, B, splits, status, st)
+    if (hd == 64) GOC(2);
+    if (hd == 128) GOC(4);
+    GOC(8);
+#undef GOC
 }
 
 int rf_attention_decode(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,

@@ -27,6 +27,9 @@ class Options:
 class StepContext:
     """Device arrays of the batch and the kernel dispatch for one step."""
 
+    WALK_DECODE_MIN_PAIRS = 128        # batch * kv heads from which one CTA per pair fills the GPU
+    WALK_DECODE_LIMIT = 4096           # keys a single CTA walks page by page before chunking pays again
+
     def __init__(self, model, views, *, T: int, B: int, R: int, is_decode: bool, max_new: int, max_end: int,
                  host=None):
         self.model = model
@@ -122,22 +125,30 @@ class StepContext:
         nh, nkv, hd = mixer.n_heads, mixer.n_kv_heads, mixer.head_dim
         longest = self.model_cache_limit if self.replayed else self.max_end
         if (self.is_decode and self.compute_dtype == torch.bfloat16 and self.options.tuned_attention
-                and kernels.attention_decode_supported(nh, nkv, hd)
-                and longest <= kernels.DECODE_CHUNK * kernels.DECODE_CHUNK):
-            need = max(1, (longest + kernels.DECODE_CHUNK - 1) // kernels.DECODE_CHUNK)
-            max_chunks = 1
-            while max_chunks < need:                   # powers of two: few distinct scratch sizes
-                max_chunks *= 2
-            cap = 1
-            while cap < self.B:
-                cap *= 2
-            n_o, n_ml, n_c = kernels.attention_decode_scratch(cap, nh, nkv, hd, max_chunks)
-            scratch = self.model.scratch
-            return kernels.attention_decode(
-                q, nh, nkv, hd, view.k_pages, view.v_pages, self.tok_seq, self.tok_pos, self.seq_slot,
-                view.block_table, mixer.scale, view.window, max_chunks,
-                scratch("attn_decode_o", n_o, torch.float32), scratch("attn_decode_ml", n_ml, torch.float32),
-                scratch("attn_decode_counters", n_c, torch.int32))
+                and kernels.attention_decode_supported(nh, nkv, hd)):
+            if self.B * nkv >= self.WALK_DECODE_MIN_PAIRS and longest <= self.WALK_DECODE_LIMIT:
+                # many (sequence, kv head) pairs: one CTA each walks the whole context, nothing to merge
+                # (measured at 7B shape, batch 64: 10 % faster per step than the chunked kernel below;
+                # clusters of 2..8 CTAs merging through distributed shared memory were not faster at any batch)
+                return kernels.attention_decode_cluster(q, nh, nkv, hd, view.k_pages, view.v_pages, self.tok_seq,
+                                                        self.tok_pos, self.seq_slot, view.block_table, mixer.scale,
+                                                        view.window, splits=1)
+            if longest <= kernels.DECODE_CHUNK * kernels.DECODE_CHUNK:
+                # long contexts: one CTA per 128-key chunk, partial results merged through scratch memory
+                need = max(1, (longest + kernels.DECODE_CHUNK - 1) // kernels.DECODE_CHUNK)
+                max_chunks = 1
+                while max_chunks < need:                   # powers of two: few distinct scratch sizes
+                    max_chunks *= 2
+                cap = 1
+                while cap < self.B:
+                    cap *= 2
+                n_o, n_ml, n_c = kernels.attention_decode_scratch(cap, nh, nkv, hd, max_chunks)
+                scratch = self.model.scratch
+                return kernels.attention_decode(
+                    q, nh, nkv, hd, view.k_pages, view.v_pages, self.tok_seq, self.tok_pos, self.seq_slot,
+                    view.block_table, mixer.scale, view.window, max_chunks,
+                    scratch("attn_decode_o", n_o, torch.float32), scratch("attn_decode_ml", n_ml, torch.float32),
+                    scratch("attn_decode_counters", n_c, torch.int32))
         if (not self.is_decode and self.compute_dtype == torch.bfloat16 and self.options.tuned_attention
                 and self.q_tiles.numel() > 0 and kernels.attention_prefill_supported(nh, nkv, hd)
                 and q.data_ptr() % 4 == 0 and q.stride(0) % 2 == 0):

@@ -32,20 +32,30 @@ class DecodeRunner:
         self.cache = cache
         self.desc = DeviceDescriptor(model.device, capacity=StepBatch.layout(max_batch, max_batch, max_batch)[1])
         self.max_batch = max_batch
-        self.graphs: Dict[int, _Captured] = {}
+        self.graphs: Dict[tuple, _Captured] = {}
         from ..sampling import DeviceSampler
         self.sampler = DeviceSampler(model.device)
         self.replays = 0
 
-    def _context(self, B: int) -> StepContext:
+    @staticmethod
+    def length_bucket(longest: int) -> int:
+        """Sequence-length bound a graph is captured for: the next power of two (at least 512).  Kernels
+        whose launch shape grows with the context get this bound, so a graph serves until a sequence
+        outgrows it; then the next bucket's graph is captured."""
+        b = 512
+        while b < longest:
+            b *= 2
+        return b
+
+    def _context(self, B: int, bound: int) -> StepContext:
         views = self.desc.views(B, B, B)
         ctx = StepContext(self.model, views, T=B, B=B, R=B, is_decode=True, max_new=1,
-                          max_end=self.cache.max_seq_len)
+                          max_end=min(bound, self.cache.max_seq_len))
         ctx.replayed = True          # launch shapes must not depend on this step's lengths
         return ctx
 
-    def _capture(self, B: int) -> _Captured:
-        ctx = self._context(B)
+    def _capture(self, B: int, bound: int) -> _Captured:
+        ctx = self._context(B, bound)
         side = torch.cuda.Stream(device=self.model.device)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
@@ -66,9 +76,10 @@ class DecodeRunner:
         batch = StepBatch(requests, starts, self.model.spec.vocab_size)
         self.cache.prepare(slots, [1] * B)
         self.desc.upload(batch.pack())
-        cap = self.graphs.get(B)
+        key = (B, self.length_bucket(max(starts) + 1))
+        cap = self.graphs.get(key)
         if cap is None:
-            cap = self.graphs[B] = self._capture(B)
+            cap = self.graphs[key] = self._capture(B, key[1])
         cap.graph.replay()
         self.replays += 1
         self.cache.commit(slots, [1] * B)
@@ -88,11 +99,12 @@ class DecodeRunner:
         requests = [StepRequest(s, [int(t)], [0]) for s, t in zip(slots, tokens)]
         batch = StepBatch(requests, [self.cache.length(s) for s in slots], self.model.spec.vocab_size)
         self.desc.upload(batch.pack())
-        key = ("loop", B)
+        bound = self.length_bucket(max(self.cache.length(s) for s in slots) + steps)
+        key = ("loop", B, bound)
         out = torch.empty((steps, B), dtype=torch.int32, device=self.model.device)
         cap = self.graphs.get(key)
         if cap is None:
-            ctx = self._context(B)
+            ctx = self._context(B, bound)
             sampled = torch.zeros((B,), dtype=torch.int32, device=self.model.device)
             side = torch.cuda.Stream(device=self.model.device)
             side.wait_stream(torch.cuda.current_stream())

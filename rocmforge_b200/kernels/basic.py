@@ -317,3 +317,42 @@ def attention_prefill(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: 
             ptr(status_word(q.device)), stream()),
           f"attention_prefill (heads={n_heads}, kv_heads={n_kv_heads}, head_dim={head_dim})")
     return out
+
+
+def decode_splits(B: int, n_kv_heads: int, sm_count: int = 148) -> int:
+    """CTAs that share one (sequence, kv head) in the clustered decode attention: from the batch alone
+    (a captured graph keeps its launch shape), aiming at two CTAs per SM, at most 8 (a portable cluster)."""
+    pairs = max(1, B * n_kv_heads)
+    s = 1
+    while s < 8 and pairs * s < 2 * sm_count:
+        s *= 2
+    return s
+
+
+def attention_decode_cluster(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, k_pages, v_pages,
+                             tok_seq, tok_pos, seq_slot, block_table, scale: float, window: int | None,
+                             splits: int | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """One new token per sequence over the bfloat16 paged cache; the CTAs of a (sequence, kv head) form a
+    cluster and merge through distributed shared memory (no scratch memory)."""
+    need_cuda(q, k_pages, v_pages, tok_seq, tok_pos, seq_slot, block_table)
+    B = q.shape[0]
+    need(q.dtype == torch.bfloat16 and q.dim() == 2 and q.stride(1) == 1, "attention_decode: q must be bfloat16 [B, ...]")
+    need(k_pages.dtype == torch.bfloat16 and tuple(k_pages.shape[1:]) == (n_kv_heads, PAGE, head_dim)
+         and k_pages.is_contiguous() and v_pages.shape == k_pages.shape and v_pages.is_contiguous(),
+         "attention_decode: bad cache page shape or dtype")
+    need(attention_decode_supported(n_heads, n_kv_heads, head_dim),
+         f"attention_decode: heads={n_heads}, kv_heads={n_kv_heads}, head_dim={head_dim} is not supported")
+    need(q.data_ptr() % 16 == 0 and (q.stride(0) * 2) % 16 == 0, "attention_decode: q rows must be 16-byte aligned")
+    if splits is None:
+        splits = decode_splits(B, n_kv_heads)
+    if out is None:
+        out = torch.empty((B, n_heads * head_dim), dtype=torch.bfloat16, device=q.device)
+    from .tensor_core import status_word
+    f = _f("attention_decode", "rf_attention_decode_cluster", c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+           c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p,
+           c_void_p)
+    check(f(ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(k_pages), ptr(v_pages), ptr(tok_seq), ptr(tok_pos),
+            ptr(seq_slot), ptr(block_table), block_table.shape[1], n_heads, n_kv_heads, head_dim, float(scale),
+            int(window or 0), B, splits, ptr(status_word(q.device)), stream()),
+          f"attention_decode_cluster (heads={n_heads}, kv_heads={n_kv_heads}, head_dim={head_dim}, splits={splits})")
+    return out

@@ -263,6 +263,14 @@ def test_attention_decode(nh, nkv, hd, window):
     gen = kernels.attention_generic(q.to(DEV), nh, nkv, hd, k_pages, v_pages, tok_seq, tok_pos, seq_slot, table,
                                     scale, window)
     torch.testing.assert_close(out.float(), gen.float(), atol=2e-2, rtol=2e-2)
+    # the clustered variant: every cluster size, the same answers
+    for splits in (1, 2, 4, 8):
+        out = kernels.attention_decode_cluster(q.to(DEV), nh, nkv, hd, k_pages, v_pages, tok_seq, tok_pos, seq_slot,
+                                               table, scale, window, splits=splits)
+        assert torch.isfinite(out.float()).all()
+        for b in range(B):
+            torch.testing.assert_close(out[b].cpu().double().view(nh, hd), refs[b], atol=2e-2, rtol=2e-2)
+    assert kernels.decode_splits(1, 4) == 8 and kernels.decode_splits(64, 4) == 2 and kernels.decode_splits(512, 8) == 1
 
 
 def test_attention_decode_finds_far_keys_and_the_window_edge():
@@ -274,16 +282,25 @@ def test_attention_decode_finds_far_keys_and_the_window_edge():
     n_o, n_ml, n_c = kernels.attention_decode_scratch(1, nh, nkv, hd, 8)
     scratch = (torch.zeros(n_o, device=DEV), torch.zeros(n_ml, device=DEV), torch.zeros(n_c, dtype=torch.int32, device=DEV))
 
+    which = {"kernel": "chunked"}
+
     def run(t0, t1, window):
         kp = k_pages.clone()
         for dim, t in ((0, t0), (1, t1)):
             page = int(table[1, t // 64])
             kp[page, 0, t % 64, dim] = 60.0
-        return kernels.attention_decode(q.to(dt).to(DEV), nh, nkv, hd, kp, v_pages, zero,
-                                        torch.tensor([n - 1], dtype=torch.int32, device=DEV),
-                                        torch.tensor([1], dtype=torch.int32, device=DEV), table, 1.0 / math.sqrt(hd),
-                                        window, 8, *scratch)[0].float().cpu().view(nh, hd)
+        args = (q.to(dt).to(DEV), nh, nkv, hd, kp, v_pages, zero, torch.tensor([n - 1], dtype=torch.int32, device=DEV),
+                torch.tensor([1], dtype=torch.int32, device=DEV), table, 1.0 / math.sqrt(hd), window)
+        if which["kernel"] == "chunked":
+            return kernels.attention_decode(*args, 8, *scratch)[0].float().cpu().view(nh, hd)
+        return kernels.attention_decode_cluster(*args, splits=4)[0].float().cpu().view(nh, hd)
 
+    for kernel in ("chunked", "clustered"):
+        which["kernel"] = kernel
+        check_far_keys(run, vs)
+
+
+def check_far_keys(run, vs):
     for t0, t1 in ((0, 899), (127, 128), (511, 512), (63, 64), (700, 3), (895, 896)):
         out = run(t0, t1, None)
         torch.testing.assert_close(out[0], vs[0][t0, 0].float(), atol=2e-2, rtol=2e-2)
