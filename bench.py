@@ -212,6 +212,8 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (quick check)")
+    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
+                    help="run one phase only and print a short line (small cases for profilers)")
     ap.add_argument("--seed", type=int, default=0)
     args = ap.parse_args()
     if args.impl == "reference":
@@ -233,6 +235,15 @@ def main():
     model = rf.Model.random(cfg, seed=args.seed, dtype=torch.bfloat16)
     llm = rf.LLM(model, cache_tokens=args.batch * (PROMPT_LEN + args.steps + 80), max_batch=args.batch)
 
+    if args.only == "decode":
+        r = decode_rate(model, args.batch, args.steps, warmup, args.seed)
+        print(json.dumps({"only": "decode", "layers": cfg.num_hidden_layers, "batch": args.batch,
+                          "ms_per_step": round(r["ms_per_step"], 4), "tok_s": round(r["tok_s"], 1)}))
+        return 0
+    if args.only == "prefill":
+        ms = prefill_rate(model, PREFILL_TOKENS, 2, args.seed + 2)
+        print(json.dumps({"only": "prefill", "layers": cfg.num_hidden_layers, "tokens": PREFILL_TOKENS, "ms": round(ms, 3)}))
+        return 0
     sampler = ClockSampler()
     sampler.start()
     main_run = decode_rate(model, args.batch, args.steps, warmup, args.seed)
