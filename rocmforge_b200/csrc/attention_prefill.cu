@@ -34,6 +34,14 @@ __device__ __forceinline__ void pf_mma(float* c, const uint32_t* a, uint32_t b0,
 
 // Address of the 16-byte chunk `chunk` (0..7) of row `row` in a [64 rows x 128 bytes] tile written by TMA
 // with the 128-byte swizzle (the tile starts on a 1024-byte boundary).
+// 2^x on the special-function unit (32-bit, relative error about 2^-22): the softmax weights are
+// rounded to bfloat16 right after, and their sum is formed from the same values
+__device__ __forceinline__ float pf_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __device__ __forceinline__ uint32_t pf_swz(uint32_t tile, int row, int chunk) {
     return tile + row * 128 + ((chunk ^ (row & 7)) << 4);
 }
@@ -178,33 +186,48 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
                 }
             }
         }
-        // ---- mask, running maximum, weights (32-bit)
+        // ---- mask, running maximum, weights (32-bit; scores in units of log2 e so that exp is one ex2)
+        const float sl2 = scale * 1.4426950408889634f;
+        // a page wholly inside every row's range of this warp (below the diagonal, inside the window) needs no mask
+        const bool no_mask = warp_needed && key0 + RF_PAGE - 1 <= pos_first + warp * 16 && warp * 16 + 15 < rows_here &&
+                             (window <= 0 || key0 >= pos_first + warp * 16 + 15 - window + 1);
         float mx0 = -INFINITY, mx1 = -INFINITY;
+        if (no_mask) {
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt)
+            for (int nt = 0; nt < 8; ++nt) {
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int j = key0 + nt * 8 + tig * 2 + e;
-                const bool ok0 = warp_needed && j <= pos0 && j >= lo0 && r0 < rows_here;
-                const bool ok1 = warp_needed && j <= pos1 && j >= lo1 && r1 < rows_here;
-                sc[nt][e] = ok0 ? sc[nt][e] * scale : -INFINITY;
-                sc[nt][2 + e] = ok1 ? sc[nt][2 + e] * scale : -INFINITY;
-                mx0 = fmaxf(mx0, sc[nt][e]);
-                mx1 = fmaxf(mx1, sc[nt][2 + e]);
+                for (int e = 0; e < 4; ++e) sc[nt][e] *= sl2;
+                mx0 = fmaxf(mx0, fmaxf(sc[nt][0], sc[nt][1]));
+                mx1 = fmaxf(mx1, fmaxf(sc[nt][2], sc[nt][3]));
             }
+        } else {
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int j = key0 + nt * 8 + tig * 2 + e;
+                    const bool ok0 = warp_needed && j <= pos0 && j >= lo0 && r0 < rows_here;
+                    const bool ok1 = warp_needed && j <= pos1 && j >= lo1 && r1 < rows_here;
+                    sc[nt][e] = ok0 ? sc[nt][e] * sl2 : -INFINITY;
+                    sc[nt][2 + e] = ok1 ? sc[nt][2 + e] * sl2 : -INFINITY;
+                    mx0 = fmaxf(mx0, sc[nt][e]);
+                    mx1 = fmaxf(mx1, sc[nt][2 + e]);
+                }
+        }
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
         const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
-        const float cr0 = (m0 == -INFINITY) ? 0.f : expf(m0 - mn0), cr1 = (m1 == -INFINITY) ? 0.f : expf(m1 - mn1);
+        // ex2(-inf) = 0 covers masked scores and the first page; a row that has seen no key yet keeps mn = -inf,
+        // where (-inf) - (-inf) would be NaN: such rows use 0 as the reference instead
+        const float ref0 = mn0 == -INFINITY ? 0.f : mn0, ref1 = mn1 == -INFINITY ? 0.f : mn1;
+        const float cr0 = pf_exp2(m0 - ref0), cr1 = pf_exp2(m1 - ref1);
         m0 = mn0; m1 = mn1;
         float s0 = 0.f, s1 = 0.f;
         uint32_t pa[4][4];                               // P as A fragments: 4 steps of 16 keys
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt) {
-            const float p00 = sc[nt][0] == -INFINITY ? 0.f : expf(sc[nt][0] - mn0);
-            const float p01 = sc[nt][1] == -INFINITY ? 0.f : expf(sc[nt][1] - mn0);
-            const float p10 = sc[nt][2] == -INFINITY ? 0.f : expf(sc[nt][2] - mn1);
-            const float p11 = sc[nt][3] == -INFINITY ? 0.f : expf(sc[nt][3] - mn1);
+            const float p00 = pf_exp2(sc[nt][0] - ref0), p01 = pf_exp2(sc[nt][1] - ref0);
+            const float p10 = pf_exp2(sc[nt][2] - ref1), p11 = pf_exp2(sc[nt][3] - ref1);
             s0 += p00 + p01; s1 += p10 + p11;
             const __nv_bfloat162 x = __floats2bfloat162_rn(p00, p01), y = __floats2bfloat162_rn(p10, p11);
             pa[nt >> 1][(nt & 1) * 2] = *reinterpret_cast<const uint32_t*>(&x);

@@ -211,8 +211,11 @@ static int launch_add_rmsnorm(float* h, const void* pending, int kind, int n_pen
     if (H % 4 == 0 && H <= 4 * 4 * 1024 && (pstride % 4) == 0 &&
         !(reinterpret_cast<uintptr_t>(h) & 15) && !(kind == 1 && (reinterpret_cast<uintptr_t>(pending) & 15))) {
         const int nvec = H / 4;
-        int threads = ((nvec + 31) / 32) * 32;            // one 16-byte vector per thread where the row allows
+        // few rows (decode): one 16-byte vector per thread, the shortest chain per row;
+        // many rows (prompts): 256 threads a row, so that eight rows per SM are in flight
+        int threads = ((nvec + 31) / 32) * 32;
         if (threads > 1024) threads = 1024;
+        if (n_rows >= 512 && nvec > 256 && nvec <= 1024) threads = 256;
         const int per = (nvec + threads - 1) / threads;
         T* yy = reinterpret_cast<T*>(y);
         if (per <= 1) rf_launch(add_rmsnorm_vec_kernel<T, 1>, dim3(n_rows), dim3(threads), 0, st, h, pending, kind, n_pending, pstride, w, w_is_f32, eps, yy, rows, H);

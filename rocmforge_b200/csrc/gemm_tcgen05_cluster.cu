@@ -14,6 +14,11 @@
 //   * The accumulator has two buffers in tensor memory (2 x 256 columns): while the four epilogue
 //     warps drain tile i, the MMA thread is already accumulating tile i + 1, and the TMA ring runs
 //     ahead across tile borders.
+//   * The epilogue leaves through shared memory and TMA: a thread owns one output row, so direct stores
+//     would scatter 16-byte pieces over 32 rows per instruction; instead the four epilogue warps write a
+//     128-row x 128-byte slab into a swizzled staging buffer (two of them, alternating) and one thread
+//     hands it to TMA, which writes full lines, clips at the matrix edge, and for the residual epilogue
+//     ADDS in L2 (cp.reduce.async.bulk .add.f32), so the 32-bit stream is never read back into the SM.
 // A stage of a CTA's ring is written by its own loads and by its peers' multicasts, so it may be
 // refilled only when every CTA of the cluster has finished reading it: the "empty" barrier of a
 // stage counts CL arrivals, and each CTA's MMA thread signals all of them with one multicast
@@ -48,16 +53,30 @@ __device__ __forceinline__ void tcgen05_commit_multicast(uint32_t bar, uint16_t 
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
                  ::"r"(bar), "h"(mask) : "memory");
 }
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int c1, uint32_t src) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(map), "r"(c0), "r"(c1), "r"(src) : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, int c0, int c1, uint32_t src) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(map), "r"(c0), "r"(c1), "r"(src) : "memory");
+}
+__device__ __forceinline__ void epi_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }   // the 4 epilogue warps
+
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
 // grid.x = n_clusters * CL (cluster dimension CL along x).  Work item w -> row group w % groups_m,
-// column tile w / groups_m; CTA `rank` of the cluster owns row tile group * CL + rank.
+// column tile (w / groups_m) % tiles_n, K half w / (groups_m * tiles_n); CTA `rank` of the cluster owns
+// row tile group * CL + rank.  With two K halves (p.splits == 2, used when the tiles would fill the last
+// round of clusters less than two thirds) the first half ends in the requested epilogue and the second
+// half stores its 32-bit sums to p.out2, which the caller adds later in a fixed order.
 template <int CL>
 __global__ void __launch_bounds__(CG_THREADS, 1)
-gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p,
-                       int groups_m, int tiles_n) {
+gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                       const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_out2,
+                       TcParams p, int groups_m, int tiles_n) {
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2;
     constexpr uint32_t B_BYTES = CG_BN * TC_BK * 2;
     constexpr uint32_t B_PART = B_BYTES / CL;
@@ -66,7 +85,8 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * STAGE_BYTES);
+    uint8_t* staging = smem + S * STAGE_BYTES;                       // 2 x [128 rows x 128 bytes], swizzled
+    uint64_t* bars = reinterpret_cast<uint64_t*>(staging + 2 * 16384);
     // full[S], empty[S], acc_full[2], acc_empty[2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 4);
     __shared__ int abort_flag;
@@ -75,8 +95,10 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
     const int cluster_id = blockIdx.x / CL, n_clusters = gridDim.x / CL;
-    const int n_work = groups_m * tiles_n;
-    const int kb_total = (p.K + TC_BK - 1) / TC_BK;
+    const int n_tiles = groups_m * tiles_n;
+    const int n_work = n_tiles * p.splits;
+    const int kb_all = (p.K + TC_BK - 1) / TC_BK;
+    const int kb_half = p.splits == 2 ? (kb_all + 1) / 2 : kb_all;
     const uint16_t all = (uint16_t)((1u << CL) - 1);
 
     if (threadIdx.x == 0) {
@@ -108,8 +130,9 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         if (lane == 0) {
             int it = 0;                                  // running k-block count across work items
             for (int w = cluster_id; w < n_work && !abort_flag; w += n_clusters) {
-                const int tile_m = (w % groups_m) * CL + (int)rank, tile_n = w / groups_m;
-                for (int kb = 0; kb < kb_total; ++kb, ++it) {
+                const int tile_m = (w % groups_m) * CL + (int)rank, tile_n = (w / groups_m) % tiles_n;
+                const int kb0 = (w / n_tiles) * kb_half, kb1 = (w / n_tiles) ? kb_all : kb_half;
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % S;
                     if (!mbar_wait(smem_u32(&bars[S + s]), ((it / S) & 1) ^ 1, &abort_flag)) break;
                     const uint32_t full = smem_u32(&bars[s]);
@@ -131,6 +154,7 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 tcgen05_fence_after();
                 const uint32_t acc = tmem_base + buf * CG_BN;
                 bool ok = true;
+                const int kb_total = (w / n_tiles) ? kb_all - kb_half : kb_half;
                 for (int kb = 0; kb < kb_total; ++kb, ++it) {
                     const int s = it % S;
                     ok = mbar_wait(smem_u32(&bars[s]), (it / S) & 1, &abort_flag);
@@ -149,24 +173,85 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         }
     } else {
         const int quarter = warp & 3;
-        int local = 0;
+        const int row = quarter * 32 + lane;             // this thread's row of the tile
+        const bool leader = (warp == 2 && lane == 0);    // hands the slabs to TMA
+        int local = 0, slab = 0;
         for (int w = cluster_id; w < n_work; w += n_clusters, ++local) {
             const int buf = local & 1;
-            const int tile_m = (w % groups_m) * CL + (int)rank, tile_n = w / groups_m;
+            const int tile_m = (w % groups_m) * CL + (int)rank, tile_n = (w / groups_m) % tiles_n;
+            const bool second = (w / n_tiles) != 0;      // second K half: plain 32-bit store to out2
+            const int mode = second ? EPI_F32 : p.mode;
+            const CUtensorMap* omap = second ? &map_out2 : &map_out;
             if (!mbar_wait(smem_u32(&bars[2 * S + buf]), (local >> 1) & 1, &abort_flag)) break;
             tcgen05_fence_after();
-            const int m = tile_m * TC_BM + quarter * 32 + lane;
             const uint32_t taddr = tmem_base + buf * CG_BN + ((uint32_t)(quarter * 32) << 16);
+            // accumulator columns per 128-byte slab row: 32 as float, 64 as bfloat16, 128 through SwiGLU
+            const int cols_per_slab = (mode == EPI_F32 || mode == EPI_RESIDUAL) ? 32 : (mode == EPI_STORE ? 64 : 128);
 #pragma unroll 1
-            for (int c0 = 0; c0 < CG_BN; c0 += 32) {
-                uint32_t r[32];
-                tcgen05_ld32(taddr + c0, r);
-                tcgen05_wait_ld();
-                epilogue_rows<32>(p, r, m, tile_n * CG_BN + c0);
+            for (int c0 = 0; c0 < CG_BN; c0 += cols_per_slab, ++slab) {
+                uint8_t* st = staging + (slab & 1) * 16384;
+                // the slab before last used this buffer: TMA must have read it
+                if (leader) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                epi_barrier();
+                const uint32_t srow = smem_u32(st) + row * 128;
+#pragma unroll 1
+                for (int cc = 0; cc < cols_per_slab; cc += 32) {
+                    uint32_t r[32];
+                    tcgen05_ld32(taddr + c0 + cc, r);
+                    tcgen05_wait_ld();
+                    const int n0 = tile_n * CG_BN + c0 + cc;
+                    if (mode == EPI_SWIGLU) {            // 32 accumulators -> 16 bfloat16 = 2 chunks of 16 bytes
+#pragma unroll
+                        for (int h8 = 0; h8 < 2; ++h8) {
+                            uint32_t wv[4];
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                const int j = h8 * 16 + 4 * q;
+                                wv[q] = pack_bf16x2(silu_fast(__uint_as_float(r[j])) * __uint_as_float(r[j + 1]),
+                                                    silu_fast(__uint_as_float(r[j + 2])) * __uint_as_float(r[j + 3]));
+                            }
+                            const int chunk = (cc >> 4) + h8;
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(srow + ((chunk ^ (row & 7)) << 4)),
+                                         "r"(wv[0]), "r"(wv[1]), "r"(wv[2]), "r"(wv[3]) : "memory");
+                        }
+                    } else {
+                        float v[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            v[j] = __uint_as_float(r[j]);
+                            if (!second && p.bias && n0 + j < p.N) v[j] += load_vec(p.bias, p.bias_is_f32, n0 + j);
+                        }
+                        if (mode == EPI_STORE) {         // 32 accumulators -> 4 chunks of 8 bfloat16
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                const int chunk = (cc >> 3) + q;
+                                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(srow + ((chunk ^ (row & 7)) << 4)),
+                                             "r"(pack_bf16x2(v[8 * q], v[8 * q + 1])), "r"(pack_bf16x2(v[8 * q + 2], v[8 * q + 3])),
+                                             "r"(pack_bf16x2(v[8 * q + 4], v[8 * q + 5])), "r"(pack_bf16x2(v[8 * q + 6], v[8 * q + 7]))
+                                             : "memory");
+                            }
+                        } else {                         // 32 floats = the whole slab row
+#pragma unroll
+                            for (int q = 0; q < 8; ++q)
+                                asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(srow + ((q ^ (row & 7)) << 4)),
+                                             "f"(v[4 * q]), "f"(v[4 * q + 1]), "f"(v[4 * q + 2]), "f"(v[4 * q + 3]) : "memory");
+                        }
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // the slab is for TMA to read
+                epi_barrier();
+                if (leader) {
+                    // output column of the slab's first element, in elements of the output matrix
+                    const int oc0 = (mode == EPI_SWIGLU) ? (tile_n * CG_BN + c0) / 2 : tile_n * CG_BN + c0;
+                    if (mode == EPI_RESIDUAL) tma_reduce_add_2d(omap, oc0, tile_m * TC_BM, smem_u32(st));
+                    else tma_store_2d(omap, oc0, tile_m * TC_BM, smem_u32(st));
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                }
             }
             tcgen05_fence_before();
             mbar_arrive(smem_u32(&bars[2 * S + 2 + buf]));                   // 128 arrivals hand the buffer back
         }
+        if (leader) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // all output has left before the CTA ends
     }
     tcgen05_fence_before();
     __syncthreads();
@@ -178,10 +263,53 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     if (threadIdx.x == 0 && abort_flag && p.status) atomicExch(p.status, 4);
 }
 
+// Map of an output matrix [rows, cols] (bfloat16 or float32, row stride ld elements); box = 128 rows x 128 bytes.
+static int make_out_map(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, bool f32) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return RF_ERR_UNSUPPORTED;
+    const int esz = f32 ? 4 : 2;
+    if ((reinterpret_cast<uintptr_t>(base) & 15) || (ld * esz) % 16) return RF_ERR_BAD_ARG;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * esz};
+    cuuint32_t box[2] = {(cuuint32_t)(128 / esz), TC_BM};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                    const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : RF_ERR_BAD_ARG;
+}
+
+template <int CL>
+static int cluster_width() {
+    constexpr size_t smem = (size_t)CG_STAGES * (TC_BM * TC_BK * 2 + CG_BN * TC_BK * 2) + 2 * 16384 + (2 * CG_STAGES + 4) * 8 + 16 + 1024;
+    static int max_clusters = -1;
+    if (max_clusters < 0) {
+        cudaLaunchConfig_t cfg = {};
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = CL; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        cfg.blockDim = dim3(CG_THREADS);
+        cfg.dynamicSmemBytes = smem;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        cfg.gridDim = dim3(CL);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_cluster_kernel<CL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)smem);
+        if (e != cudaSuccess) return -(int)e - 100;
+        int n = 0;
+        e = cudaOccupancyMaxActiveClusters(&n, gemm_tc_cluster_kernel<CL>, &cfg);
+        if (e != cudaSuccess) return -(int)e - 100;
+        if (n <= 0) return RF_ERR_UNSUPPORTED;
+        max_clusters = n;
+    }
+    return max_clusters;
+}
+
 template <int CL>
 static int launch_cluster(const void* X, int ldx, const void* W, TcParams p, cudaStream_t st) {
-    constexpr size_t smem = (size_t)CG_STAGES * (TC_BM * TC_BK * 2 + CG_BN * TC_BK * 2) + (2 * CG_STAGES + 4) * 8 + 16 + 1024;
-    static int max_clusters = -1;
+    constexpr size_t smem = (size_t)CG_STAGES * (TC_BM * TC_BK * 2 + CG_BN * TC_BK * 2) + 2 * 16384 + (2 * CG_STAGES + 4) * 8 + 16 + 1024;
+    const int max_clusters = cluster_width<CL>();
+    if (max_clusters <= 0) return max_clusters < -100 ? -(max_clusters + 100) : RF_ERR_UNSUPPORTED;
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -193,26 +321,20 @@ static int launch_cluster(const void* X, int ldx, const void* W, TcParams p, cud
     cfg.stream = st;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (max_clusters < 0) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_cluster_kernel<CL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        cfg.gridDim = dim3(CL);
-        int n = 0;
-        e = cudaOccupancyMaxActiveClusters(&n, gemm_tc_cluster_kernel<CL>, &cfg);
-        if (e != cudaSuccess) return (int)e;
-        if (n <= 0) return RF_ERR_UNSUPPORTED;
-        max_clusters = n;
-    }
-    CUtensorMap ma, mb;
+    CUtensorMap ma, mb, mo, mo2;
     int e;
     if ((e = make_map(&ma, X, p.M, p.K, ldx, TC_BM)) || (e = make_map(&mb, W, p.N, p.K, p.K, CG_BN / CL))) return e;
+    const bool f32_out = p.mode == EPI_F32 || p.mode == EPI_RESIDUAL;
+    const long long out_cols = p.mode == EPI_SWIGLU ? p.N / 2 : p.N;
+    if ((e = make_out_map(&mo, p.out, p.M, out_cols, p.ldo, f32_out))) return e;
+    mo2 = mo;
+    if (p.out2 && (e = make_out_map(&mo2, p.out2, p.M, p.N, p.N, true))) return e;
     const int tiles_m = (p.M + TC_BM - 1) / TC_BM, groups_m = (tiles_m + CL - 1) / CL, tiles_n = (p.N + CG_BN - 1) / CG_BN;
-    int n_clusters = groups_m * tiles_n;
+    int n_clusters = groups_m * tiles_n * p.splits;
     if (n_clusters > max_clusters) n_clusters = max_clusters;
     cfg.gridDim = dim3(n_clusters * CL);
     cfg.numAttrs = g_rf_pdl ? 2 : 1;
-    cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_tc_cluster_kernel<CL>, ma, mb, p, groups_m, tiles_n);
+    cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_tc_cluster_kernel<CL>, ma, mb, mo, mo2, p, groups_m, tiles_n);
     if (le != cudaSuccess) return (int)le;
     RF_LAUNCH_CHECK();
     return 0;
@@ -224,16 +346,28 @@ int rf_gemm_tc_cluster_supported(int M, int N, int K, int mode) {
     if (M < 2 * TC_BM || N < CG_BN || K <= 0 || K % 8) return 0;
     if (mode == EPI_SWIGLU && (N % 2)) return 0;
     if (mode == EPI_PARTIAL) return 0;
+    const int out_cols = mode == EPI_SWIGLU ? N / 2 : N;
+    if (out_cols % 8) return 0;                      // TMA stores need 16-byte row strides
     return encode_fn() != nullptr;
 }
 
 // Same contract as rf_gemm_tc (tokens as rows), for M >= 256 and N >= 256.  cluster = 2 or 4 CTAs along M.
+// How many clusters of `cluster` CTAs run at once (what the persistent grid is sized to), or a negative code.
+int rf_gemm_tc_cluster_width(int cluster);
+
 int rf_gemm_tc_cluster(const void* X, int ldx, const void* W, const void* bias, int bias_is_f32, void* out, int ldo,
-                       int M, int N, int K, int mode, int cluster, int* status, cudaStream_t st) {
+                       int M, int N, int K, int mode, int cluster, void* out2, int* status, cudaStream_t st) {
     if (!rf_gemm_tc_cluster_supported(M, N, K, mode)) return RF_ERR_UNSUPPORTED;
-    TcParams p{out, bias, bias_is_f32, M, N, K, ldo, mode, (K + TC_BK - 1) / TC_BK, 0, status};
+    if (out2 && (K + TC_BK - 1) / TC_BK < 2) return RF_ERR_BAD_ARG;
+    TcParams p{out, bias, bias_is_f32, M, N, K, ldo, mode, (K + TC_BK - 1) / TC_BK, 0, status, out2, out2 ? 2 : 1};
     if (cluster == 2) return launch_cluster<2>(X, ldx, W, p, st);
     if (cluster == 4) return launch_cluster<4>(X, ldx, W, p, st);
+    return RF_ERR_BAD_ARG;
+}
+
+int rf_gemm_tc_cluster_width(int cluster) {
+    if (cluster == 2) return cluster_width<2>();
+    if (cluster == 4) return cluster_width<4>();
     return RF_ERR_BAD_ARG;
 }
 
