@@ -27,7 +27,18 @@ TINY_C = dict(   # as many kv heads as heads, head_dim given and != hidden/heads
     num_key_value_heads=5, head_dim=48, intermediate_size=112, vocab_size=300, rope_theta=50000.0,
     rms_norm_eps=3e-6, tie_word_embeddings=True, max_position_embeddings=512, use_sliding_window=True,
     sliding_window=24, max_window_layers=2, eos_token_id=[3, 5])
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+# Two more whose head sizes (64, 128) and widths let the bfloat16 engine take its tuned kernels (tcgen05 products
+# of every orientation, tiled prefill attention, chunked decode attention) instead of the generic ones.
+TINY_D = dict(   # head_dim 64, 2 query heads per kv head
+    seed=3, architectures=["Qwen2ForCausalLM"], num_hidden_layers=2, hidden_size=256, num_attention_heads=4,
+    num_key_value_heads=2, head_dim=64, intermediate_size=328, vocab_size=520, rope_theta=1e6,
+    rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=1024, use_sliding_window=False)
+TINY_E = dict(   # head_dim 128, 8 query heads on one kv head, a window of 200 from layer 1 on
+    seed=4, architectures=["Qwen2ForCausalLM"], num_hidden_layers=2, hidden_size=320, num_attention_heads=8,
+    num_key_value_heads=1, head_dim=128, intermediate_size=264, vocab_size=300, rope_theta=1e4,
+    rms_norm_eps=1e-5, tie_word_embeddings=True, max_position_embeddings=1024, use_sliding_window=True,
+    sliding_window=200, max_window_layers=1)
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
 
 F32_ATOL, F32_RTOL = 2e-5, 1e-4          # maeddesg/ROCmForge compares at 1e-4 (tests/gpu_test_utils.rs:12)
 BF16_REL_TO_MAX = 2e-2                   # bfloat16 path against the plain model on the same weights

@@ -42,6 +42,42 @@ def poison_free_pages(cache):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_tuned_kernel_paths_prompt_chunk_decode_and_batch(folders, name, dtype):
+    """Sizes at which the bfloat16 engine runs its tensor-core products (clustered for >= 256 rows), the tiled
+    prefill attention and the chunked decode attention: a 300-token prompt, a chunk, decoding across page and
+    chunk borders, then a ragged batch that reuses the pages."""
+    from rocmforge_b200 import StepRequest
+    m, p = engine(folders, name, dtype), plain(folders, name, dtype)
+    V = CONFIGS[name]["vocab_size"]
+    cache = m.new_cache(max_tokens=64 * 16, max_slots=4)
+    toks = random_tokens(V, 420, 31)
+    ref = p.logits(toks)
+    poison_free_pages(cache)
+    s = cache.alloc_slot()
+    got = [m.step(cache, [StepRequest(s, toks[:300], range(300))]).cpu(),
+           m.step(cache, [StepRequest(s, toks[300:380], range(80))]).cpu()]
+    for i in range(380, 420):
+        got.append(m.step(cache, [StepRequest(s, [toks[i]], [0])]).cpu())
+    assert_logits_close(torch.cat(got), ref, dtype, f"{name} {dtype} prompt + chunk + decode")
+    cache.free_slot(s)
+    poison_free_pages(cache)
+    lens = [(257, 20), (70, 30), (1, 40), (130, 5)]
+    seqs = [random_tokens(V, a + b, 50 + i) for i, (a, b) in enumerate(lens)]
+    refs = [p.logits(t) for t in seqs]
+    slots = [cache.alloc_slot() for _ in lens]
+    got = m.step(cache, [StepRequest(sl, t[:a], [a - 1]) for sl, t, (a, _) in zip(slots, seqs, lens)])
+    assert_logits_close(got.cpu(), torch.stack([r[a - 1] for r, (a, _) in zip(refs, lens)]), dtype, f"{name} ragged prompts")
+    live = list(range(4))
+    for step in range(40):
+        for i in [i for i in live if lens[i][1] <= step]:
+            cache.free_slot(slots[i]); live.remove(i)
+        got = m.step(cache, [StepRequest(slots[i], [seqs[i][lens[i][0] + step]], [0]) for i in live])
+        assert_logits_close(got.cpu(), torch.stack([refs[i][lens[i][0] + step] for i in live]), dtype,
+                            f"{name} batch decode step {step}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_each_request_alone_and_whole(folders, name, dtype):
     from rocmforge_b200 import StepRequest
@@ -278,11 +314,12 @@ def test_sampled_generation_follows_the_plain_sampler(folders):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_graph_replay_equals_plain_steps(folders, dtype):
+@pytest.mark.parametrize("name", ["C", "D"])
+def test_graph_replay_equals_plain_steps(folders, name, dtype):
     import rocmforge_b200 as rf
     prompts = [random_tokens(300, n, n) for n in (3, 30, 64)]
-    a = rf.LLM(folders("C", dtype), dtype=dtype, options=rf.Options(decode_graphs=True))
-    b = rf.LLM(folders("C", dtype), dtype=dtype, options=rf.Options(decode_graphs=False))
+    a = rf.LLM(folders(name, dtype), dtype=dtype, options=rf.Options(decode_graphs=True))
+    b = rf.LLM(folders(name, dtype), dtype=dtype, options=rf.Options(decode_graphs=False))
     ra = a.generate(prompts, max_tokens=70, temperature=0.0, stop_token_ids=[])
     rb = b.generate(prompts, max_tokens=70, temperature=0.0, stop_token_ids=[])
     assert a.engine.decode_runner.replays > 0 and b.engine.decode_runner is None

@@ -131,6 +131,42 @@ def test_attention_part_over_its_cache(dt, window):
 
 
 @pytest.mark.parametrize("dt", DTS)
+def test_prenorm_block_alone(dt):
+    """The arrangement itself: x += mixer(norm1(x)); x += ffn(norm2(x)), against the plain layer."""
+    from rocmforge_b200.cache import SequenceCache
+    from rocmforge_b200.engine import ResidualStream
+    from rocmforge_b200.parts import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS
+    H, nh, nkv, hd, I, T = 48, 3, 3, 16, 72, 37
+    block = BLOCKS.build(
+        "prenorm", norm1=NORMS.build("rmsnorm", size=H, eps=1e-5),
+        mixer=MIXERS.build("gqa_attention", hidden=H, n_heads=nh, n_kv_heads=nkv, head_dim=hd, qkv_bias=True,
+                           position=POSITIONS.build("rope_neox", head_dim=hd, theta=777.0)),
+        norm2=NORMS.build("rmsnorm", size=H, eps=1e-5), ffn=FEED_FORWARDS.build("gated_mlp", hidden=H, intermediate=I),
+        names={"norm1": "input_layernorm.", "mixer": "self_attn.", "norm2": "post_attention_layernorm.", "ffn": "mlp."})
+    tensors = {}
+    for prefix, part in block.sub_parts().items():
+        local = {}
+        for i, (name, spec) in enumerate(part.param_specs().items()):
+            t = rnd(*spec.shape, dt=dt if spec.kind == "matrix" else torch.float32, seed=len(tensors) + i, scale=0.15)
+            if spec.init == "ones":
+                t = t + 1
+            local[name] = t
+            tensors["model.layers.0." + prefix + name] = t.double().cpu()
+        part.bind(local, dt)
+    cache = SequenceCache({0: block.mixer.cache_request()}, max_tokens=128, dtype=dt, device=DEV)
+    slot = cache.alloc_slot()
+    cache.prepare([slot], [T])
+    ctx = context(dt, [(slot, [0] * T, [])], [0])
+    x = rnd(T, H, seed=99)
+    stream = ResidualStream(x.clone())
+    block.forward(ctx, stream, cache.view(0))
+    cfg = dict(num_attention_heads=nh, num_key_value_heads=nkv, head_dim=hd, hidden_size=H, rope_theta=777.0,
+               rms_norm_eps=1e-5, use_sliding_window=False)
+    ref = P.decoder_layer(x.double().cpu(), torch.arange(T), tensors, cfg, 0)
+    close(stream.flush().double().cpu(), ref, dt)
+
+
+@pytest.mark.parametrize("dt", DTS)
 def test_embedding_and_head_parts(dt):
     from rocmforge_b200.parts import OutputHead, TokenEmbedding
     emb, head = TokenEmbedding(333, 40), OutputHead(333, 40, tied_to="model.embed_tokens.weight")
