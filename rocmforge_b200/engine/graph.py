@@ -14,7 +14,10 @@ from typing import Dict, Sequence
 
 import torch
 
-from .batch import DeviceDescriptor, StepBatch, StepRequest
+import numpy as np
+
+from ..cache import CacheError
+from .batch import BatchError, DeviceDescriptor, StepBatch, StepRequest
 from .context import StepContext
 
 
@@ -36,6 +39,7 @@ class DecodeRunner:
         from ..sampling import DeviceSampler
         self.sampler = DeviceSampler(model.device)
         self.replays = 0
+        self._ready = None             # (slots, starts, packed descriptor without token ids, longest) of the next step
 
     @staticmethod
     def length_bucket(longest: int) -> int:
@@ -54,7 +58,9 @@ class DecodeRunner:
         ctx.replayed = True          # launch shapes must not depend on this step's lengths
         return ctx
 
-    def _capture(self, B: int, bound: int) -> _Captured:
+    def _capture(self, B: int, bound: int, greedy: bool = False) -> _Captured:
+        """The step's graph; with ``greedy`` the argmax is part of it and ``ids`` holds its result."""
+        from .. import kernels
         ctx = self._context(B, bound)
         side = torch.cuda.Stream(device=self.model.device)
         side.wait_stream(torch.cuda.current_stream())
@@ -62,28 +68,63 @@ class DecodeRunner:
             self.model.forward(ctx, self.cache)            # warm-up: loads modules, sizes the allocator
         torch.cuda.current_stream().wait_stream(side)
         graph = torch.cuda.CUDAGraph()
+        ids = torch.zeros((B,), dtype=torch.int32, device=self.model.device) if greedy else None
         with torch.cuda.graph(graph):
             logits = self.model.forward(ctx, self.cache)
-        return _Captured(graph, logits)
+            if greedy:
+                kernels.argmax(logits, out=ids)
+        cap = _Captured(graph, logits)
+        cap.ids = ids
+        return cap
 
-    def logits(self, slots: Sequence[int], tokens: Sequence[int]) -> torch.Tensor:
-        """Step one token per slot; float32 logits [B, vocab] (a buffer reused by the next call)."""
+    def logits(self, slots: Sequence[int], tokens: Sequence[int], greedy: bool = False) -> torch.Tensor:
+        """Step one token per slot; float32 logits [B, vocab] (a buffer reused by the next call), or with
+        ``greedy`` the int32 ids [B] that the argmax inside the graph picked.
+
+        The host's part of a step is split in two.  What does not depend on the new token ids (pages for the
+        next position, the descriptor with every position moved on by one) is prepared right after the step's
+        launch, while the device is busy; when the caller comes back with the sampled ids only those are
+        filled in, copied and the graph replayed.  If the batch has changed meanwhile the prepared part is
+        dropped and built afresh.
+        """
         B = len(slots)
         if B > self.max_batch:
             raise ValueError(f"a decode batch of {B} exceeds the runner's limit of {self.max_batch}")
-        requests = [StepRequest(s, [int(t)], [0]) for s, t in zip(slots, tokens)]
+        slots = [int(s) for s in slots]
         starts = [self.cache.length(s) for s in slots]
-        batch = StepBatch(requests, starts, self.model.spec.vocab_size)
-        self.cache.prepare(slots, [1] * B)
-        self.desc.upload(batch.pack())
-        key = (B, self.length_bucket(max(starts) + 1))
+        ready = self._ready
+        self._ready = None
+        if ready is not None and ready[0] == slots and ready[1] == starts:
+            packed, longest = ready[2], ready[3]
+            toks = np.asarray(tokens, dtype=np.int64)
+            if ((toks < 0) | (toks >= self.model.spec.vocab_size)).any():
+                raise BatchError("a token id is outside the vocabulary")
+            packed[:B] = toks
+        else:
+            requests = [StepRequest(s, [int(t)], [0]) for s, t in zip(slots, tokens)]
+            batch = StepBatch(requests, starts, self.model.spec.vocab_size)
+            self.cache.prepare(slots, [1] * B)
+            packed, longest = batch.pack(), max(starts) + 1
+        self.desc.upload(packed)
+        key = (B, self.length_bucket(longest), greedy)
         cap = self.graphs.get(key)
         if cap is None:
-            cap = self.graphs[key] = self._capture(B, key[1])
+            cap = self.graphs[key] = self._capture(B, key[1], greedy)
         cap.graph.replay()
         self.replays += 1
         self.cache.commit(slots, [1] * B)
-        return cap.logits
+        # while the device works: the next step of the same batch, all but its token ids
+        try:
+            self.cache.prepare(slots, [1] * B)
+            lay, _ = StepBatch.layout(B, B, B)
+            nxt = packed.copy()
+            for name in ("tok_pos", "seq_start"):
+                o, n = lay[name]
+                nxt[o:o + n] += 1
+            self._ready = (slots, [x + 1 for x in starts], nxt, longest + 1)
+        except CacheError:
+            self._ready = None                     # no room for a further token: the next call will say so if it comes
+        return cap.ids if greedy else cap.logits
 
     # ---------------------------------------------------------------- replay without host work
     def greedy_loop(self, slots: Sequence[int], tokens: Sequence[int], steps: int):
@@ -130,4 +171,6 @@ class DecodeRunner:
         return out, start, end, cap.launches
 
     def run(self, slots, tokens, requests, draws, sampling) -> torch.Tensor:
+        if sampling.greedy:
+            return self.logits(slots, tokens, greedy=True)
         return self.sampler.sample(self.logits(slots, tokens), sampling, requests, draws)
