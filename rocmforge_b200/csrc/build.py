@@ -38,6 +38,7 @@ MODULES: Dict[str, List[str]] = {
     "gemm_tcgen05_cluster": ["gemm_tcgen05_cluster.cu", "tcgen05_common.cuh", "common.cuh"],
     "attention_decode": ["attention_decode.cu", "common.cuh"],
     "attention_prefill": ["attention_prefill.cu", "common.cuh"],
+    "attention_prefill_tc": ["attention_prefill_tc.cu", "tcgen05_common.cuh", "common.cuh"],
     "attention_decode_noalloc": ["attention_decode_noalloc.cu", "attention_decode_noalloc.h", "attention_decode.cu",
                                  "common.cuh"],
 }

@@ -67,15 +67,19 @@ class StepBatch:
         tiles = [(i, q0) for i in range(self.B) for q0 in range(0, int(self.n_new[i]), Q_TILE)]
         self.q_tiles = np.asarray(tiles, dtype=np.int32).reshape(-1)
         self.n_tiles = len(tiles)
+        big = [(i, q0) for i in range(self.B) for q0 in range(0, int(self.n_new[i]), 2 * Q_TILE)]
+        self.q_tiles128 = np.asarray(big, dtype=np.int32).reshape(-1)      # for the kernel with 128-row tiles
+        self.n_tiles128 = len(big)
         self.is_decode = bool((self.n_new == 1).all())
         self.max_new = int(self.n_new.max())
         self.max_end = int((self.starts + self.n_new).max())
 
     # layout of the packed descriptor, in int32 elements
     @staticmethod
-    def layout(T: int, B: int, R: int, n_tiles: int = 0):
+    def layout(T: int, B: int, R: int, n_tiles: int = 0, n_tiles128: int = 0):
         names = [("tokens", T), ("tok_seq", T), ("tok_pos", T), ("seq_slot", B), ("seq_start", B),
-                 ("seq_nnew", B), ("cu_q", B + 1), ("want_rows", R), ("q_tiles", 2 * n_tiles)]
+                 ("seq_nnew", B), ("cu_q", B + 1), ("want_rows", R), ("q_tiles", 2 * n_tiles),
+                 ("q_tiles128", 2 * n_tiles128)]
         off, out = 0, {}
         for name, n in names:
             out[name] = (off, n)
@@ -83,12 +87,12 @@ class StepBatch:
         return out, off
 
     def pack(self) -> np.ndarray:
-        lay, total = self.layout(self.T, self.B, self.R, self.n_tiles)
+        lay, total = self.layout(self.T, self.B, self.R, self.n_tiles, self.n_tiles128)
         buf = np.zeros((total,), dtype=np.int32)
         for name, arr in (("tokens", self.tokens), ("tok_seq", self.tok_seq), ("tok_pos", self.tok_pos),
                           ("seq_slot", np.asarray(self.slots, dtype=np.int32)), ("seq_start", self.starts),
                           ("seq_nnew", self.n_new), ("cu_q", self.cu_q), ("want_rows", self.want_rows),
-                          ("q_tiles", self.q_tiles)):
+                          ("q_tiles", self.q_tiles), ("q_tiles128", self.q_tiles128)):
             o, n = lay[name]
             buf[o:o + n] = arr
         return buf
@@ -126,6 +130,6 @@ class DeviceDescriptor:
             self._done = torch.cuda.Event()
             self._done.record()
 
-    def views(self, T: int, B: int, R: int, n_tiles: int = 0):
-        lay, _ = StepBatch.layout(T, B, R, n_tiles)
+    def views(self, T: int, B: int, R: int, n_tiles: int = 0, n_tiles128: int = 0):
+        lay, _ = StepBatch.layout(T, B, R, n_tiles, n_tiles128)
         return {name: self.dev[o:o + n] for name, (o, n) in lay.items()}

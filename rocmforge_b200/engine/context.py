@@ -21,6 +21,7 @@ class Options:
     """Switches of the engine (all default to the serving configuration)."""
     tensor_core_gemm: bool = True        # tcgen05 products on the bfloat16 path where the shape allows
     tuned_attention: bool = True         # split-KV decode attention / tiled prefill attention on bfloat16
+    tcgen05_attention: bool = True       # prefill attention with tcgen05.mma (else the mma.sync kernel)
     decode_graphs: bool = True           # replay decode steps from CUDA graphs in the generation loop
 
 
@@ -50,6 +51,7 @@ class StepContext:
         self.cu_q = views["cu_q"]
         self.want_rows = views["want_rows"]
         self.q_tiles = views["q_tiles"]
+        self.q_tiles128 = views["q_tiles128"]
 
     # ---------------------------------------------------------------- matrix products
     def _tensor_cores(self, x, w, mode) -> bool:
@@ -149,6 +151,13 @@ class StepContext:
                     view.block_table, mixer.scale, view.window, max_chunks,
                     scratch("attn_decode_o", n_o, torch.float32), scratch("attn_decode_ml", n_ml, torch.float32),
                     scratch("attn_decode_counters", n_c, torch.int32))
+        if (not self.is_decode and self.compute_dtype == torch.bfloat16 and self.options.tuned_attention
+                and self.options.tcgen05_attention and self.q_tiles128.numel() > 0
+                and kernels.attention_prefill_tc_supported(nh, nkv, hd)
+                and q.data_ptr() % 16 == 0 and (q.stride(0) * 2) % 16 == 0):
+            return kernels.attention_prefill_tc(q, nh, nkv, hd, view.k_pages, view.v_pages, self.q_tiles128,
+                                                self.seq_slot, self.seq_start, self.seq_nnew, self.cu_q,
+                                                view.block_table, mixer.scale, view.window)
         if (not self.is_decode and self.compute_dtype == torch.bfloat16 and self.options.tuned_attention
                 and self.q_tiles.numel() > 0 and kernels.attention_prefill_supported(nh, nkv, hd)
                 and q.data_ptr() % 4 == 0 and q.stride(0) % 2 == 0):

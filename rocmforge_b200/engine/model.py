@@ -166,7 +166,7 @@ class Model:
         batch = StepBatch(requests, starts_now, self.spec.vocab_size)
         cache.prepare(slots, n_new)
         self._desc.upload(batch.pack())
-        views = self._desc.views(batch.T, batch.B, batch.R, batch.n_tiles)
+        views = self._desc.views(batch.T, batch.B, batch.R, batch.n_tiles, batch.n_tiles128)
         ctx = StepContext(self, views, T=batch.T, B=batch.B, R=batch.R, is_decode=batch.is_decode,
                           max_new=batch.max_new, max_end=batch.max_end, host=batch)
         logits = self.forward(ctx, cache)

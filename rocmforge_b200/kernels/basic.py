@@ -356,3 +356,41 @@ def attention_decode_cluster(q: torch.Tensor, n_heads: int, n_kv_heads: int, hea
             int(window or 0), B, splits, ptr(status_word(q.device)), stream()),
           f"attention_decode_cluster (heads={n_heads}, kv_heads={n_kv_heads}, head_dim={head_dim}, splits={splits})")
     return out
+
+
+PREFILL_TC_TILE = 128
+
+
+def attention_prefill_tc_supported(n_heads: int, n_kv_heads: int, head_dim: int) -> bool:
+    f = _f("attention_prefill_tc", "rf_attention_prefill_tc_supported", c_int, c_int, c_int)
+    return bool(f(n_heads, n_kv_heads, head_dim))
+
+
+def attention_prefill_tc(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, k_pages, v_pages,
+                         q_tiles: torch.Tensor, seq_slot, seq_start, seq_nnew, cu_q, block_table, scale: float,
+                         window: int | None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """The same attention as ``attention_prefill`` with both products as tcgen05.mma (accumulators in tensor
+    memory); ``q_tiles`` holds (sequence, first row) pairs of 128-row tiles."""
+    need_cuda(q, k_pages, v_pages, q_tiles, seq_slot, seq_start, seq_nnew, cu_q, block_table)
+    T = q.shape[0]
+    need(q.dtype == torch.bfloat16 and q.dim() == 2 and q.stride(1) == 1 and q.shape[1] >= n_heads * head_dim,
+         "attention_prefill_tc: q must be bfloat16 [T, >= heads*head_dim]")
+    need(q.data_ptr() % 16 == 0 and (q.stride(0) * 2) % 16 == 0, "attention_prefill_tc: q rows must be 16-byte aligned")
+    need(k_pages.dtype == torch.bfloat16 and tuple(k_pages.shape[1:]) == (n_kv_heads, PAGE, head_dim)
+         and k_pages.is_contiguous() and v_pages.shape == k_pages.shape and v_pages.is_contiguous(),
+         "attention_prefill_tc: bad cache page shape or dtype")
+    need(attention_prefill_tc_supported(n_heads, n_kv_heads, head_dim),
+         f"attention_prefill_tc: heads={n_heads}, kv_heads={n_kv_heads}, head_dim={head_dim} is not supported")
+    need(q_tiles.dtype == torch.int32 and q_tiles.numel() % 2 == 0, "attention_prefill_tc: q_tiles must be int32 pairs")
+    if out is None:
+        out = torch.empty((T, n_heads * head_dim), dtype=torch.bfloat16, device=q.device)
+    from .tensor_core import status_word
+    f = _f("attention_prefill_tc", "rf_attention_prefill_tc", c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
+           c_ll, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
+           c_int, c_void_p, c_void_p)
+    check(f(ptr(q), q.stride(0), T, ptr(out), out.stride(0), ptr(k_pages), ptr(v_pages), k_pages.shape[0], ptr(q_tiles),
+            q_tiles.numel() // 2, ptr(seq_slot), ptr(seq_start), ptr(seq_nnew), ptr(cu_q), ptr(block_table),
+            block_table.shape[1], n_heads, n_kv_heads, head_dim, float(scale), int(window or 0),
+            ptr(status_word(q.device)), stream()),
+          f"attention_prefill_tc (heads={n_heads}, kv_heads={n_kv_heads}, head_dim={head_dim})")
+    return out

@@ -70,7 +70,7 @@ class GQAAttention(Mixer):
     def cuda_modules(self, compute_dtype):
         mods = ["elementwise", "attention_generic"]
         if compute_dtype == torch.bfloat16:
-            mods += ["attention_decode", "attention_prefill"]
+            mods += ["attention_decode", "attention_prefill", "attention_prefill_tc"]
         return mods
 
     def cache_request(self):

@@ -312,9 +312,11 @@ def check_far_keys(run, vs):
 
 @pytest.mark.parametrize("nh,nkv,hd,window", [(28, 4, 128, None), (14, 2, 64, None), (4, 4, 64, 100), (6, 1, 128, 70),
                                               (2, 2, 128, 64), (3, 1, 64, 1)])
-def test_attention_prefill(nh, nkv, hd, window):
+@pytest.mark.parametrize("kernel", ["mma_sync", "tcgen05"])
+def test_attention_prefill(nh, nkv, hd, window, kernel):
     """Tiled attention: a whole prompt, a chunk appended to a context, tiny and page-straddling pieces."""
     from rocmforge_b200 import kernels
+    tile, run = (64, kernels.attention_prefill) if kernel == "mma_sync" else (128, kernels.attention_prefill_tc)
     dt = torch.bfloat16
     lens = [300, 333, 65, 1, 64, 130]
     new = [300, 50, 65, 1, 3, 129]
@@ -325,10 +327,10 @@ def test_attention_prefill(nh, nkv, hd, window):
     cu = [0]
     for n in new:
         cu.append(cu[-1] + n)
-    tiles = [(i, q0) for i, n in enumerate(new) for q0 in range(0, n, 64)]
+    tiles = [(i, q0) for i, n in enumerate(new) for q0 in range(0, n, tile)]
     dev = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
     scale = 1.0 / math.sqrt(hd)
-    out = kernels.attention_prefill(q.to(DEV), nh, nkv, hd, k_pages, v_pages, dev(tiles).view(-1),
+    out = run(q.to(DEV), nh, nkv, hd, k_pages, v_pages, dev(tiles).view(-1),
                                     dev(list(range(1, len(lens) + 1))), dev([L - n for L, n in zip(lens, new)]),
                                     dev(new), dev(cu), table, scale, window)
     assert torch.isfinite(out.float()).all()
@@ -340,8 +342,10 @@ def test_attention_prefill(nh, nkv, hd, window):
             t += 1
 
 
-def test_attention_prefill_finds_far_keys_and_the_window_edge():
+@pytest.mark.parametrize("kernel", ["mma_sync", "tcgen05"])
+def test_attention_prefill_finds_far_keys_and_the_window_edge(kernel):
     from rocmforge_b200 import kernels
+    fn = kernels.attention_prefill if kernel == "mma_sync" else kernels.attention_prefill_tc
     dt, nh, nkv, hd, n = torch.bfloat16, 1, 1, 64, 700
     ks, vs, k_pages, v_pages, table = paged([n], nkv, hd, dt, n_pages=16, seed=9)
     # the last two rows are the queries; both look along dim 0
@@ -353,8 +357,8 @@ def test_attention_prefill_finds_far_keys_and_the_window_edge():
         page = int(table[1, target // 64])
         kp[page, 0, target % 64] = 0
         kp[page, 0, target % 64, 0] = 60.0
-        return kernels.attention_prefill(q.to(dt).to(DEV), nh, nkv, hd, kp, v_pages, dev([0, 0]), dev([1]), dev([n - 2]),
-                                         dev([2]), dev([0, 2]), table, 1.0 / math.sqrt(hd), window).float().cpu()
+        return fn(q.to(dt).to(DEV), nh, nkv, hd, kp, v_pages, dev([0, 0]), dev([1]), dev([n - 2]),
+                  dev([2]), dev([0, 2]), table, 1.0 / math.sqrt(hd), window).float().cpu()
 
     for target in (0, 63, 64, 320, 697):
         out = run(target, None)

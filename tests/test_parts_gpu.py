@@ -48,7 +48,7 @@ def context(dt, requests, starts, vocab=1 << 20):
     batch = StepBatch([StepRequest(*r) for r in requests], starts, vocab)
     desc = DeviceDescriptor(DEV)
     desc.upload(batch.pack())
-    ctx = StepContext(fake_model, desc.views(batch.T, batch.B, batch.R, batch.n_tiles), T=batch.T, B=batch.B, R=batch.R,
+    ctx = StepContext(fake_model, desc.views(batch.T, batch.B, batch.R, batch.n_tiles, batch.n_tiles128), T=batch.T, B=batch.B, R=batch.R,
                       is_decode=batch.is_decode, max_new=batch.max_new, max_end=batch.max_end, host=batch)
     ctx._keep = desc
     return ctx
