@@ -28,6 +28,15 @@ __device__ __forceinline__ float at_exp2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// Weights are rounded to bfloat16 with integer arithmetic (add half an ulp, keep the upper 16 bits): the
+// conversion instruction shares the special-function unit with ex2.  Two variants that measured SLOWER here
+// and were dropped: a share of the exponentials as a polynomial on the FMA pipe (763 -> 734 TFLOP/s at 8,192
+// tokens), and two softmax threads per row (763 -> 435): the softmax warps lack neither ex2 throughput nor
+// threads; what helped was letting the next page's scores be computed while they work (see issue_s).
+__device__ __forceinline__ uint32_t at_pack_bf16x2(float a, float b) {      // a, b >= 0 and finite
+    return __byte_perm(__float_as_uint(a) + 0x8000u, __float_as_uint(b) + 0x8000u, 0x7632);
+}
+
 __device__ __forceinline__ void tcgen05_st32(uint32_t taddr, const uint32_t* r) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -74,17 +83,17 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     constexpr uint32_t Q_BYTES = HALVES * QH_BYTES;
     constexpr uint32_t KH_BYTES = AT_BN * 128;          // one column block of a page of keys (or values)
     constexpr uint32_t KV_BYTES = HALVES * KH_BYTES;
-    constexpr uint32_t TMEM_COLS = 256;                 // S: columns 0..63, O: columns 64..64+HD-1
+    constexpr uint32_t TMEM_COLS = 256;                 // S (two buffers): columns 0..127, O: columns 128..128+HD-1
     extern __shared__ __align__(1024) uint8_t smem[];   // no static shared memory: the window starts aligned
     uint8_t* q_s = smem;                                 // [HALVES][128][128 B]
     uint8_t* kv_s = q_s + Q_BYTES;                       // [2 stages][K | V][HALVES][64][128 B]
     uint8_t* p_s = kv_s + 4 * KV_BYTES;                  // [128][128 B]: 64 keys of bfloat16 per row
     uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + QH_BYTES);
-    // q_full, kv_full[2], kv_free[2], s_full, p_ready, pv_done
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+    // q_full, kv_full[2], kv_free[2], s_full[2], p_ready, pv_done
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
     int& abort_flag = *reinterpret_cast<int*>(tmem_slot + 1);
     const uint32_t b_q = smem_u32(&bars[0]), b_kvfull = smem_u32(&bars[1]), b_kvfree = smem_u32(&bars[3]);
-    const uint32_t b_sfull = smem_u32(&bars[5]), b_pready = smem_u32(&bars[6]), b_pvdone = smem_u32(&bars[7]);
+    const uint32_t b_sfull = smem_u32(&bars[5]), b_pready = smem_u32(&bars[7]), b_pvdone = smem_u32(&bars[8]);
 
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -106,6 +115,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         mbar_init(b_q, 1);
         for (int s = 0; s < 2; ++s) { mbar_init(b_kvfull + 8 * s, 1); mbar_init(b_kvfree + 8 * s, 1); }
         mbar_init(b_sfull, 1);
+        mbar_init(b_sfull + 8, 1);
         mbar_init(b_pready, 128);
         mbar_init(b_pvdone, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -121,7 +131,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + AT_BN;
+    const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * AT_BN;
     pdl_wait();                                         // queries, keys and values come from the kernel before us
 
     if (warp == 0) {
@@ -146,21 +156,29 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         // ---------------- MMA issuer
         if (lane == 0) {
             constexpr uint32_t idesc_s = at_idesc(AT_BN, 0), idesc_o = at_idesc(HD, 1);
-            bool ok = mbar_wait(b_q, 0, &abort_flag);
-            for (int t = 0; t < n_kt && ok; ++t) {
+            // S has two buffers in tensor memory: the scores of page t + 1 are computed while the softmax
+            // warps are still busy with page t, so they find their next input ready when they come back.
+            auto issue_s = [&](int t) -> bool {
                 const int st = t & 1;
-                ok = mbar_wait(b_kvfull + 8 * st, (t >> 1) & 1, &abort_flag);
-                if (!ok) break;
+                if (!mbar_wait(b_kvfull + 8 * st, (t >> 1) & 1, &abort_flag)) return false;
                 tcgen05_fence_after();
-                const uint32_t k_t = smem_u32(kv_s + (size_t)st * 2 * KV_BYTES), v_t = k_t + KV_BYTES;
+                const uint32_t k_t = smem_u32(kv_s + (size_t)st * 2 * KV_BYTES);
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ++ks)      // S = Q K^T over the head dimension
-                    tcgen05_mma_bf16(tmem_s, make_smem_desc(smem_u32(q_s) + (ks >> 2) * QH_BYTES + (ks & 3) * 32),
+                    tcgen05_mma_bf16(tmem_s + st * AT_BN, make_smem_desc(smem_u32(q_s) + (ks >> 2) * QH_BYTES + (ks & 3) * 32),
                                      make_smem_desc(k_t + (ks >> 2) * KH_BYTES + (ks & 3) * 32), idesc_s, ks ? 1u : 0u);
-                tcgen05_commit(b_sfull);
-                ok = mbar_wait(b_pready, t & 1, &abort_flag);          // P is in shared memory, S has been read
+                tcgen05_commit(b_sfull + 8 * st);
+                return true;
+            };
+            bool ok = mbar_wait(b_q, 0, &abort_flag);
+            if (ok && n_kt > 0) ok = issue_s(0);
+            for (int t = 0; t < n_kt && ok; ++t) {
+                const int st = t & 1;
+                if (t + 1 < n_kt) { ok = issue_s(t + 1); if (!ok) break; }
+                ok = mbar_wait(b_pready, t & 1, &abort_flag);          // P(t) is in shared memory, S(t) has been read
                 if (!ok) break;
                 tcgen05_fence_after();
+                const uint32_t v_t = smem_u32(kv_s + (size_t)st * 2 * KV_BYTES) + KV_BYTES;
 #pragma unroll
                 for (int ks = 0; ks < AT_BN / 16; ++ks)   // O += P V over the page's 64 keys
                     tcgen05_mma_bf16(tmem_o, make_smem_desc(smem_u32(p_s) + ks * 32),
@@ -183,7 +201,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         for (int t = 0; t < n_kt; ++t) {
             const int st = t & 1;
             const int key0 = (kt_lo + t) * AT_BN;
-            ok = mbar_wait(b_sfull, t & 1, &abort_flag);
+            ok = mbar_wait(b_sfull + 8 * st, (t >> 1) & 1, &abort_flag);
             if (!ok) break;
             tcgen05_fence_after();
             // the value rows past the sequence's end were never written (or belong to a page that was not
@@ -199,45 +217,53 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             }
             const bool no_mask = key0 + AT_BN - 1 <= pos_first && rows_here == AT_BM &&
                                  (window <= 0 || key0 >= pos_last - window + 1);
-            // the row of S, once, into registers (scores in units of log2 e; masked ones -inf)
+            // the row of S, once, into registers (raw products; masked ones -inf).  Maximum and sum are kept
+            // in four independent partial results each: one warp per scheduler cannot hide a chain of 64
+            // dependent operations
             float sc[AT_BN];
             {
                 uint32_t r[32];
 #pragma unroll
                 for (int c0 = 0; c0 < AT_BN; c0 += 32) {
-                    tcgen05_ld32(tmem_s + lane_base + c0, r);
+                    tcgen05_ld32(tmem_s + st * AT_BN + lane_base + c0, r);
                     tcgen05_wait_ld();
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) sc[c0 + j] = __uint_as_float(r[j]) * sl2;
+                    for (int j = 0; j < 32; ++j) sc[c0 + j] = __uint_as_float(r[j]);
                 }
             }
-            float mx = -INFINITY;
-            if (no_mask) {
-#pragma unroll
-                for (int j = 0; j < AT_BN; ++j) mx = fmaxf(mx, sc[j]);
-            } else {
+            if (!no_mask) {
 #pragma unroll
                 for (int j = 0; j < AT_BN; ++j) {
                     const int key = key0 + j;
                     if (!(row_ok && key <= pos_i && key >= lo_i)) sc[j] = -INFINITY;
-                    mx = fmaxf(mx, sc[j]);
                 }
             }
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int j = 0; j < AT_BN; j += 4) {
+                mx4[0] = fmaxf(mx4[0], sc[j]); mx4[1] = fmaxf(mx4[1], sc[j + 1]);
+                mx4[2] = fmaxf(mx4[2], sc[j + 2]); mx4[3] = fmaxf(mx4[3], sc[j + 3]);
+            }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl2;      // in units of log2 e (sl2 > 0)
             // move the reference only when the maximum has grown by more than 8: then O and l are rescaled
             float corr = 1.f;
             if (mx > m_ref + 8.f) {
                 corr = (m_ref == -INFINITY) ? 0.f : at_exp2(m_ref - mx);
                 m_ref = mx;
             }
-            const float ref = (m_ref == -INFINITY) ? 0.f : m_ref;
-            float sum = 0.f;
+            const float nref = (m_ref == -INFINITY) ? 0.f : -m_ref;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
             uint32_t pk[AT_BN / 2];
 #pragma unroll
-            for (int j = 0; j < AT_BN; j += 2) {
-                const float p0 = at_exp2(sc[j] - ref), p1 = at_exp2(sc[j + 1] - ref);     // ex2(-inf) = 0
-                sum += p0 + p1;
-                pk[j >> 1] = pack_bf16x2(p0, p1);
+            for (int j = 0; j < AT_BN; j += 4) {
+                // weight = 2^(raw * scale * log2 e - reference): one FMA and one ex2 each; ex2(-inf) = 0
+                const float p0 = at_exp2(fmaf(sc[j], sl2, nref)), p1 = at_exp2(fmaf(sc[j + 1], sl2, nref));
+                const float p2 = at_exp2(fmaf(sc[j + 2], sl2, nref)), p3 = at_exp2(fmaf(sc[j + 3], sl2, nref));
+                sum4[0] += p0; sum4[1] += p1; sum4[2] += p2; sum4[3] += p3;
+                pk[j >> 1] = at_pack_bf16x2(p0, p1);
+                pk[(j >> 1) + 1] = at_pack_bf16x2(p2, p3);
             }
+            const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             // the previous P V must be complete before P is overwritten or O touched
             if (t > 0) {
                 ok = mbar_wait(b_pvdone, (t - 1) & 1, &abort_flag);
@@ -309,7 +335,7 @@ static int at_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtenso
                      const int* tiles, int n_tiles, const int* seq_slot, const int* seq_start, const int* seq_nnew,
                      const int* cu_q, const int* block_table, int max_pages, int nh, int nkv, float scale, int window,
                      int* status, cudaStream_t st) {
-    constexpr size_t smem = (size_t)(HD / 64) * AT_BM * 128 + 4 * (size_t)(HD / 64) * AT_BN * 128 + AT_BM * 128 + 8 * 8 + 16;
+    constexpr size_t smem = (size_t)(HD / 64) * AT_BM * 128 + 4 * (size_t)(HD / 64) * AT_BN * 128 + AT_BM * 128 + 9 * 8 + 16;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
