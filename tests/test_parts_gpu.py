@@ -360,3 +360,99 @@ def _params_of(model):
             out[prefix + "gate_proj.weight"], out[prefix + "up_proj.weight"] = gu[0::2], gu[1::2]
             out[prefix + "down_proj.weight"] = part.down.weight
     return out
+
+
+def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_plug_in():
+    """Two more kinds defined here and reached through the registries alone: a feed-forward that routes every
+    token to one of several small experts (router logits in 32-bit), and a position encoding that stretches
+    positions by a factor (it only has to hand the attention part its table of frequencies)."""
+    import rocmforge_b200 as rf
+    from rocmforge_b200.cache import SequenceCache
+    from rocmforge_b200.engine import ResidualStream
+    from rocmforge_b200.parts import FEED_FORWARDS, MIXERS, POSITIONS, FeedForward, PositionEncoding
+    from rocmforge_b200.weights import ParamSpec
+    dt = torch.float32
+
+    @FEED_FORWARDS.register("toy_top1_experts")
+    class Top1Experts(FeedForward):
+        def __init__(self, hidden, inner, n_experts):
+            self.hidden, self.inner, self.n = hidden, inner, n_experts
+
+        def param_specs(self):
+            s = {"router.weight": ParamSpec((self.n, self.hidden), std=0.5)}
+            for e in range(self.n):
+                s[f"experts.{e}.up.weight"] = ParamSpec((self.inner, self.hidden), std=0.2)
+                s[f"experts.{e}.down.weight"] = ParamSpec((self.hidden, self.inner), std=0.2)
+            return s
+
+        def bind(self, params, compute_dtype):
+            self.p = params
+
+        def forward(self, ctx, y, stream):
+            logits = ctx.matmul(y, self.p["router.weight"], out_f32=True)           # 32-bit router logits
+            choice = logits.argmax(dim=-1)
+            gate = torch.softmax(logits, dim=-1).gather(1, choice[:, None])
+            for e in range(self.n):                                                  # tokens of expert e, as one batch
+                rows = torch.nonzero(choice == e)[:, 0]
+                if rows.numel() == 0:
+                    continue
+                h = torch.relu(ctx.matmul(y[rows].contiguous(), self.p[f"experts.{e}.up.weight"]))
+                upd = ctx.matmul(h, self.p[f"experts.{e}.down.weight"], out_f32=True) * gate[rows]
+                stream.flush().index_add_(0, rows, upd)
+
+    @POSITIONS.register("toy_stretched_rope")
+    class StretchedRope(PositionEncoding):
+        """Rotation by (position / factor): the same kernel, another table."""
+        def __init__(self, head_dim, theta, factor):
+            i = torch.arange(head_dim // 2, dtype=torch.float64)
+            self.inv_freq_host = (1.0 / (theta ** (2.0 * i / head_dim)) / factor).to(torch.float32)
+            self.inv_freq = None
+
+        def prepare(self, device):
+            self.inv_freq = self.inv_freq_host.to(device)
+
+    # ---- the routed feed-forward against the same thing written out
+    H, I, E, T = 40, 24, 3, 50
+    ffn = FEED_FORWARDS.build("toy_top1_experts", hidden=H, inner=I, n_experts=E)
+    p = {n: rnd(*sp.shape, seed=i, scale=sp.std) for i, (n, sp) in enumerate(ffn.param_specs().items())}
+    ffn.bind(p, dt)
+    ctx = context(dt, [(0, [1] * T, [])], [0])
+    y = rnd(T, H, seed=77)
+    stream = ResidualStream(torch.zeros(T, H, device=DEV))
+    ffn.forward(ctx, y, stream)
+    yd = y.double().cpu()
+    logits = yd @ p["router.weight"].double().cpu().t()
+    ref = torch.zeros(T, H, dtype=torch.float64)
+    for t in range(T):
+        e = int(logits[t].argmax())
+        g = torch.softmax(logits[t], dim=-1)[e]
+        h = torch.relu(yd[t] @ p[f"experts.{e}.up.weight"].double().cpu().t())
+        ref[t] = g * (h @ p[f"experts.{e}.down.weight"].double().cpu().t())
+    torch.testing.assert_close(stream.flush().double().cpu(), ref, atol=2e-5, rtol=1e-4)
+    assert len(set(int(logits[t].argmax()) for t in range(T))) == E, "every expert should get tokens in this test"
+
+    # ---- the stretched rotation inside the framework's attention part
+    nh, nkv, hd, factor = 4, 2, 16, 4.0
+    mixer = MIXERS.build("gqa_attention", hidden=H, n_heads=nh, n_kv_heads=nkv, head_dim=hd, qkv_bias=False,
+                         position=POSITIONS.build("toy_stretched_rope", head_dim=hd, theta=100.0, factor=factor))
+    pm = {n: rnd(*sp.shape, seed=20 + i, scale=0.2) for i, (n, sp) in enumerate(mixer.param_specs().items())}
+    mixer.bind(pm, dt)
+    cache = SequenceCache({0: mixer.cache_request()}, max_tokens=128, dtype=dt, device=DEV)
+    slot = cache.alloc_slot()
+    cache.prepare([slot], [T])
+    ctx = context(dt, [(slot, [0] * T, [])], [0])
+    stream = ResidualStream(torch.zeros(T, H, device=DEV))
+    mixer.forward(ctx, y, cache.view(0), stream)
+    # plain: rotate by positions / factor (the plain rope takes integer positions, so stretch theta-free by hand)
+    q = (yd @ pm["q_proj.weight"].double().cpu().t()).view(T, nh, hd)
+    k = (yd @ pm["k_proj.weight"].double().cpu().t()).view(T, nkv, hd)
+    v = (yd @ pm["v_proj.weight"].double().cpu().t()).view(T, nkv, hd)
+
+    def rot(x):
+        half = hd // 2
+        ang = (torch.arange(T, dtype=torch.float32)[:, None] * mixer.position.inv_freq_host[None, :]).double()
+        c, s_ = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+        return torch.cat([x[..., :half] * c - x[..., half:] * s_, x[..., :half] * s_ + x[..., half:] * c], dim=-1)
+    o = P.causal_attention(rot(q), rot(k), v)
+    ref = o.reshape(T, nh * hd) @ pm["o_proj.weight"].double().cpu().t()
+    torch.testing.assert_close(stream.flush().double().cpu(), ref, atol=2e-5, rtol=1e-4)
