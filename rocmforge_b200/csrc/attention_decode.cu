@@ -15,6 +15,7 @@
 // the chunks in index order, so the result does not depend on which CTA that was.  The grid
 // may be larger than the context needs (a replayed CUDA graph keeps its launch shape): CTAs
 // beyond the sequence's last chunk, or wholly before its window, leave at once.
+#include <cuda.h>
 #include "common.cuh"
 
 #define DEC_THREADS 128
@@ -36,7 +37,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
                         int* __restrict__ counters, int* __restrict__ status) {
     constexpr int HD = EPL * 32;
     constexpr uint32_t SLAB = RF_PAGE * HD * 2;                 // bytes of one page's keys of one kv head
-    extern __shared__ __align__(128) uint8_t dec_smem[];
+    extern __shared__ __align__(1024) uint8_t dec_smem[];
     __nv_bfloat16* k_s = reinterpret_cast<__nv_bfloat16*>(dec_smem);                   // [128][HD]
     __nv_bfloat16* v_s = k_s + DEC_CHUNK * HD;                                          // [128][HD]
     float* p_s = reinterpret_cast<float*>(v_s + DEC_CHUNK * HD);                        // [GP][128] scores, then weights
@@ -288,14 +289,17 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
 // For contexts of ordinary length the merge through global memory above costs more than the attention
 // itself (write partials, fence, count arrivals, fence, read them back: five trips to L2).  Here the
 // CTAs that share a (sequence, kv head) form a thread-block cluster of `splits` CTAs instead.  CTA r
-// walks the pages r, r + splits, r + 2*splits, ... of the context with a three-stage ring of bulk
-// copies; each warp owns 16 of a page's 64 keys and keeps its own running maximum, sum and output
+// walks the pages r, r + splits, r + 2*splits, ... of the context with a ring of TMA copies (128-byte
+// swizzle, so that ldmatrix reads the key and value fragments without bank conflicts; with plain
+// 256-byte rows the fragment loads were 8-way conflicted and took most of a page's time); each warp
+// owns 16 of a page's 64 keys and keeps its own running maximum, sum and output
 // across pages (the online softmax, as in the prefill kernel), so a page costs one mbarrier wait and
 // one CTA barrier.  At the end the four warps' states are merged in shared memory, and CTA 0 reads its
 // peers' states through distributed shared memory, in rank order, and writes the result.  No scratch
 // memory, no atomics; the launch shape depends on the batch alone, so a captured graph stays valid
 // while the context grows.
-#define DCL_STAGES 3
+#define DCL_MAX_STAGES 6
+#define DCL_MAX_PAGES 256             // pages one CTA may walk (16,384 keys)
 
 __device__ __forceinline__ uint32_t dcl_cluster_rank() {
     uint32_t r;
@@ -316,24 +320,28 @@ __device__ __forceinline__ float dcl_ld_remote(const float* local, uint32_t rank
 
 template <int EPL>
 __global__ void __launch_bounds__(DEC_THREADS)
-attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* __restrict__ out,
-                                int out_stride, const __nv_bfloat16* __restrict__ k_pages,
-                                const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ tok_seq,
+attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                                const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* __restrict__ out,
+                                int out_stride, const int* __restrict__ tok_seq,
                                 const int* __restrict__ tok_pos, const int* __restrict__ seq_slot,
                                 const int* __restrict__ block_table, int max_pages, int nh, int nkv, float scale,
-                                int window, int splits, int* __restrict__ status) {
+                                int window, int splits, int stages, int* __restrict__ status) {
     constexpr int HD = EPL * 32;
     constexpr uint32_t SLAB = RF_PAGE * HD * 2;                 // one page's keys (or values) of one kv head
-    extern __shared__ __align__(128) uint8_t dec_smem[];
-    __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(dec_smem);                  // [stage][K | V][64][HD]
-    float* w_m = reinterpret_cast<float*>(dec_smem);                                   // [4 warps][GP]: over the ring,
+    constexpr int HALVES = HD / 64;                             // 128-byte column blocks of a row
+    constexpr uint32_t HALF_BYTES = RF_PAGE * 128;              // one column block of a page: [64 rows][128 B], swizzled
+    extern __shared__ __align__(1024) uint8_t dec_smem[];
+    // the swizzle pattern is a function of the address: the ring starts on a 1024-byte boundary (the same in every CTA)
+    uint8_t* ring = dec_smem + ((1024u - (dec_smem_u32(dec_smem) & 1023u)) & 1023u);    // [stage][K | V][HALVES][64][128 B]
+    float* w_m = reinterpret_cast<float*>(ring);                                       // [4 warps][GP]: over the ring,
     float* w_l = w_m + DEC_WARPS * DEC_GP;                                              // [4][GP]        once the last
     float* w_o = w_l + DEC_WARPS * DEC_GP;                                              // [4][GP][HD]    page is done
-    float* c_m = reinterpret_cast<float*>(dec_smem + DCL_STAGES * 2 * SLAB);           // this CTA: [GP]
+    float* c_m = reinterpret_cast<float*>(ring + (size_t)stages * 2 * SLAB);            // this CTA: [GP]
     float* c_l = c_m + DEC_GP;                                                          // [GP]
     float* c_o = c_l + DEC_GP;                                                          // [GP][HD]
     uint64_t* bars = reinterpret_cast<uint64_t*>(c_o + DEC_GP * HD);                   // [stages]
     __shared__ int gave_up;
+    __shared__ int page_of[DCL_MAX_PAGES];              // this CTA's pages, read from the block table once
 
     pdl_trigger();
     const int G = nh / nkv;
@@ -345,30 +353,41 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, int q_strid
     const int p_lo = lo / RF_PAGE, p_hi = pos / RF_PAGE;
     const int n_my = (p_hi - p_lo - rank) >= 0 ? (p_hi - p_lo - rank) / splits + 1 : 0;     // pages of this CTA
     const int* bt = block_table + (size_t)seq_slot[tok_seq[b]] * max_pages;
+    if (p_hi - p_lo + 1 > DCL_MAX_PAGES * splits) {     // more pages than a CTA's table holds: the same verdict in
+        if (tid == 0 && status) atomicExch(status, 7);  // every CTA of the cluster; the caller bounds the context
+        return;
+    }
+    // the block table is not written by any kernel of the step: fetch this CTA's entries now, all at once,
+    // instead of one dependent global load per page on the copy-issuing thread's critical path
+    for (int k = tid; k < n_my && k < DCL_MAX_PAGES; k += DEC_THREADS) page_of[k] = bt[p_lo + rank + k * splits];
 
     if (tid == 0) {
         gave_up = 0;
-        for (int s = 0; s < DCL_STAGES; ++s)
+        for (int s = 0; s < stages; ++s)
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(dec_smem_u32(&bars[s])));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
     }
     __syncthreads();
     pdl_wait();                                         // queries and the newest keys/values come from the kernel before us
 
     auto issue = [&](int k) {                           // thread 0: page p_lo + rank + k*splits into stage k % stages
-        const int stage = k % DCL_STAGES;
+        const int stage = k % stages;
         const uint32_t bar = dec_smem_u32(&bars[stage]);
-        const int page = bt[p_lo + rank + k * splits];
-        const size_t off = ((size_t)page * nkv + kvh) * RF_PAGE * HD;
-        __nv_bfloat16* dst = ring + (size_t)stage * 2 * RF_PAGE * HD;
+        const int row = (page_of[k] * nkv + kvh) * RF_PAGE;      // first row of the page in the [pages*kv*64, HD] view
+        const uint32_t dst = dec_smem_u32(ring + (size_t)stage * 2 * SLAB);
         asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(2 * SLAB) : "memory");
-        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                     ::"r"(dec_smem_u32(dst)), "l"(k_pages + off), "r"(SLAB), "r"(bar) : "memory");
-        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                     ::"r"(dec_smem_u32(dst + RF_PAGE * HD)), "l"(v_pages + off), "r"(SLAB), "r"(bar) : "memory");
+#pragma unroll
+        for (int h = 0; h < HALVES; ++h) {
+            asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                         ::"r"(dst + h * HALF_BYTES), "l"(&map_k), "r"(h * 64), "r"(row), "r"(bar) : "memory");
+            asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                         ::"r"(dst + SLAB + h * HALF_BYTES), "l"(&map_v), "r"(h * 64), "r"(row), "r"(bar) : "memory");
+        }
     };
     if (tid == 0)
-        for (int k = 0; k < n_my && k < DCL_STAGES - 1; ++k) issue(k);
+        for (int k = 0; k < n_my && k < stages - 1; ++k) issue(k);
 
     uint32_t qa[HD / 16][2];
 #pragma unroll
@@ -386,11 +405,11 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, int q_strid
     float m_run = -INFINITY, l_run = 0.f;
 
     for (int k = 0; k < n_my; ++k) {
-        const int stage = k % DCL_STAGES;
-        if (tid == 0 && k + DCL_STAGES - 1 < n_my) issue(k + DCL_STAGES - 1);      // its stage was released by the last sync
+        const int stage = k % stages;
+        if (tid == 0 && k + stages - 1 < n_my) issue(k + stages - 1);              // its stage was released by the last sync
         {
             const uint32_t bar = dec_smem_u32(&bars[stage]);
-            const uint32_t parity = (k / DCL_STAGES) & 1;
+            const uint32_t parity = (k / stages) & 1;
             uint32_t ok = 0;
             unsigned long long t0 = 0;
             for (long long it = 0; !ok; ++it) {
@@ -407,21 +426,23 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, int q_strid
         }
         __syncthreads();                                 // one verdict for everyone
         if (gave_up) break;
-        const __nv_bfloat16* k_s = ring + (size_t)stage * 2 * RF_PAGE * HD;
-        __nv_bfloat16* v_s = ring + (size_t)stage * 2 * RF_PAGE * HD + RF_PAGE * HD;
+        const uint32_t k_t = dec_smem_u32(ring + (size_t)stage * 2 * SLAB), v_t = k_t + SLAB;
         const int key0 = (p_lo + rank + k * splits) * RF_PAGE;
         int k_begin = lo - key0; if (k_begin < 0) k_begin = 0;                    // valid rows of this page
         int k_last = pos - key0; if (k_last > RF_PAGE - 1) k_last = RF_PAGE - 1;
         if (k_begin > 0 || k_last < RF_PAGE - 1) {
             // rows outside the sequence get weight zero, but 0 * (whatever bits lie there) must be 0
-            for (int i = tid; i < RF_PAGE * (HD / 8); i += DEC_THREADS) {
-                const int row = i / (HD / 8);
-                if (row < k_begin || row > k_last) reinterpret_cast<uint4*>(v_s)[i] = make_uint4(0u, 0u, 0u, 0u);
+            // (the swizzle permutes 16-byte pieces inside a row: clearing whole rows needs no address math)
+            for (int i = tid; i < RF_PAGE * HALVES * 8; i += DEC_THREADS) {
+                const int row = (i >> 3) % RF_PAGE, h = i / (RF_PAGE * 8);
+                if (row < k_begin || row > k_last)
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(v_t + h * HALF_BYTES + row * 128 + (i & 7) * 16),
+                                 "r"(0u) : "memory");
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncthreads();
         }
-        // ---- scores of this warp's 16 keys: two tiles of 8
+        // ---- scores of this warp's 16 keys: two tiles of 8, both from one ldmatrix.x4 per 16 dimensions
         const int kb = warp * 16;
         float sc[2][4];
 #pragma unroll
@@ -429,16 +450,22 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, int q_strid
         const bool warp_active = kb <= k_last && kb + 15 >= k_begin;
         if (warp_active) {
 #pragma unroll
-            for (int ks = 0; ks < HD / 16; ++ks)
-#pragma unroll
-                for (int nt = 0; nt < 2; ++nt) {
-                    const __nv_bfloat16* kr = k_s + (kb + nt * 8 + gid) * HD + ks * 16 + tig * 2;
-                    const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kr);
-                    const uint32_t b1 = *reinterpret_cast<const uint32_t*>(kr + 8);
-                    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                                 : "+f"(sc[nt][0]), "+f"(sc[nt][1]), "+f"(sc[nt][2]), "+f"(sc[nt][3])
-                                 : "r"(qa[ks][0]), "r"(0u), "r"(qa[ks][1]), "r"(0u), "r"(b0), "r"(b1));
-                }
+            for (int ks = 0; ks < HD / 16; ++ks) {
+                // matrices: (keys kb + 0..7, dims ks*16 + 0..7), (same keys, dims + 8), (keys + 8, dims), (keys + 8, dims + 8)
+                const int mi = lane >> 3, r = lane & 7;
+                const int krow = kb + (mi >> 1) * 8 + r;
+                const int gc = ks * 2 + (mi & 1);                                  // 16-byte chunk along the row
+                const uint32_t a = k_t + (gc >> 3) * HALF_BYTES + krow * 128 + (((gc & 7) ^ (krow & 7)) << 4);
+                uint32_t b0, b1, b2, b3;
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(a));
+                asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                             : "+f"(sc[0][0]), "+f"(sc[0][1]), "+f"(sc[0][2]), "+f"(sc[0][3])
+                             : "r"(qa[ks][0]), "r"(0u), "r"(qa[ks][1]), "r"(0u), "r"(b0), "r"(b1));
+                asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                             : "+f"(sc[1][0]), "+f"(sc[1][1]), "+f"(sc[1][2]), "+f"(sc[1][3])
+                             : "r"(qa[ks][0]), "r"(0u), "r"(qa[ks][1]), "r"(0u), "r"(b2), "r"(b3));
+            }
         }
         float mx = -INFINITY;
 #pragma unroll
@@ -474,10 +501,11 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, int q_strid
 #pragma unroll
             for (int nt = 0; nt < HD / 8; nt += 2) {
                 const int mi = lane >> 3, r = lane & 7;
-                const __nv_bfloat16* vr = v_s + (kb + (mi & 1) * 8 + r) * HD + (nt + (mi >> 1)) * 8;
+                const int vrow = kb + (mi & 1) * 8 + r, gc = nt + (mi >> 1);
+                const uint32_t va = v_t + (gc >> 3) * HALF_BYTES + vrow * 128 + (((gc & 7) ^ (vrow & 7)) << 4);
                 uint32_t v0, v1, v2, v3;
                 asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                             : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3) : "r"(dec_smem_u32(vr)));
+                             : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3) : "r"(va));
                 float d0[4] = {oc[nt][0], oc[nt][1], 0.f, 0.f}, d1[4] = {oc[nt + 1][0], oc[nt + 1][1], 0.f, 0.f};
                 asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                              : "+f"(d0[0]), "+f"(d0[1]), "+f"(d0[2]), "+f"(d0[3])
@@ -521,7 +549,7 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, int q_strid
         // Bring the peers' states (max | sum | output, contiguous) into this CTA's memory first: batches of
         // independent 16-byte remote loads, so that their latencies overlap instead of adding up.
         constexpr int STATE4 = (2 * DEC_GP + DEC_GP * HD) / 4;            // float4 per CTA state
-        float4* stage = reinterpret_cast<float4*>(dec_smem);                // [splits - 1][STATE4], over the ring
+        float4* stage = reinterpret_cast<float4*>(ring);                    // [splits - 1][STATE4], over the ring
         const int total = (splits - 1) * STATE4;
         for (int i0 = tid; i0 < total; i0 += DEC_THREADS * 4) {
             float4 v[4];
@@ -563,18 +591,47 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, int q_strid
     if (gave_up && tid == 0 && status) atomicExch(status, 5);
 }
 
+// pages [n_pages, nkv, 64, hd] seen as a matrix [n_pages * nkv * 64, hd]; box = 64 rows x 64 columns, 128-byte swizzle
+typedef CUresult (*DecEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static int dec_make_map(CUtensorMap* map, const void* pages, long long rows, int hd) {
+    static DecEncodeFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qr) != cudaSuccess ||
+            qr != cudaDriverEntryPointSuccess)
+            return RF_ERR_UNSUPPORTED;
+        fn = reinterpret_cast<DecEncodeFn>(ptr);
+    }
+    if (reinterpret_cast<uintptr_t>(pages) & 15) return RF_ERR_BAD_ARG;
+    cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
+    cuuint32_t box[2] = {64, 64};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pages), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : RF_ERR_BAD_ARG;
+}
+
 template <int EPL>
 static int launch_cluster(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
-                          const void* v_pages, const int* tok_seq, const int* tok_pos, const int* seq_slot,
+                          const void* v_pages, long long n_pages, const int* tok_seq, const int* tok_pos, const int* seq_slot,
                           const int* block_table, int max_pages, int nh, int nkv, float scale, int window, int B,
-                          int splits, int* status, cudaStream_t st) {
+                          int splits, int stages, int* status, cudaStream_t st) {
     constexpr int HD = EPL * 32;
-    const size_t smem = (size_t)DCL_STAGES * 2 * RF_PAGE * HD * 2 +
-                        (size_t)(2 * DEC_GP + DEC_GP * HD) * sizeof(float) + DCL_STAGES * 8 + 16;
+    auto bytes = [](int n) {
+        return (size_t)n * 2 * RF_PAGE * HD * 2 + (size_t)(2 * DEC_GP + DEC_GP * HD) * sizeof(float) + DCL_MAX_STAGES * 8 + 16 + 1024;
+    };
+    while (stages > 2 && bytes(stages) > 200 * 1024) --stages;        // head_dim 256: fewer stages fit
+    const size_t smem = bytes(stages);
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_decode_cluster_kernel<EPL>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(200 * 1024));
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
@@ -597,10 +654,13 @@ static int launch_cluster(const void* q, int q_stride, void* out, int out_stride
     }
     cfg.attrs = attr;
     cfg.numAttrs = n;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, attention_decode_cluster_kernel<EPL>,
-        reinterpret_cast<const __nv_bfloat16*>(q), q_stride, reinterpret_cast<__nv_bfloat16*>(out), out_stride,
-        reinterpret_cast<const __nv_bfloat16*>(k_pages), reinterpret_cast<const __nv_bfloat16*>(v_pages), tok_seq,
-        tok_pos, seq_slot, block_table, max_pages, nh, nkv, scale, window, splits, status);
+    CUtensorMap mk, mv;
+    int me;
+    if ((me = dec_make_map(&mk, k_pages, n_pages * nkv * RF_PAGE, HD)) || (me = dec_make_map(&mv, v_pages, n_pages * nkv * RF_PAGE, HD)))
+        return me;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, attention_decode_cluster_kernel<EPL>, mk, mv,
+        reinterpret_cast<const __nv_bfloat16*>(q), q_stride, reinterpret_cast<__nv_bfloat16*>(out), out_stride, tok_seq,
+        tok_pos, seq_slot, block_table, max_pages, nh, nkv, scale, window, splits, stages, status);
     if (e != cudaSuccess) return (int)e;
     RF_LAUNCH_CHECK();
     return 0;
@@ -649,16 +709,20 @@ void rf_attention_decode_scratch(int B, int nh, int nkv, int hd, int max_chunks,
 }
 
 // The clustered variant: `splits` (1, 2, 4 or 8) CTAs share a (sequence, kv head); no scratch memory.
+// `stages` (2..6) pages of keys and values are in flight per CTA: 3 lets two CTAs share an SM (many
+// sequences), 6 hides the copy latency when a single CTA walks a whole context (few sequences).
 int rf_attention_decode_cluster(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
-                                const void* v_pages, const int* tok_seq, const int* tok_pos, const int* seq_slot,
+                                const void* v_pages, long long n_pages, const int* tok_seq, const int* tok_pos,
+                                const int* seq_slot,
                                 const int* block_table, int max_pages, int nh, int nkv, int hd, float scale,
-                                int window, int B, int splits, int* status, cudaStream_t st) {
+                                int window, int B, int splits, int stages, int* status, cudaStream_t st) {
     if (B <= 0) return 0;
     if (!rf_attention_decode_supported(nh, nkv, hd) || B > 65535) return RF_ERR_UNSUPPORTED;
+    if (stages < 2 || stages > DCL_MAX_STAGES) return RF_ERR_BAD_ARG;
     if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return RF_ERR_BAD_ARG;
     if ((reinterpret_cast<uintptr_t>(q) & 15) || (q_stride * 2) % 16) return RF_ERR_BAD_ARG;
-#define GOC(EPL) return launch_cluster<EPL>(q, q_stride, out, out_stride, k_pages, v_pages, tok_seq, tok_pos, seq_slot, \
-                                            block_table, max_pages, nh, nkv, scale, window, B, splits, status, st)
+#define GOC(EPL) return launch_cluster<EPL>(q, q_stride, out, out_stride, k_pages, v_pages, n_pages, tok_seq, tok_pos, seq_slot, \
+                                            block_table, max_pages, nh, nkv, scale, window, B, splits, stages, status, st)
     if (hd == 64) GOC(2);
     if (hd == 128) GOC(4);
     GOC(8);

@@ -28,9 +28,6 @@ class Options:
 class StepContext:
     """Device arrays of the batch and the kernel dispatch for one step."""
 
-    WALK_DECODE_MIN_PAIRS = 128        # batch * kv heads from which one CTA per pair fills the GPU
-    WALK_DECODE_LIMIT = 4096           # keys a single CTA walks page by page before chunking pays again
-
     def __init__(self, model, views, *, T: int, B: int, R: int, is_decode: bool, max_new: int, max_end: int,
                  host=None):
         self.model = model
@@ -128,13 +125,13 @@ class StepContext:
         longest = self.model_cache_limit if self.replayed else self.max_end
         if (self.is_decode and self.compute_dtype == torch.bfloat16 and self.options.tuned_attention
                 and kernels.attention_decode_supported(nh, nkv, hd)):
-            if self.B * nkv >= self.WALK_DECODE_MIN_PAIRS and longest <= self.WALK_DECODE_LIMIT:
-                # many (sequence, kv head) pairs: one CTA each walks the whole context, nothing to merge
-                # (measured at 7B shape, batch 64: 10 % faster per step than the chunked kernel below;
-                # clusters of 2..8 CTAs merging through distributed shared memory were not faster at any batch)
-                return kernels.attention_decode_cluster(q, nh, nkv, hd, view.k_pages, view.v_pages, self.tok_seq,
-                                                        self.tok_pos, self.seq_slot, view.block_table, mixer.scale,
-                                                        view.window, splits=1)
+            if kernels.decode_walks(self.B, nkv, longest, view.window):
+                # a cluster of 1..8 CTAs per (sequence, kv head) walks the pages and merges through
+                # distributed shared memory: no scratch memory, no second pass
+                return kernels.attention_decode_cluster(
+                    q, nh, nkv, hd, view.k_pages, view.v_pages, self.tok_seq, self.tok_pos, self.seq_slot,
+                    view.block_table, mixer.scale, view.window,
+                    splits=kernels.decode_splits(self.B, nkv, longest, view.window))
             if longest <= kernels.DECODE_CHUNK * kernels.DECODE_CHUNK:
                 # long contexts: one CTA per 128-key chunk, partial results merged through scratch memory
                 need = max(1, (longest + kernels.DECODE_CHUNK - 1) // kernels.DECODE_CHUNK)

@@ -264,13 +264,16 @@ def test_attention_decode(nh, nkv, hd, window):
                                     scale, window)
     torch.testing.assert_close(out.float(), gen.float(), atol=2e-2, rtol=2e-2)
     # the clustered variant: every cluster size, the same answers
-    for splits in (1, 2, 4, 8):
+    for splits, stages in ((1, 3), (1, 6), (2, 2), (4, 3), (8, 4)):
         out = kernels.attention_decode_cluster(q.to(DEV), nh, nkv, hd, k_pages, v_pages, tok_seq, tok_pos, seq_slot,
-                                               table, scale, window, splits=splits)
+                                               table, scale, window, splits=splits, stages=stages)
         assert torch.isfinite(out.float()).all()
         for b in range(B):
             torch.testing.assert_close(out[b].cpu().double().view(nh, hd), refs[b], atol=2e-2, rtol=2e-2)
-    assert kernels.decode_splits(1, 4) == 8 and kernels.decode_splits(64, 4) == 2 and kernels.decode_splits(512, 8) == 1
+    assert kernels.decode_splits(1, 4) == 8 and kernels.decode_splits(8, 4) == 4 and kernels.decode_splits(64, 4) == 1
+    assert kernels.decode_splits(1, 4, longest=100) == 2 and kernels.decode_splits(1, 4, 4096, window=128) == 2
+    assert kernels.decode_walks(8, 4, 2048, None) and not kernels.decode_walks(1, 4, 16384, None)
+    assert kernels.decode_walks(1, 4, 1 << 20, 1024)            # a window bounds the pages whatever the length
 
 
 def test_attention_decode_finds_far_keys_and_the_window_edge():
