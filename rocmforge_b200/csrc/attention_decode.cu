@@ -370,7 +370,6 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k, const
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
     }
     __syncthreads();
-    pdl_wait();                                         // queries and the newest keys/values come from the kernel before us
 
     auto issue = [&](int k) {                           // thread 0: page p_lo + rank + k*splits into stage k % stages
         const int stage = k % stages;
@@ -386,8 +385,14 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k, const
                          ::"r"(dst + SLAB + h * HALF_BYTES), "l"(&map_v), "r"(h * 64), "r"(row), "r"(bar) : "memory");
         }
     };
+    // Only the page of the newest position is written in this step (by the kernel before this one); the
+    // older pages were written by earlier steps, which are complete: their copies start before the wait.
+    int early = 0;
     if (tid == 0)
-        for (int k = 0; k < n_my && k < stages - 1; ++k) issue(k);
+        for (; early < n_my && early < stages - 1 && p_lo + rank + early * splits < p_hi; ++early) issue(early);
+    pdl_wait();                                         // queries and the newest keys/values come from the kernel before us
+    if (tid == 0)
+        for (int k = early; k < n_my && k < stages - 1; ++k) issue(k);
 
     uint32_t qa[HD / 16][2];
 #pragma unroll

@@ -77,6 +77,20 @@ add_rmsnorm_vec_kernel(float* __restrict__ h, const void* __restrict__ pending, 
     const int r = blockIdx.x;
     const int t = rows ? rows[r] : r;
     const int nvec = H >> 2;
+    uint4 wraw[NV];                              // the norm's weights (four floats, or four bfloat16 in x and y):
+#pragma unroll                                   // no kernel writes them, so they are fetched while the kernel
+    for (int i = 0; i < NV; ++i) {               // before this one still runs
+        const int c = threadIdx.x + i * blockDim.x;
+        wraw[i] = make_uint4(0u, 0u, 0u, 0u);
+        if (c < nvec) {
+            if (w_is_f32) {
+                wraw[i] = reinterpret_cast<const uint4*>(w)[c];
+            } else {
+                const uint2 two = reinterpret_cast<const uint2*>(w)[c];
+                wraw[i].x = two.x; wraw[i].y = two.y;
+            }
+        }
+    }
     pdl_wait();
     float4* hrow = reinterpret_cast<float4*>(h + (size_t)t * H);
     float4 v[NV];
@@ -109,8 +123,16 @@ add_rmsnorm_vec_kernel(float* __restrict__ h, const void* __restrict__ pending, 
         const int c = threadIdx.x + i * blockDim.x;
         if (c < nvec) {
             if (!rows && pending_kind != 0) hrow[c] = v[i];
-            const float o0 = v[i].x * inv * load_vec(w, w_is_f32, 4 * c), o1 = v[i].y * inv * load_vec(w, w_is_f32, 4 * c + 1);
-            const float o2 = v[i].z * inv * load_vec(w, w_is_f32, 4 * c + 2), o3 = v[i].w * inv * load_vec(w, w_is_f32, 4 * c + 3);
+            float w0, w1, w2, w3;
+            if (w_is_f32) {
+                w0 = __uint_as_float(wraw[i].x); w1 = __uint_as_float(wraw[i].y);
+                w2 = __uint_as_float(wraw[i].z); w3 = __uint_as_float(wraw[i].w);
+            } else {                             // a bfloat16 is the upper half of a float
+                w0 = __uint_as_float(wraw[i].x << 16); w1 = __uint_as_float(wraw[i].x & 0xffff0000u);
+                w2 = __uint_as_float(wraw[i].y << 16); w3 = __uint_as_float(wraw[i].y & 0xffff0000u);
+            }
+            const float o0 = v[i].x * inv * w0, o1 = v[i].y * inv * w1;
+            const float o2 = v[i].z * inv * w2, o3 = v[i].w * inv * w3;
             T* o = yrow + 4 * c;
             o[0] = Cvt<T>::from_f32(o0); o[1] = Cvt<T>::from_f32(o1);
             o[2] = Cvt<T>::from_f32(o2); o[3] = Cvt<T>::from_f32(o3);
@@ -135,8 +157,10 @@ __global__ void rope_kv_write_kernel(const void* __restrict__ src, int row_strid
                                      T* __restrict__ k_pages, T* __restrict__ v_pages, int write_kv) {
     // grid: (token, block of pairs).  Pair index space: nh + nkv rotated heads, then nkv value heads,
     // hd/2 pairs each (a value "pair" is two neighbouring elements, copied).
+    // Position, slot, page, frequency, bias and the angle's sine and cosine do not depend on the kernel
+    // before this one (no kernel of a step writes them): all of that is done before pdl_wait(), so that
+    // after it only the loads of the product's sums and the stores remain.
     pdl_trigger();
-    pdl_wait();
     const int t = blockIdx.x;
     const int half = hd >> 1;
     const int idx = blockIdx.y * blockDim.x + threadIdx.x;
@@ -145,26 +169,33 @@ __global__ void rope_kv_write_kernel(const void* __restrict__ src, int row_strid
     const int head = idx / half, i = idx - head * half;
     if (head >= nh && !write_kv) return;
     const int pos = tok_pos[t];
-    auto value = [&](int col) -> float {
-        if (PARTIALS) {
-            const float* p = reinterpret_cast<const float*>(src) + (size_t)t * row_stride + col;
-            float v = bias ? load_vec(bias, bias_is_f32, col) : 0.f;
-            for (int s = 0; s < n_partials; ++s) v += p[(size_t)s * partial_stride];
-            return v;
-        }
-        return Cvt<T>::to_f32(reinterpret_cast<const T*>(src)[(size_t)t * row_stride + col]);
-    };
+    const bool rotated = head < nh + nkv;
+    const int col0 = rotated ? head * hd + i : head * hd + 2 * i;
+    const int col1 = rotated ? col0 + half : col0 + 1;
+    float b0 = 0.f, b1 = 0.f;
+    if (PARTIALS && bias) { b0 = load_vec(bias, bias_is_f32, col0); b1 = load_vec(bias, bias_is_f32, col1); }
     size_t page_base = 0;
     if (head >= nh) {
         const int slot = seq_slot[tok_seq[t]];
         const int page = block_table[(size_t)slot * max_pages + pos / RF_PAGE];
         page_base = (size_t)page * nkv * RF_PAGE * hd + (size_t)(pos % RF_PAGE) * hd;
     }
-    if (head < nh + nkv) {
-        const float angle = (float)pos * inv_freq[i];
-        float s, c;
-        sincosf(angle, &s, &c);
-        const float x0 = value(head * hd + i), x1 = value(head * hd + i + half);
+    float s = 0.f, c = 1.f;
+    if (rotated) sincosf((float)pos * inv_freq[i], &s, &c);
+    pdl_wait();
+    float x0, x1;
+    if (PARTIALS) {
+        const float* p = reinterpret_cast<const float*>(src) + (size_t)t * row_stride;
+        x0 = b0; x1 = b1;
+        for (int sp = 0; sp < n_partials; ++sp) {       // in index order
+            x0 += p[(size_t)sp * partial_stride + col0];
+            x1 += p[(size_t)sp * partial_stride + col1];
+        }
+    } else {
+        x0 = Cvt<T>::to_f32(reinterpret_cast<const T*>(src)[(size_t)t * row_stride + col0]);
+        x1 = Cvt<T>::to_f32(reinterpret_cast<const T*>(src)[(size_t)t * row_stride + col1]);
+    }
+    if (rotated) {
         const float r0 = x0 * c - x1 * s, r1 = x0 * s + x1 * c;
         T* dst = head < nh ? q_out + (size_t)t * q_out_stride + (size_t)head * hd
                            : k_pages + page_base + (size_t)(head - nh) * RF_PAGE * hd;
@@ -173,8 +204,8 @@ __global__ void rope_kv_write_kernel(const void* __restrict__ src, int row_strid
     } else {
         const int vh = head - nh - nkv;
         T* dst = v_pages + page_base + (size_t)vh * RF_PAGE * hd;
-        dst[2 * i] = Cvt<T>::from_f32(value(head * hd + 2 * i));
-        dst[2 * i + 1] = Cvt<T>::from_f32(value(head * hd + 2 * i + 1));
+        dst[2 * i] = Cvt<T>::from_f32(x0);
+        dst[2 * i + 1] = Cvt<T>::from_f32(x1);
     }
 }
 
@@ -209,7 +240,8 @@ static int launch_add_rmsnorm(float* h, const void* pending, int kind, int n_pen
                               int n_rows, int H, cudaStream_t st) {
     if (n_rows <= 0) return 0;
     if (H % 4 == 0 && H <= 4 * 4 * 1024 && (pstride % 4) == 0 &&
-        !(reinterpret_cast<uintptr_t>(h) & 15) && !(kind == 1 && (reinterpret_cast<uintptr_t>(pending) & 15))) {
+        !(reinterpret_cast<uintptr_t>(h) & 15) && !(reinterpret_cast<uintptr_t>(w) & 15) &&
+        !(kind == 1 && (reinterpret_cast<uintptr_t>(pending) & 15))) {
         const int nvec = H / 4;
         // few rows (decode): one 16-byte vector per thread, the shortest chain per row;
         // many rows (prompts): 256 threads a row, so that eight rows per SM are in flight
