@@ -285,22 +285,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
     if (tid == 0) counters[b * nkv + kvh] = 0;          // ready for the next launch
 }
 
-// ---------------------------------------------------------------- the clustered variant
-// For contexts of ordinary length the merge through global memory above costs more than the attention
-// itself (write partials, fence, count arrivals, fence, read them back: five trips to L2).  Here the
-// CTAs that share a (sequence, kv head) form a thread-block cluster of `splits` CTAs instead.  CTA r
-// walks the pages r, r + splits, r + 2*splits, ... of the context with a ring of TMA copies (128-byte
-// swizzle, so that ldmatrix reads the key and value fragments without bank conflicts; with plain
-// 256-byte rows the fragment loads were 8-way conflicted and took most of a page's time); each warp
-// owns 16 of a page's 64 keys and keeps its own running maximum, sum and output
-// across pages (the online softmax, as in the prefill kernel), so a page costs one mbarrier wait and
-// one CTA barrier.  At the end the four warps' states are merged in shared memory, and CTA 0 reads its
-// peers' states through distributed shared memory, in rank order, and writes the result.  No scratch
-// memory, no atomics; the launch shape depends on the batch alone, so a captured graph stays valid
-// while the context grows.
-#define DCL_MAX_STAGES 6
-#define DCL_MAX_PAGES 256             // pages one CTA may walk (16,384 keys)
-
+// ---------------------------------------------------------------- thread-block clusters
 __device__ __forceinline__ uint32_t dcl_cluster_rank() {
     uint32_t r;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -310,38 +295,58 @@ __device__ __forceinline__ void dcl_cluster_sync() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-__device__ __forceinline__ float dcl_ld_remote(const float* local, uint32_t rank) {
-    uint32_t raddr;
-    float v;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr) : "r"(dec_smem_u32(local)), "r"(rank));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(raddr) : "memory");
-    return v;
-}
 
-template <int EPL>
-__global__ void __launch_bounds__(DEC_THREADS)
-attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
-                                const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* __restrict__ out,
-                                int out_stride, const int* __restrict__ tok_seq,
-                                const int* __restrict__ tok_pos, const int* __restrict__ seq_slot,
-                                const int* __restrict__ block_table, int max_pages, int nh, int nkv, float scale,
-                                int window, int splits, int stages, int* __restrict__ status) {
+// ---------------------------------------------------------------- a warp per tile of keys
+// For contexts of ordinary length the merge through global memory above costs more than the attention
+// itself (write partials, fence, count arrivals, fence, read them back: five trips to L2).  Here the CTAs
+// that share a (sequence, kv head) form a thread-block cluster of `splits` CTAs; CTA r takes the pages
+// r, r + splits, ... of the context, brought in by TMA with the 128-byte swizzle so that ldmatrix reads
+// them without bank conflicts.  No scratch memory, no atomics; the launch shape depends on the batch
+// alone, so a captured graph stays valid while the context grows.  Inside a CTA every warp works alone: the
+// CTA's pages are cut into tiles of ROWS keys, warp w takes the tiles w, w + WARPS, ... and has a buffer for
+// one tile of keys and one of values, each with its own mbarrier.  A warp computes all scores of a tile,
+// releases the key buffer to the copy of its next tile, rescales once per tile and multiplies by the values,
+// then releases the value buffer: the copy of the next keys runs under the value product and the copy
+// of the next values under the next score product, and no barrier of the whole CTA lies on the way.  With
+// contexts of a few hundred keys every warp has one tile, all copies are in flight at once (those of pages
+// older than the newest position even before the kernel ahead of this one has finished).
+//
+// mma.sync is the slow tensor path of this GPU, so the products are turned to need as few of them as
+// possible: the 16 rows of an instruction hold keys (scores, S^T = K Q^T) or output dimensions (O^T = V^T P^T)
+// and its 8 columns the up to 8 query heads of the kv head, instead of 16 rows of which 7 or 8 are heads.
+// K is the A operand as it lies in shared memory, V^T comes from ldmatrix.trans, Q^T is the B operand straight
+// from the query's registers, and P^T becomes a B operand by transposing the 8x8 blocks of the score
+// accumulators with movmatrix.  A thread then holds two heads' running maximum and sum.
+//
+// The merge: warps leave their states in shared memory, the CTA folds them, and every CTA pushes to each peer
+// the slice of output dimensions that this peer owns (remote stores into a slot per sender); after ONE cluster
+// barrier each CTA folds the slots of its slice in rank order and writes it.  No CTA reads a peer's memory,
+// so none has to wait for its peers before it exits.
+template <int EPL, int ROWS, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32)
+attention_decode_warps_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                              const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* __restrict__ out,
+                              int out_stride, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                              const int* __restrict__ seq_slot, const int* __restrict__ block_table, int max_pages,
+                              int nh, int nkv, float scale, int window, int splits, int* __restrict__ status) {
     constexpr int HD = EPL * 32;
-    constexpr uint32_t SLAB = RF_PAGE * HD * 2;                 // one page's keys (or values) of one kv head
+    constexpr int NT = WARPS * 32;
     constexpr int HALVES = HD / 64;                             // 128-byte column blocks of a row
-    constexpr uint32_t HALF_BYTES = RF_PAGE * 128;              // one column block of a page: [64 rows][128 B], swizzled
+    constexpr uint32_t HALF_BYTES = ROWS * 128;                 // one column block of a tile: [ROWS][128 B], swizzled
+    constexpr uint32_t TILE = ROWS * HD * 2;                    // a tile's keys (or values)
+    constexpr int UPP = RF_PAGE / ROWS;                         // tiles per page
+    constexpr int NB = ROWS / 16;                               // blocks of 16 keys per tile
+    constexpr int SP = HD + 4;                                  // floats between two heads of a warp's state
+    static_assert(HALF_BYTES % 1024 == 0, "a column block must keep the swizzle pattern's 1024-byte period");
+    static_assert((2 * DEC_GP + DEC_GP * SP) * 4 <= 2 * TILE, "a warp's state lies where its tiles lay");
     extern __shared__ __align__(1024) uint8_t dec_smem[];
-    // the swizzle pattern is a function of the address: the ring starts on a 1024-byte boundary (the same in every CTA)
-    uint8_t* ring = dec_smem + ((1024u - (dec_smem_u32(dec_smem) & 1023u)) & 1023u);    // [stage][K | V][HALVES][64][128 B]
-    float* w_m = reinterpret_cast<float*>(ring);                                       // [4 warps][GP]: over the ring,
-    float* w_l = w_m + DEC_WARPS * DEC_GP;                                              // [4][GP]        once the last
-    float* w_o = w_l + DEC_WARPS * DEC_GP;                                              // [4][GP][HD]    page is done
-    float* c_m = reinterpret_cast<float*>(ring + (size_t)stages * 2 * SLAB);            // this CTA: [GP]
+    uint8_t* ring = dec_smem + ((1024u - (dec_smem_u32(dec_smem) & 1023u)) & 1023u);    // [warp][K | V][HALVES][ROWS][128 B]
+    float* f_w = reinterpret_cast<float*>(ring + (size_t)WARPS * 2 * TILE);             // [WARPS][GP] weights of the warps
+    float* c_m = f_w + WARPS * DEC_GP;                                                  // this CTA: [GP]
     float* c_l = c_m + DEC_GP;                                                          // [GP]
-    float* c_o = c_l + DEC_GP;                                                          // [GP][HD]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(c_o + DEC_GP * HD);                   // [stages]
+    float* slots = c_l + DEC_GP;                                // [splits][2*GP + GP * HD/splits]: what the peers push
+    uint64_t* bars = reinterpret_cast<uint64_t*>(slots + splits * 2 * DEC_GP + DEC_GP * HD);     // [warp][K | V]
     __shared__ int gave_up;
-    __shared__ int page_of[DCL_MAX_PAGES];              // this CTA's pages, read from the block table once
 
     pdl_trigger();
     const int G = nh / nkv;
@@ -352,247 +357,264 @@ attention_decode_cluster_kernel(const __grid_constant__ CUtensorMap map_k, const
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     const int p_lo = lo / RF_PAGE, p_hi = pos / RF_PAGE;
     const int n_my = (p_hi - p_lo - rank) >= 0 ? (p_hi - p_lo - rank) / splits + 1 : 0;     // pages of this CTA
+    const int n_units = n_my * UPP;
     const int* bt = block_table + (size_t)seq_slot[tok_seq[b]] * max_pages;
-    if (p_hi - p_lo + 1 > DCL_MAX_PAGES * splits) {     // more pages than a CTA's table holds: the same verdict in
-        if (tid == 0 && status) atomicExch(status, 7);  // every CTA of the cluster; the caller bounds the context
-        return;
-    }
-    // the block table is not written by any kernel of the step: fetch this CTA's entries now, all at once,
-    // instead of one dependent global load per page on the copy-issuing thread's critical path
-    for (int k = tid; k < n_my && k < DCL_MAX_PAGES; k += DEC_THREADS) page_of[k] = bt[p_lo + rank + k * splits];
+    uint8_t* my_k = ring + (size_t)warp * 2 * TILE;
+    const uint32_t k_t = dec_smem_u32(my_k), v_t = k_t + TILE;
+    const uint32_t bar_k = dec_smem_u32(&bars[warp * 2]), bar_v = bar_k + 8;
 
-    if (tid == 0) {
-        gave_up = 0;
-        for (int s = 0; s < stages; ++s)
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(dec_smem_u32(&bars[s])));
+    if (tid == 0) gave_up = 0;
+    if (lane == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_k));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_v));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
     }
     __syncthreads();
 
-    auto issue = [&](int k) {                           // thread 0: page p_lo + rank + k*splits into stage k % stages
-        const int stage = k % stages;
-        const uint32_t bar = dec_smem_u32(&bars[stage]);
-        const int row = (page_of[k] * nkv + kvh) * RF_PAGE;      // first row of the page in the [pages*kv*64, HD] view
-        const uint32_t dst = dec_smem_u32(ring + (size_t)stage * 2 * SLAB);
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(2 * SLAB) : "memory");
-#pragma unroll
-        for (int h = 0; h < HALVES; ++h) {
-            asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                         ::"r"(dst + h * HALF_BYTES), "l"(&map_k), "r"(h * 64), "r"(row), "r"(bar) : "memory");
-            asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                         ::"r"(dst + SLAB + h * HALF_BYTES), "l"(&map_v), "r"(h * 64), "r"(row), "r"(bar) : "memory");
+    // tile u of this CTA: page p_lo + rank + (u / UPP) * splits, rows (u % UPP) * ROWS ... of it
+    auto first_key = [&](int u) { return (p_lo + rank + (u / UPP) * splits) * RF_PAGE + (u % UPP) * ROWS; };
+    auto next_tile = [&](int u) {                     // the next of this warp's tiles that holds a key in [lo, pos]
+        for (u += WARPS; u < n_units; u += WARPS) {
+            const int k0 = first_key(u);
+            if (k0 <= pos && k0 + ROWS - 1 >= lo) break;
         }
+        return u;
     };
-    // Only the page of the newest position is written in this step (by the kernel before this one); the
-    // older pages were written by earlier steps, which are complete: their copies start before the wait.
-    int early = 0;
-    if (tid == 0)
-        for (; early < n_my && early < stages - 1 && p_lo + rank + early * splits < p_hi; ++early) issue(early);
-    pdl_wait();                                         // queries and the newest keys/values come from the kernel before us
-    if (tid == 0)
-        for (int k = early; k < n_my && k < stages - 1; ++k) issue(k);
-
-    uint32_t qa[HD / 16][2];
+    auto issue = [&](int u, bool keys) {              // lane 0: the keys or the values of tile u into this warp's buffer
+        const int page = bt[p_lo + rank + (u / UPP) * splits];
+        const int row = (page * nkv + kvh) * RF_PAGE + (u % UPP) * ROWS;
+        const uint32_t bar = keys ? bar_k : bar_v, dst = keys ? k_t : v_t;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(TILE) : "memory");
 #pragma unroll
-    for (int ks = 0; ks < HD / 16; ++ks) {
-        qa[ks][0] = qa[ks][1] = 0u;
-        if (gid < G) {
-            const __nv_bfloat16* qrow = q + (size_t)b * q_stride + (size_t)(kvh * G + gid) * HD + ks * 16 + tig * 2;
-            qa[ks][0] = *reinterpret_cast<const uint32_t*>(qrow);
-            qa[ks][1] = *reinterpret_cast<const uint32_t*>(qrow + 8);
-        }
-    }
-    float oc[HD / 8][2];                                 // this thread: head gid, dims nt*8 + tig*2 + {0,1}
-#pragma unroll
-    for (int nt = 0; nt < HD / 8; ++nt) oc[nt][0] = oc[nt][1] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
-
-    for (int k = 0; k < n_my; ++k) {
-        const int stage = k % stages;
-        if (tid == 0 && k + stages - 1 < n_my) issue(k + stages - 1);              // its stage was released by the last sync
-        {
-            const uint32_t bar = dec_smem_u32(&bars[stage]);
-            const uint32_t parity = (k / stages) & 1;
-            uint32_t ok = 0;
-            unsigned long long t0 = 0;
-            for (long long it = 0; !ok; ++it) {
-                asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-                             "selp.u32 %0, 1, 0, p;\n\t}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-                if (ok) break;
-                if ((it & 63) == 63) {
-                    unsigned long long now;
-                    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-                    if (t0 == 0) t0 = now;
-                    if (now - t0 > DEC_WAIT_LIMIT_NS || gave_up) { gave_up = 1; break; }
-                }
+        for (int h = 0; h < HALVES; ++h)
+            asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                         ::"r"(dst + h * HALF_BYTES), "l"(keys ? &map_k : &map_v), "r"(h * 64), "r"(row), "r"(bar) : "memory");
+    };
+    auto wait = [&](uint32_t bar, uint32_t parity) -> bool {          // bounded; the whole warp gets one verdict
+        uint32_t ok = 0;
+        unsigned long long t0 = 0;
+        for (long long it = 0; !ok; ++it) {
+            asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                         "selp.u32 %0, 1, 0, p;\n\t}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+            if (ok) break;
+            if ((it & 63) == 63) {
+                unsigned long long now;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+                if (t0 == 0) t0 = now;
+                if (now - t0 > DEC_WAIT_LIMIT_NS) break;
             }
         }
-        __syncthreads();                                 // one verdict for everyone
-        if (gave_up) break;
-        const uint32_t k_t = dec_smem_u32(ring + (size_t)stage * 2 * SLAB), v_t = k_t + SLAB;
-        const int key0 = (p_lo + rank + k * splits) * RF_PAGE;
-        int k_begin = lo - key0; if (k_begin < 0) k_begin = 0;                    // valid rows of this page
-        int k_last = pos - key0; if (k_last > RF_PAGE - 1) k_last = RF_PAGE - 1;
-        if (k_begin > 0 || k_last < RF_PAGE - 1) {
+        return __all_sync(0xffffffffu, ok != 0);
+    };
+
+    // Only the page of the newest position is written in this step (by the kernel before this one); the
+    // older pages were written by earlier steps, which are complete: their copies start before the wait.
+    int u = next_tile(warp - WARPS);
+    const bool early = u < n_units && first_key(u) / RF_PAGE < p_hi;
+    if (lane == 0 && early) { issue(u, true); issue(u, false); }
+    pdl_wait();                                         // queries and the newest keys/values come from the kernel before us
+    if (lane == 0 && !early && u < n_units) { issue(u, true); issue(u, false); }
+
+    uint32_t qb[HD / 16][2];                            // Q^T as the B operand: head gid, dims ks*16 + tig*2 (+8)
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+        qb[ks][0] = qb[ks][1] = 0u;
+        if (gid < G) {
+            const __nv_bfloat16* qrow = q + (size_t)b * q_stride + (size_t)(kvh * G + gid) * HD + ks * 16 + tig * 2;
+            qb[ks][0] = *reinterpret_cast<const uint32_t*>(qrow);
+            qb[ks][1] = *reinterpret_cast<const uint32_t*>(qrow + 8);
+        }
+    }
+    // O^T: block mt of 16 dimensions: [0] (dim gid, head tig*2), [1] (dim gid, head tig*2+1), [2], [3] the same for dim gid + 8
+    float oc[HD / 16][4];
+#pragma unroll
+    for (int mt = 0; mt < HD / 16; ++mt) oc[mt][0] = oc[mt][1] = oc[mt][2] = oc[mt][3] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};        // heads tig*2 and tig*2 + 1
+    const int mi = lane >> 3, r8 = lane & 7;
+    bool failed = false;
+
+    for (uint32_t it = 0; u < n_units; ++it) {
+        const int un = next_tile(u);
+        const int key0 = first_key(u);
+        int k_begin = lo - key0; if (k_begin < 0) k_begin = 0;                    // valid rows of this tile
+        int k_last = pos - key0; if (k_last > ROWS - 1) k_last = ROWS - 1;
+        if (!wait(bar_k, it & 1)) { failed = true; break; }
+        // ---- scores, transposed: [0] (key gid, head tig*2), [1] (key gid, head tig*2+1), [2], [3] the same for key gid + 8
+        float sc[NB][4];
+#pragma unroll
+        for (int kb = 0; kb < NB; ++kb) sc[kb][0] = sc[kb][1] = sc[kb][2] = sc[kb][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+#pragma unroll
+            for (int kb = 0; kb < NB; ++kb) {
+                // matrices: (keys + 0..7, dims ks*16 + 0..7), (keys + 8.., same dims), (keys + 0..7, dims + 8), (keys + 8.., dims + 8)
+                const int krow = kb * 16 + (mi & 1) * 8 + r8;
+                const int gc = ks * 2 + (mi >> 1);                                 // 16-byte chunk along the row
+                const uint32_t a = k_t + (gc >> 3) * HALF_BYTES + krow * 128 + (((gc & 7) ^ (krow & 7)) << 4);
+                uint32_t a0, a1, a2, a3;
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3) : "r"(a));
+                asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                             : "+f"(sc[kb][0]), "+f"(sc[kb][1]), "+f"(sc[kb][2]), "+f"(sc[kb][3])
+                             : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(qb[ks][0]), "r"(qb[ks][1]));
+            }
+        }
+        __syncwarp();                                    // every lane has read the keys: the buffer may be refilled
+        if (lane == 0 && un < n_units) issue(un, true);
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int kb = 0; kb < NB; ++kb)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int kk = kb * 16 + gid + (e >> 1) * 8;
+                sc[kb][e] = (kk >= k_begin && kk <= k_last) ? sc[kb][e] * scale : -INFINITY;
+                mx[e & 1] = fmaxf(mx[e & 1], sc[kb][e]);
+            }
+        float corr[2], psum[2] = {0.f, 0.f};
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {                    // the tile's keys lie across the lanes of equal tig
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 4));
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 8));
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 16));
+            const float m_new = fmaxf(m_run[h], mx[h]);  // finite: the tile holds a key of the sequence
+            corr[h] = (m_run[h] == -INFINITY) ? 0.f : expf(m_run[h] - m_new);
+            m_run[h] = m_new;
+        }
+        uint32_t pb[NB][2];                              // P^T as the B operand: head gid, keys tig*2.. (+8) of block kb
+#pragma unroll
+        for (int kb = 0; kb < NB; ++kb) {
+            float p[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                p[e] = sc[kb][e] == -INFINITY ? 0.f : expf(sc[kb][e] - m_run[e & 1]);
+                psum[e & 1] += p[e];
+            }
+            const __nv_bfloat162 lo8 = __floats2bfloat162_rn(p[0], p[1]), hi8 = __floats2bfloat162_rn(p[2], p[3]);
+            // an 8x8 block (row = key gid, columns = heads tig*2, tig*2+1) transposed: row = head gid, columns = keys tig*2, tig*2+1
+            asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(pb[kb][0]) : "r"(*reinterpret_cast<const uint32_t*>(&lo8)));
+            asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(pb[kb][1]) : "r"(*reinterpret_cast<const uint32_t*>(&hi8)));
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            psum[h] += __shfl_xor_sync(0xffffffffu, psum[h], 4);
+            psum[h] += __shfl_xor_sync(0xffffffffu, psum[h], 8);
+            psum[h] += __shfl_xor_sync(0xffffffffu, psum[h], 16);
+            l_run[h] = l_run[h] * corr[h] + psum[h];
+        }
+#pragma unroll
+        for (int mt = 0; mt < HD / 16; ++mt) {
+            oc[mt][0] *= corr[0]; oc[mt][1] *= corr[1]; oc[mt][2] *= corr[0]; oc[mt][3] *= corr[1];
+        }
+        if (!wait(bar_v, it & 1)) { failed = true; break; }
+        if (k_begin > 0 || k_last < ROWS - 1) {
             // rows outside the sequence get weight zero, but 0 * (whatever bits lie there) must be 0
             // (the swizzle permutes 16-byte pieces inside a row: clearing whole rows needs no address math)
-            for (int i = tid; i < RF_PAGE * HALVES * 8; i += DEC_THREADS) {
-                const int row = (i >> 3) % RF_PAGE, h = i / (RF_PAGE * 8);
+            for (int i = lane; i < ROWS * HALVES * 8; i += 32) {
+                const int row = (i >> 3) % ROWS, h = i / (ROWS * 8);
                 if (row < k_begin || row > k_last)
                     asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(v_t + h * HALF_BYTES + row * 128 + (i & 7) * 16),
                                  "r"(0u) : "memory");
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncthreads();
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // before a later copy overwrites them
+            __syncwarp();
         }
-        // ---- scores of this warp's 16 keys: two tiles of 8, both from one ldmatrix.x4 per 16 dimensions
-        const int kb = warp * 16;
-        float sc[2][4];
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt) sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
-        const bool warp_active = kb <= k_last && kb + 15 >= k_begin;
-        if (warp_active) {
+        for (int kb = 0; kb < NB; ++kb) {
+            if (kb * 16 > k_last || kb * 16 + 15 < k_begin) continue;             // a block without a key of the sequence
 #pragma unroll
-            for (int ks = 0; ks < HD / 16; ++ks) {
-                // matrices: (keys kb + 0..7, dims ks*16 + 0..7), (same keys, dims + 8), (keys + 8, dims), (keys + 8, dims + 8)
-                const int mi = lane >> 3, r = lane & 7;
-                const int krow = kb + (mi >> 1) * 8 + r;
-                const int gc = ks * 2 + (mi & 1);                                  // 16-byte chunk along the row
-                const uint32_t a = k_t + (gc >> 3) * HALF_BYTES + krow * 128 + (((gc & 7) ^ (krow & 7)) << 4);
-                uint32_t b0, b1, b2, b3;
-                asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-                             : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(a));
-                asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                             : "+f"(sc[0][0]), "+f"(sc[0][1]), "+f"(sc[0][2]), "+f"(sc[0][3])
-                             : "r"(qa[ks][0]), "r"(0u), "r"(qa[ks][1]), "r"(0u), "r"(b0), "r"(b1));
-                asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                             : "+f"(sc[1][0]), "+f"(sc[1][1]), "+f"(sc[1][2]), "+f"(sc[1][3])
-                             : "r"(qa[ks][0]), "r"(0u), "r"(qa[ks][1]), "r"(0u), "r"(b2), "r"(b3));
-            }
-        }
-        float mx = -INFINITY;
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int kk = kb + nt * 8 + tig * 2 + e;
-                const bool ok = warp_active && kk >= k_begin && kk <= k_last;
-                sc[nt][e] = ok ? sc[nt][e] * scale : -INFINITY;
-                mx = fmaxf(mx, sc[nt][e]);
-            }
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        const float m_new = fmaxf(m_run, mx);
-        const float corr = (m_run == -INFINITY) ? 0.f : expf(m_run - m_new);
-        float psum = 0.f;
-        uint32_t pa[2];
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-            const float p0 = sc[nt][0] == -INFINITY ? 0.f : expf(sc[nt][0] - m_new);
-            const float p1 = sc[nt][1] == -INFINITY ? 0.f : expf(sc[nt][1] - m_new);
-            psum += p0 + p1;
-            const __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
-            pa[nt] = *reinterpret_cast<const uint32_t*>(&pk);
-        }
-        psum += __shfl_xor_sync(0xffffffffu, psum, 1);
-        psum += __shfl_xor_sync(0xffffffffu, psum, 2);
-        l_run = l_run * corr + psum;
-        m_run = m_new;
-#pragma unroll
-        for (int nt = 0; nt < HD / 8; ++nt) { oc[nt][0] *= corr; oc[nt][1] *= corr; }
-        if (warp_active) {
-#pragma unroll
-            for (int nt = 0; nt < HD / 8; nt += 2) {
-                const int mi = lane >> 3, r = lane & 7;
-                const int vrow = kb + (mi & 1) * 8 + r, gc = nt + (mi >> 1);
+            for (int mt = 0; mt < HD / 16; ++mt) {
+                // V^T: matrices (keys + 0..7, dims mt*16 + 0..7), (same keys, dims + 8), (keys + 8.., dims), (keys + 8.., dims + 8)
+                const int vrow = kb * 16 + (mi >> 1) * 8 + r8, gc = mt * 2 + (mi & 1);
                 const uint32_t va = v_t + (gc >> 3) * HALF_BYTES + vrow * 128 + (((gc & 7) ^ (vrow & 7)) << 4);
-                uint32_t v0, v1, v2, v3;
+                uint32_t a0, a1, a2, a3;
                 asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                             : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3) : "r"(va));
-                float d0[4] = {oc[nt][0], oc[nt][1], 0.f, 0.f}, d1[4] = {oc[nt + 1][0], oc[nt + 1][1], 0.f, 0.f};
+                             : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3) : "r"(va));
                 asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                             : "+f"(d0[0]), "+f"(d0[1]), "+f"(d0[2]), "+f"(d0[3])
-                             : "r"(pa[0]), "r"(0u), "r"(pa[1]), "r"(0u), "r"(v0), "r"(v1));
-                asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                             : "+f"(d1[0]), "+f"(d1[1]), "+f"(d1[2]), "+f"(d1[3])
-                             : "r"(pa[0]), "r"(0u), "r"(pa[1]), "r"(0u), "r"(v2), "r"(v3));
-                oc[nt][0] = d0[0]; oc[nt][1] = d0[1]; oc[nt + 1][0] = d1[0]; oc[nt + 1][1] = d1[1];
+                             : "+f"(oc[mt][0]), "+f"(oc[mt][1]), "+f"(oc[mt][2]), "+f"(oc[mt][3])
+                             : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(pb[kb][0]), "r"(pb[kb][1]));
             }
         }
-        __syncthreads();                                 // the stage may be refilled
+        __syncwarp();                                    // the values have been read
+        if (lane == 0 && un < n_units) issue(un, false);
+        u = un;
     }
+    if (failed) gave_up = 1;
 
-    // ---- the four warps' states -> this CTA's state
-    if (tig == 0) { w_m[warp * DEC_GP + gid] = m_run; w_l[warp * DEC_GP + gid] = l_run; }
+    // ---- a warp leaves its state where its tiles lay: max [GP] | sum [GP] | output [GP][SP]
+    {
+        float* st = reinterpret_cast<float*>(my_k);
+        if (gid == 0) {
+            st[tig * 2] = m_run[0]; st[tig * 2 + 1] = m_run[1];
+            st[DEC_GP + tig * 2] = l_run[0]; st[DEC_GP + tig * 2 + 1] = l_run[1];
+        }
+        float* o0 = st + 2 * DEC_GP + (tig * 2) * SP, *o1 = o0 + SP;
 #pragma unroll
-    for (int nt = 0; nt < HD / 8; ++nt) {
-        w_o[(warp * DEC_GP + gid) * HD + nt * 8 + tig * 2] = oc[nt][0];
-        w_o[(warp * DEC_GP + gid) * HD + nt * 8 + tig * 2 + 1] = oc[nt][1];
+        for (int mt = 0; mt < HD / 16; ++mt) {
+            o0[mt * 16 + gid] = oc[mt][0]; o1[mt * 16 + gid] = oc[mt][1];
+            o0[mt * 16 + gid + 8] = oc[mt][2]; o1[mt * 16 + gid + 8] = oc[mt][3];
+        }
     }
     __syncthreads();
-    for (int i = tid; i < DEC_GP * HD; i += DEC_THREADS) {
-        const int g = i / HD, d = i - g * HD;
+    if (tid < DEC_GP) {                                  // the warps' weights for head tid, and the CTA's maximum and sum
         float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, w_m[w * DEC_GP + g]);
-        float L = 0.f, O = 0.f;
+        for (int w = 0; w < WARPS; ++w) M = fmaxf(M, reinterpret_cast<const float*>(ring + (size_t)w * 2 * TILE)[tid]);
+        float L = 0.f;
 #pragma unroll
-        for (int w = 0; w < DEC_WARPS; ++w) {            // warps in index order
-            const float mw = w_m[w * DEC_GP + g];
-            const float f = mw == -INFINITY ? 0.f : expf(mw - M);
-            L += f * w_l[w * DEC_GP + g];
-            O += f * w_o[(w * DEC_GP + g) * HD + d];
+        for (int w = 0; w < WARPS; ++w) {                // warps in index order
+            const float* st = reinterpret_cast<const float*>(ring + (size_t)w * 2 * TILE);
+            const float f = st[tid] == -INFINITY ? 0.f : expf(st[tid] - M);
+            f_w[w * DEC_GP + tid] = f;
+            L += f * st[DEC_GP + tid];
         }
-        c_o[g * HD + d] = O;
-        if (d == 0) { c_m[g] = M; c_l[g] = L; }
+        c_m[tid] = M; c_l[tid] = L;
     }
     __syncthreads();
-    if (splits > 1) dcl_cluster_sync();                  // every CTA's state is complete and visible in the cluster
-    if (rank == 0 && !gave_up) {
-        // Bring the peers' states (max | sum | output, contiguous) into this CTA's memory first: batches of
-        // independent 16-byte remote loads, so that their latencies overlap instead of adding up.
-        constexpr int STATE4 = (2 * DEC_GP + DEC_GP * HD) / 4;            // float4 per CTA state
-        float4* stage = reinterpret_cast<float4*>(ring);                    // [splits - 1][STATE4], over the ring
-        const int total = (splits - 1) * STATE4;
-        for (int i0 = tid; i0 < total; i0 += DEC_THREADS * 4) {
-            float4 v[4];
+    const int DS = HD / splits;                          // output dimensions per CTA of the cluster
+    const int slot_floats = 2 * DEC_GP + DEC_GP * DS;
+    for (int i = tid; i < G * HD; i += NT) {
+        const int g = i / HD, d = i - g * HD;
+        float O = 0.f;
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int i = i0 + u * DEC_THREADS;
-                if (i < total) {
-                    const int r = 1 + i / STATE4, j = i - (r - 1) * STATE4;
-                    uint32_t raddr;
-                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr) : "r"(dec_smem_u32(c_m) + 16 * j), "r"(r));
-                    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
-                                 : "=f"(v[u].x), "=f"(v[u].y), "=f"(v[u].z), "=f"(v[u].w) : "r"(raddr) : "memory");
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int i = i0 + u * DEC_THREADS;
-                if (i < total) stage[i] = v[u];
-            }
-        }
-        __syncthreads();
-        const float* st = reinterpret_cast<const float*>(stage);
-        for (int i = tid; i < G * HD; i += DEC_THREADS) {
-            const int g = i / HD, d = i - g * HD;
-            float M = c_m[g];
-            for (int r = 1; r < splits; ++r) M = fmaxf(M, st[(r - 1) * STATE4 * 4 + g]);
-            float L = 0.f, O = 0.f;
-            for (int r = 0; r < splits; ++r) {           // CTAs in rank order
-                const float* base = st + (r - 1) * STATE4 * 4;
-                const float mr = r ? base[g] : c_m[g];
-                const float f = mr == -INFINITY ? 0.f : expf(mr - M);
-                L += f * (r ? base[DEC_GP + g] : c_l[g]);
-                O += f * (r ? base[2 * DEC_GP + g * HD + d] : c_o[g * HD + d]);
-            }
-            out[(size_t)b * out_stride + (size_t)(kvh * G + g) * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+        for (int w = 0; w < WARPS; ++w)
+            O += f_w[w * DEC_GP + g] * reinterpret_cast<const float*>(ring + (size_t)w * 2 * TILE)[2 * DEC_GP + g * SP + d];
+        if (splits == 1) {
+            if (!gave_up)
+                out[(size_t)b * out_stride + (size_t)(kvh * G + g) * HD + d] = __float2bfloat16_rn(c_l[g] > 0.f ? O / c_l[g] : 0.f);
+        } else {                                         // to the CTA that owns dimension d, into this CTA's slot there
+            const int t = d / DS;
+            uint32_t raddr;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr)
+                         : "r"(dec_smem_u32(slots + rank * slot_floats + 2 * DEC_GP + g * DS + (d - t * DS))), "r"(t));
+            asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(raddr), "f"(O) : "memory");
         }
     }
-    if (splits > 1) dcl_cluster_sync();                  // peers stay until their state has been read
+    if (splits > 1) {
+        for (int i = tid; i < splits * 2 * DEC_GP; i += NT) {       // this CTA's maxima and sums to every peer
+            const int t = i / (2 * DEC_GP), j = i - t * 2 * DEC_GP;
+            uint32_t raddr;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr)
+                         : "r"(dec_smem_u32(slots + rank * slot_floats + j)), "r"(t));
+            asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(raddr), "f"(j < DEC_GP ? c_m[j] : c_l[j - DEC_GP]) : "memory");
+        }
+        dcl_cluster_sync();                              // every push has landed; nobody reads a peer's memory after it
+        if (!gave_up)
+            for (int i = tid; i < G * DS; i += NT) {
+                const int g = i / DS, dd = i - g * DS;
+                float M = -INFINITY;
+                for (int r = 0; r < splits; ++r) M = fmaxf(M, slots[r * slot_floats + g]);
+                float L = 0.f, O = 0.f;
+                for (int r = 0; r < splits; ++r) {       // CTAs in rank order
+                    const float* sl = slots + r * slot_floats;
+                    const float f = sl[g] == -INFINITY ? 0.f : expf(sl[g] - M);
+                    L += f * sl[DEC_GP + g];
+                    O += f * sl[2 * DEC_GP + g * DS + dd];
+                }
+                out[(size_t)b * out_stride + (size_t)(kvh * G + g) * HD + rank * DS + dd] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+            }
+    }
     if (gave_up && tid == 0 && status) atomicExch(status, 5);
 }
 
@@ -601,7 +623,7 @@ typedef CUresult (*DecEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, v
                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-static int dec_make_map(CUtensorMap* map, const void* pages, long long rows, int hd) {
+static int dec_make_map(CUtensorMap* map, const void* pages, long long rows, int hd, int box_rows = 64) {
     static DecEncodeFn fn = nullptr;
     if (!fn) {
         void* ptr = nullptr;
@@ -614,7 +636,7 @@ static int dec_make_map(CUtensorMap* map, const void* pages, long long rows, int
     if (reinterpret_cast<uintptr_t>(pages) & 15) return RF_ERR_BAD_ARG;
     cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
-    cuuint32_t box[2] = {64, 64};
+    cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pages), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -622,27 +644,24 @@ static int dec_make_map(CUtensorMap* map, const void* pages, long long rows, int
     return r == CUDA_SUCCESS ? 0 : RF_ERR_BAD_ARG;
 }
 
-template <int EPL>
-static int launch_cluster(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
-                          const void* v_pages, long long n_pages, const int* tok_seq, const int* tok_pos, const int* seq_slot,
-                          const int* block_table, int max_pages, int nh, int nkv, float scale, int window, int B,
-                          int splits, int stages, int* status, cudaStream_t st) {
+template <int EPL, int ROWS, int WARPS>
+static int launch_warps(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                        const void* v_pages, long long n_pages, const int* tok_seq, const int* tok_pos,
+                        const int* seq_slot, const int* block_table, int max_pages, int nh, int nkv, float scale,
+                        int window, int B, int splits, int* status, cudaStream_t st) {
     constexpr int HD = EPL * 32;
-    auto bytes = [](int n) {
-        return (size_t)n * 2 * RF_PAGE * HD * 2 + (size_t)(2 * DEC_GP + DEC_GP * HD) * sizeof(float) + DCL_MAX_STAGES * 8 + 16 + 1024;
-    };
-    while (stages > 2 && bytes(stages) > 200 * 1024) --stages;        // head_dim 256: fewer stages fit
-    const size_t smem = bytes(stages);
+    const size_t smem = (size_t)WARPS * 2 * ROWS * HD * 2 +
+                        (size_t)(WARPS * DEC_GP + 2 * DEC_GP + 8 * 2 * DEC_GP + DEC_GP * HD) * sizeof(float) + WARPS * 2 * 8 + 16 + 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_decode_cluster_kernel<EPL>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(200 * 1024));
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_warps_kernel<EPL, ROWS, WARPS>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(splits, nkv, B);
-    cfg.blockDim = dim3(DEC_THREADS);
+    cfg.blockDim = dim3(WARPS * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[2];
@@ -661,11 +680,12 @@ static int launch_cluster(const void* q, int q_stride, void* out, int out_stride
     cfg.numAttrs = n;
     CUtensorMap mk, mv;
     int me;
-    if ((me = dec_make_map(&mk, k_pages, n_pages * nkv * RF_PAGE, HD)) || (me = dec_make_map(&mv, v_pages, n_pages * nkv * RF_PAGE, HD)))
+    if ((me = dec_make_map(&mk, k_pages, n_pages * nkv * RF_PAGE, HD, ROWS)) ||
+        (me = dec_make_map(&mv, v_pages, n_pages * nkv * RF_PAGE, HD, ROWS)))
         return me;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, attention_decode_cluster_kernel<EPL>, mk, mv,
+    cudaError_t e = cudaLaunchKernelEx(&cfg, attention_decode_warps_kernel<EPL, ROWS, WARPS>, mk, mv,
         reinterpret_cast<const __nv_bfloat16*>(q), q_stride, reinterpret_cast<__nv_bfloat16*>(out), out_stride, tok_seq,
-        tok_pos, seq_slot, block_table, max_pages, nh, nkv, scale, window, splits, stages, status);
+        tok_pos, seq_slot, block_table, max_pages, nh, nkv, scale, window, splits, status);
     if (e != cudaSuccess) return (int)e;
     RF_LAUNCH_CHECK();
     return 0;
@@ -713,25 +733,24 @@ void rf_attention_decode_scratch(int B, int nh, int nkv, int hd, int max_chunks,
     *n_counters = (long long)B * nkv;
 }
 
-// The clustered variant: `splits` (1, 2, 4 or 8) CTAs share a (sequence, kv head); no scratch memory.
-// `stages` (2..6) pages of keys and values are in flight per CTA: 3 lets two CTAs share an SM (many
-// sequences), 6 hides the copy latency when a single CTA walks a whole context (few sequences).
-int rf_attention_decode_cluster(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
-                                const void* v_pages, long long n_pages, const int* tok_seq, const int* tok_pos,
-                                const int* seq_slot,
-                                const int* block_table, int max_pages, int nh, int nkv, int hd, float scale,
-                                int window, int B, int splits, int stages, int* status, cudaStream_t st) {
+// A warp per tile of keys, `warps` (4 or 8) warps per CTA.
+int rf_attention_decode_warps(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                              const void* v_pages, long long n_pages, const int* tok_seq, const int* tok_pos,
+                              const int* seq_slot, const int* block_table, int max_pages, int nh, int nkv, int hd,
+                              float scale, int window, int B, int splits, int warps, int* status, cudaStream_t st) {
     if (B <= 0) return 0;
-    if (!rf_attention_decode_supported(nh, nkv, hd) || B > 65535) return RF_ERR_UNSUPPORTED;
-    if (stages < 2 || stages > DCL_MAX_STAGES) return RF_ERR_BAD_ARG;
+    if (!rf_attention_decode_supported(nh, nkv, hd)) return RF_ERR_UNSUPPORTED;
+    if (nkv > 65535 || B > 65535) return RF_ERR_UNSUPPORTED;
     if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return RF_ERR_BAD_ARG;
+    if (warps != 4 && warps != 8) return RF_ERR_BAD_ARG;
     if ((reinterpret_cast<uintptr_t>(q) & 15) || (q_stride * 2) % 16) return RF_ERR_BAD_ARG;
-#define GOC(EPL) return launch_cluster<EPL>(q, q_stride, out, out_stride, k_pages, v_pages, n_pages, tok_seq, tok_pos, seq_slot, \
-                                            block_table, max_pages, nh, nkv, scale, window, B, splits, stages, status, st)
-    if (hd == 64) GOC(2);
-    if (hd == 128) GOC(4);
-    GOC(8);
-#undef GOC
+#define GOW(EPL, ROWS, WARPS) return launch_warps<EPL, ROWS, WARPS>(q, q_stride, out, out_stride, k_pages, v_pages, n_pages, tok_seq, \
+                              tok_pos, seq_slot, block_table, max_pages, nh, nkv, scale, window, B, splits, status, st)
+    if (hd == 64) { if (warps == 8) GOW(2, 32, 8); GOW(2, 32, 4); }
+    if (hd == 128) { if (warps == 8) GOW(4, 32, 8); GOW(4, 32, 4); }
+    if (warps == 8) GOW(8, 16, 8);
+    GOW(8, 16, 4);
+#undef GOW
 }
 
 int rf_attention_decode(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,

@@ -22,6 +22,7 @@ class Options:
     tensor_core_gemm: bool = True        # tcgen05 products on the bfloat16 path where the shape allows
     tuned_attention: bool = True         # split-KV decode attention / tiled prefill attention on bfloat16
     tcgen05_attention: bool = True       # prefill attention with tcgen05.mma (else the mma.sync kernel)
+    clustered_decode: bool = True        # decode attention by clusters of CTAs (else one CTA per 128-key chunk)
     decode_graphs: bool = True           # replay decode steps from CUDA graphs in the generation loop
 
 
@@ -125,15 +126,15 @@ class StepContext:
         longest = self.model_cache_limit if self.replayed else self.max_end
         if (self.is_decode and self.compute_dtype == torch.bfloat16 and self.options.tuned_attention
                 and kernels.attention_decode_supported(nh, nkv, hd)):
-            if kernels.decode_walks(self.B, nkv, longest, view.window):
-                # a cluster of 1..8 CTAs per (sequence, kv head) walks the pages and merges through
-                # distributed shared memory: no scratch memory, no second pass
-                return kernels.attention_decode_cluster(
+            if self.options.clustered_decode:
+                # a cluster of 1..8 CTAs per (sequence, kv head), every warp on its own tiles of keys, merged
+                # through distributed shared memory: no scratch memory, no second pass, any context length
+                return kernels.attention_decode_warps(
                     q, nh, nkv, hd, view.k_pages, view.v_pages, self.tok_seq, self.tok_pos, self.seq_slot,
                     view.block_table, mixer.scale, view.window,
                     splits=kernels.decode_splits(self.B, nkv, longest, view.window))
             if longest <= kernels.DECODE_CHUNK * kernels.DECODE_CHUNK:
-                # long contexts: one CTA per 128-key chunk, partial results merged through scratch memory
+                # the earlier kernel: one CTA per 128-key chunk, partial results merged through scratch memory
                 need = max(1, (longest + kernels.DECODE_CHUNK - 1) // kernels.DECODE_CHUNK)
                 max_chunks = 1
                 while max_chunks < need:                   # powers of two: few distinct scratch sizes

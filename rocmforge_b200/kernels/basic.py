@@ -319,16 +319,13 @@ def attention_prefill(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: 
     return out
 
 
-DECODE_WALK_PAGES = 16      # pages one CTA walks before the chunked kernel (one CTA per 128 keys) pays again
-
-
 def decode_splits(B: int, n_kv_heads: int, longest: int | None = None, window: int | None = None) -> int:
     """CTAs that share one (sequence, kv head) in the clustered decode attention, from the batch and the
     longest context the launch may meet (a captured graph keeps its launch shape): about one CTA per SM,
     at most one CTA per page, and clusters of 8 only for very small batches, where nothing else fills the
-    GPU (their merge reads seven remote states).  Measured at 28 layers, 4 kv heads of 7 query heads:
-    batch 8 / 512 keys: 4 CTAs 3.15 ms a step, 1 CTA 3.26, chunked kernel 3.29; batch 1 / 3,800 keys:
-    8 CTAs 3.25, 1 CTA 4.64, chunked 3.29; batch 32 / 512: 2 CTAs 3.75, 8 CTAs 4.79, chunked 4.12."""
+    GPU.  Measured at 28 layers, 4 kv heads of 7 query heads, ms per decode step: batch 1 / 3,800 keys:
+    1, 2, 4, 8 CTAs 3.45, 3.16, 2.92, 2.85; batch 8 / 1,900 keys: 3.21, 3.10, 3.01, 3.05; batch 32 / 512:
+    3.54, 3.54, 3.72; batch 64 / 512: 3.76, 4.04."""
     pairs = max(1, B * n_kv_heads)
     s = 1
     while s < 8 and pairs * s * 2 <= 128:
@@ -350,20 +347,13 @@ def decode_pages(longest: int, window: int | None) -> int:
     return pages
 
 
-def decode_walks(B: int, n_kv_heads: int, longest: int, window: int | None) -> bool:
-    """Whether the clustered kernel (pages walked with a running softmax) or the chunked kernel serves a
-    decode step: the walk is the faster one until a CTA has more than ``DECODE_WALK_PAGES`` pages in a row."""
-    s = decode_splits(B, n_kv_heads, longest, window)
-    return (decode_pages(longest, window) + s - 1) // s <= DECODE_WALK_PAGES
-
-
-def attention_decode_cluster(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, k_pages, v_pages,
-                             tok_seq, tok_pos, seq_slot, block_table, scale: float, window: int | None,
-                             splits: int | None = None, stages: int = 3,
-                             out: torch.Tensor | None = None) -> torch.Tensor:
-    """One new token per sequence over the bfloat16 paged cache; the CTAs of a (sequence, kv head) form a
-    cluster and merge through distributed shared memory (no scratch memory).  ``stages`` pages are in flight
-    per CTA (3: two CTAs per SM; 6: one CTA walking a whole context hides the copy latency)."""
+def attention_decode_warps(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, k_pages, v_pages,
+                           tok_seq, tok_pos, seq_slot, block_table, scale: float, window: int | None,
+                           splits: int | None = None, warps: int | None = None,
+                           out: torch.Tensor | None = None) -> torch.Tensor:
+    """One new token per sequence over the bfloat16 paged cache: a cluster of ``splits`` CTAs per (sequence,
+    kv head), every warp on its own tiles of keys; merged through distributed shared memory.  ``warps``
+    per CTA: 8 while one CTA per SM is enough for the batch, else 4 (three CTAs fit an SM)."""
     need_cuda(q, k_pages, v_pages, tok_seq, tok_pos, seq_slot, block_table)
     B = q.shape[0]
     need(q.dtype == torch.bfloat16 and q.dim() == 2 and q.stride(1) == 1, "attention_decode: q must be bfloat16 [B, ...]")
@@ -375,17 +365,18 @@ def attention_decode_cluster(q: torch.Tensor, n_heads: int, n_kv_heads: int, hea
     need(q.data_ptr() % 16 == 0 and (q.stride(0) * 2) % 16 == 0, "attention_decode: q rows must be 16-byte aligned")
     if splits is None:
         splits = decode_splits(B, n_kv_heads)
+    if warps is None:
+        warps = 8 if B * n_kv_heads * splits <= 148 else 4
     if out is None:
         out = torch.empty((B, n_heads * head_dim), dtype=torch.bfloat16, device=q.device)
     from .tensor_core import status_word
-    f = _f("attention_decode", "rf_attention_decode_cluster", c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+    f = _f("attention_decode", "rf_attention_decode_warps", c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
            c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int,
            c_void_p, c_void_p)
     check(f(ptr(q), q.stride(0), ptr(out), out.stride(0), ptr(k_pages), ptr(v_pages), k_pages.shape[0], ptr(tok_seq),
-            ptr(tok_pos),
-            ptr(seq_slot), ptr(block_table), block_table.shape[1], n_heads, n_kv_heads, head_dim, float(scale),
-            int(window or 0), B, splits, stages, ptr(status_word(q.device)), stream()),
-          f"attention_decode_cluster (heads={n_heads}, kv_heads={n_kv_heads}, head_dim={head_dim}, splits={splits})")
+            ptr(tok_pos), ptr(seq_slot), ptr(block_table), block_table.shape[1], n_heads, n_kv_heads, head_dim,
+            float(scale), int(window or 0), B, splits, warps, ptr(status_word(q.device)), stream()),
+          f"attention_decode_warps (heads={n_heads}, kv_heads={n_kv_heads}, head_dim={head_dim}, splits={splits})")
     return out
 
 

@@ -77,6 +77,28 @@ def test_tuned_kernel_paths_prompt_chunk_decode_and_batch(folders, name, dtype):
                             f"{name} batch decode step {step}")
 
 
+@pytest.mark.parametrize("option", ["clustered_decode", "tcgen05_attention", "tuned_attention", "tensor_core_gemm"])
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_every_switch_of_the_engine_keeps_the_results(folders, name, option):
+    """Each option set to False takes another kernel for the same step (the chunked decode attention, the
+    mma.sync prefill attention, the generic attention, the CUDA-core products): same logits as the plain model."""
+    from rocmforge_b200 import StepRequest
+    m, p = engine(folders, name, "bfloat16", **{option: False}), plain(folders, name, "bfloat16")
+    V = CONFIGS[name]["vocab_size"]
+    cache = m.new_cache(max_tokens=64 * 12, max_slots=2)
+    seqs = [random_tokens(V, 330, 71), random_tokens(V, 150, 72)]
+    refs = [p.logits(t) for t in seqs]
+    poison_free_pages(cache)
+    slots = [cache.alloc_slot(), cache.alloc_slot()]
+    cut = [300, 120]
+    got = m.step(cache, [StepRequest(sl, t[:c], range(c)) for sl, t, c in zip(slots, seqs, cut)])
+    assert_logits_close(got.cpu(), torch.cat([r[:c] for r, c in zip(refs, cut)]), "bfloat16", f"{name} {option}=False prompts")
+    for step in range(30):
+        got = m.step(cache, [StepRequest(sl, [t[c + step]], [0]) for sl, t, c in zip(slots, seqs, cut)])
+        assert_logits_close(got.cpu(), torch.stack([r[c + step] for r, c in zip(refs, cut)]), "bfloat16",
+                            f"{name} {option}=False decode step {step}")
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_each_request_alone_and_whole(folders, name, dtype):

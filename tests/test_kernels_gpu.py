@@ -263,17 +263,16 @@ def test_attention_decode(nh, nkv, hd, window):
     gen = kernels.attention_generic(q.to(DEV), nh, nkv, hd, k_pages, v_pages, tok_seq, tok_pos, seq_slot, table,
                                     scale, window)
     torch.testing.assert_close(out.float(), gen.float(), atol=2e-2, rtol=2e-2)
-    # the clustered variant: every cluster size, the same answers
-    for splits, stages in ((1, 3), (1, 6), (2, 2), (4, 3), (8, 4)):
-        out = kernels.attention_decode_cluster(q.to(DEV), nh, nkv, hd, k_pages, v_pages, tok_seq, tok_pos, seq_slot,
-                                               table, scale, window, splits=splits, stages=stages)
+    # the clustered kernel: every cluster size and both CTA widths, the same answers
+    for splits, warps in ((1, 4), (1, 8), (2, 8), (4, 4), (8, 8)):
+        out = kernels.attention_decode_warps(q.to(DEV), nh, nkv, hd, k_pages, v_pages, tok_seq, tok_pos, seq_slot,
+                                             table, scale, window, splits=splits, warps=warps)
         assert torch.isfinite(out.float()).all()
         for b in range(B):
             torch.testing.assert_close(out[b].cpu().double().view(nh, hd), refs[b], atol=2e-2, rtol=2e-2)
     assert kernels.decode_splits(1, 4) == 8 and kernels.decode_splits(8, 4) == 4 and kernels.decode_splits(64, 4) == 1
     assert kernels.decode_splits(1, 4, longest=100) == 2 and kernels.decode_splits(1, 4, 4096, window=128) == 2
-    assert kernels.decode_walks(8, 4, 2048, None) and not kernels.decode_walks(1, 4, 16384, None)
-    assert kernels.decode_walks(1, 4, 1 << 20, 1024)            # a window bounds the pages whatever the length
+    assert kernels.decode_pages(1 << 20, 1024) == 17            # a window bounds the pages whatever the length
 
 
 def test_attention_decode_finds_far_keys_and_the_window_edge():
@@ -296,10 +295,12 @@ def test_attention_decode_finds_far_keys_and_the_window_edge():
                 torch.tensor([1], dtype=torch.int32, device=DEV), table, 1.0 / math.sqrt(hd), window)
         if which["kernel"] == "chunked":
             return kernels.attention_decode(*args, 8, *scratch)[0].float().cpu().view(nh, hd)
-        return kernels.attention_decode_cluster(*args, splits=4)[0].float().cpu().view(nh, hd)
+        return kernels.attention_decode_warps(*args, splits=splits, warps=warps)[0].float().cpu().view(nh, hd)
 
-    for kernel in ("chunked", "clustered"):
-        which["kernel"] = kernel
+    splits = warps = 0
+    check_far_keys(run, vs)
+    which["kernel"] = "clustered"
+    for splits, warps in ((4, 8), (1, 4), (8, 4)):
         check_far_keys(run, vs)
 
 
