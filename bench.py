@@ -251,7 +251,7 @@ def main():
     e2e = e2e_rate(llm, args.batch, args.steps, args.seed + 1)
     llm.cache = llm.engine = None
     torch.cuda.empty_cache()
-    pre_ms = prefill_rate(model, PREFILL_TOKENS, 3, args.seed + 2)
+    pre_ms = prefill_rate(model, PREFILL_TOKENS, 5, args.seed + 2)
     points = {}
     if not args.skip_points:
         points["decode_b1"] = round(decode_rate(model, 1, args.steps, warmup, args.seed + 3)["tok_s"], 1)

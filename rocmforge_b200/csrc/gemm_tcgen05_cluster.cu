@@ -76,11 +76,14 @@ template <int CL>
 __global__ void __launch_bounds__(CG_THREADS, 1)
 gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                        const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_out2,
-                       TcParams p, int groups_m, int tiles_n) {
+                       TcParams p, int groups_m, int tiles_n, int bn) {
+    // bn: columns of a tile (a multiple of 32, at most CG_BN; the host picks the width that wastes least of the last
+    // round of clusters); the ring and the accumulators are laid out for CG_BN
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2;
     constexpr uint32_t B_BYTES = CG_BN * TC_BK * 2;
-    constexpr uint32_t B_PART = B_BYTES / CL;
     constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+    const uint32_t b_part = (uint32_t)(bn / CL) * TC_BK * 2;            // bytes of the weight rows this CTA loads
+    const uint32_t stage_tx = A_BYTES + (uint32_t)bn * TC_BK * 2;
     constexpr int S = CG_STAGES;
 
     extern __shared__ uint8_t smem_raw[];
@@ -136,17 +139,17 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                     const int s = it % S;
                     if (!mbar_wait(smem_u32(&bars[S + s]), ((it / S) & 1) ^ 1, &abort_flag)) break;
                     const uint32_t full = smem_u32(&bars[s]);
-                    mbar_expect_tx(full, STAGE_BYTES);
+                    mbar_expect_tx(full, stage_tx);
                     const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
                     tma_load_2d(sa, &map_a, kb * TC_BK, tile_m * TC_BM, full);
-                    tma_load_2d_multicast(sa + A_BYTES + rank * B_PART, &map_b, kb * TC_BK,
-                                          tile_n * CG_BN + (int)rank * (CG_BN / CL), full, all);
+                    tma_load_2d_multicast(sa + A_BYTES + rank * b_part, &map_b, kb * TC_BK,
+                                          tile_n * bn + (int)rank * (bn / CL), full, all);
                 }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc(CG_BN);
+            const uint32_t idesc = make_idesc(bn);
             int it = 0, local = 0;
             for (int w = cluster_id; w < n_work && !abort_flag; w += n_clusters, ++local) {
                 const int buf = local & 1;
@@ -188,7 +191,7 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             // accumulator columns per 128-byte slab row: 32 as float, 64 as bfloat16, 128 through SwiGLU
             const int cols_per_slab = (mode == EPI_F32 || mode == EPI_RESIDUAL) ? 32 : (mode == EPI_STORE ? 64 : 128);
 #pragma unroll 1
-            for (int c0 = 0; c0 < CG_BN; c0 += cols_per_slab, ++slab) {
+            for (int c0 = 0; c0 < bn; c0 += cols_per_slab, ++slab) {
                 uint8_t* st = staging + (slab & 1) * 16384;
                 // the slab before last used this buffer: TMA must have read it
                 if (leader) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
@@ -199,7 +202,7 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                     uint32_t r[32];
                     tcgen05_ld32(taddr + c0 + cc, r);
                     tcgen05_wait_ld();
-                    const int n0 = tile_n * CG_BN + c0 + cc;
+                    const int n0 = tile_n * bn + c0 + cc;
                     if (mode == EPI_SWIGLU) {            // 32 accumulators -> 16 bfloat16 = 2 chunks of 16 bytes
 #pragma unroll
                         for (int h8 = 0; h8 < 2; ++h8) {
@@ -242,7 +245,7 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 epi_barrier();
                 if (leader) {
                     // output column of the slab's first element, in elements of the output matrix
-                    const int oc0 = (mode == EPI_SWIGLU) ? (tile_n * CG_BN + c0) / 2 : tile_n * CG_BN + c0;
+                    const int oc0 = (mode == EPI_SWIGLU) ? (tile_n * bn + c0) / 2 : tile_n * bn + c0;
                     if (mode == EPI_RESIDUAL) tma_reduce_add_2d(omap, oc0, tile_m * TC_BM, smem_u32(st));
                     else tma_store_2d(omap, oc0, tile_m * TC_BM, smem_u32(st));
                     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
@@ -321,20 +324,32 @@ static int launch_cluster(const void* X, int ldx, const void* W, TcParams p, cud
     cfg.stream = st;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    // Tile width: the persistent clusters work in rounds, and a last round that is half empty costs as much
+    // as a full one (N = 3584 in 256-column tiles on 74 clusters: 112 tiles, 1.5 rounds).  Among the widths
+    // the epilogue can cut into slabs, take the one with the least rounds x width.
+    const int tiles_m = (p.M + TC_BM - 1) / TC_BM, groups_m = (tiles_m + CL - 1) / CL;
+    const int unit = (p.mode == EPI_F32 || p.mode == EPI_RESIDUAL) ? 32 : (p.mode == EPI_STORE ? 64 : 128);
+    int bn = CG_BN;
+    long long best = -1;
+    for (int cand = CG_BN; cand >= 128; cand -= unit) {
+        const long long work = (long long)groups_m * ((p.N + cand - 1) / cand) * p.splits;
+        const long long cost = (work + max_clusters - 1) / max_clusters * cand;
+        if (best < 0 || cost < best) { best = cost; bn = cand; }
+    }
     CUtensorMap ma, mb, mo, mo2;
     int e;
-    if ((e = make_map(&ma, X, p.M, p.K, ldx, TC_BM)) || (e = make_map(&mb, W, p.N, p.K, p.K, CG_BN / CL))) return e;
+    if ((e = make_map(&ma, X, p.M, p.K, ldx, TC_BM)) || (e = make_map(&mb, W, p.N, p.K, p.K, bn / CL))) return e;
     const bool f32_out = p.mode == EPI_F32 || p.mode == EPI_RESIDUAL;
     const long long out_cols = p.mode == EPI_SWIGLU ? p.N / 2 : p.N;
     if ((e = make_out_map(&mo, p.out, p.M, out_cols, p.ldo, f32_out))) return e;
     mo2 = mo;
     if (p.out2 && (e = make_out_map(&mo2, p.out2, p.M, p.N, p.N, true))) return e;
-    const int tiles_m = (p.M + TC_BM - 1) / TC_BM, groups_m = (tiles_m + CL - 1) / CL, tiles_n = (p.N + CG_BN - 1) / CG_BN;
+    const int tiles_n = (p.N + bn - 1) / bn;
     int n_clusters = groups_m * tiles_n * p.splits;
     if (n_clusters > max_clusters) n_clusters = max_clusters;
     cfg.gridDim = dim3(n_clusters * CL);
     cfg.numAttrs = g_rf_pdl ? 2 : 1;
-    cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_tc_cluster_kernel<CL>, ma, mb, mo, mo2, p, groups_m, tiles_n);
+    cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_tc_cluster_kernel<CL>, ma, mb, mo, mo2, p, groups_m, tiles_n, bn);
     if (le != cudaSuccess) return (int)le;
     RF_LAUNCH_CHECK();
     return 0;
