@@ -209,6 +209,82 @@ __global__ void rope_kv_write_kernel(const void* __restrict__ src, int row_strid
     }
 }
 
+// The same for many tokens (prompts) whose q | k | v rows are one tensor in the compute dtype: a block per
+// token; a thread takes four neighbouring pair indices, computes their sines and cosines once and walks
+// over the heads in steps of blockDim.x / (hd/8) with loads and stores of four elements, so the
+// trigonometry is shared by the heads and every access is 8 or 16 bytes wide.
+template <typename T> struct Four;
+template <> struct Four<float> {
+    static __device__ __forceinline__ void load(const float* p, float* v) {
+        const float4 x = *reinterpret_cast<const float4*>(p);
+        v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float* v) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+};
+template <> struct Four<__nv_bfloat16> {
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* v) {
+        const uint2 x = *reinterpret_cast<const uint2*>(p);
+        v[0] = __uint_as_float(x.x << 16); v[1] = __uint_as_float(x.x & 0xffff0000u);
+        v[2] = __uint_as_float(x.y << 16); v[3] = __uint_as_float(x.y & 0xffff0000u);
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float* v) {
+        const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+        uint2 x;
+        x.x = *reinterpret_cast<const uint32_t*>(&a); x.y = *reinterpret_cast<const uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(p) = x;
+    }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+rope_kv_write_rows_kernel(const T* __restrict__ src, int row_stride, T* __restrict__ q_out, int q_out_stride,
+                          int nh, int nkv, int hd, const float* __restrict__ inv_freq,
+                          const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                          const int* __restrict__ seq_slot, const int* __restrict__ block_table, int max_pages,
+                          T* __restrict__ k_pages, T* __restrict__ v_pages, int write_kv) {
+    pdl_trigger();
+    const int t = blockIdx.x;
+    const int half = hd >> 1, groups = half >> 2;        // groups of four pairs per head
+    const int g = threadIdx.x % groups, lane_head = threadIdx.x / groups, head_step = blockDim.x / groups;
+    if (lane_head >= head_step) return;                  // threads beyond the last whole row of groups
+    const int pos = tok_pos[t];
+    size_t page_base = 0;
+    if (write_kv) {
+        const int slot = seq_slot[tok_seq[t]];
+        const int page = block_table[(size_t)slot * max_pages + pos / RF_PAGE];
+        page_base = (size_t)page * nkv * RF_PAGE * hd + (size_t)(pos % RF_PAGE) * hd;
+    }
+    float sn[4], cs[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) sincosf((float)pos * inv_freq[4 * g + j], &sn[j], &cs[j]);
+    pdl_wait();
+    const T* row = src + (size_t)t * row_stride;
+    const int rotated = write_kv ? nh + nkv : nh;
+    for (int head = lane_head; head < rotated; head += head_step) {
+        float x0[4], x1[4], r0[4], r1[4];
+        Four<T>::load(row + (size_t)head * hd + 4 * g, x0);
+        Four<T>::load(row + (size_t)head * hd + half + 4 * g, x1);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { r0[j] = x0[j] * cs[j] - x1[j] * sn[j]; r1[j] = x0[j] * sn[j] + x1[j] * cs[j]; }
+        T* dst = head < nh ? q_out + (size_t)t * q_out_stride + (size_t)head * hd
+                           : k_pages + page_base + (size_t)(head - nh) * RF_PAGE * hd;
+        Four<T>::store(dst + 4 * g, r0);
+        Four<T>::store(dst + half + 4 * g, r1);
+    }
+    if (write_kv)
+        for (int vh = lane_head; vh < nkv; vh += head_step) {
+            float a[4], b[4];
+            const T* sv = row + (size_t)(nh + nkv + vh) * hd;
+            Four<T>::load(sv + 4 * g, a);
+            Four<T>::load(sv + half + 4 * g, b);
+            T* dst = v_pages + page_base + (size_t)vh * RF_PAGE * hd;
+            Four<T>::store(dst + 4 * g, a);
+            Four<T>::store(dst + half + 4 * g, b);
+        }
+}
+
 // ---------------------------------------------------------------- SwiGLU
 // gu: [T, 2I] with gate_j at column 2j and up_j at column 2j+1 (the fused weight is
 // interleaved row by row at load time); a[t, j] = silu(gate) * up, evaluated in 32-bit.
@@ -281,6 +357,21 @@ static int launch_rope_kv_write(const void* src, int row_stride, int n_partials,
     const int n_pairs = (nh + 2 * nkv) * (hd / 2);
     const dim3 grid(T_, (n_pairs + 255) / 256);
     if (T_ > 2147483647 || grid.y > 65535) return RF_ERR_UNSUPPORTED;
+    // prompts: rows of one tensor, everything aligned for accesses of four elements
+    const size_t four = 4 * sizeof(T);
+    auto aligned = [&](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) % four) == 0; };
+    if (n_partials == 0 && T_ >= 64 && hd % 8 == 0 && hd / 8 <= 256 && row_stride % 4 == 0 && q_out_stride % 4 == 0 &&
+        aligned(src) && aligned(q_out) && (!write_kv || (aligned(k_pages) && aligned(v_pages)))) {
+        const int groups = hd / 8;
+        int threads = ((nh + 2 * nkv) * groups + 31) / 32 * 32;        // a row of groups per head, at most 256 threads
+        if (threads > 256) threads = 256;
+        if (threads < groups) threads = (groups + 31) / 32 * 32;
+        rf_launch(rope_kv_write_rows_kernel<T>, dim3(T_), dim3(threads), 0, st, reinterpret_cast<const T*>(src), row_stride,
+            reinterpret_cast<T*>(q_out), q_out_stride, nh, nkv, hd, inv_freq, tok_seq, tok_pos, seq_slot, block_table,
+            max_pages, reinterpret_cast<T*>(k_pages), reinterpret_cast<T*>(v_pages), write_kv);
+        RF_LAUNCH_CHECK();
+        return 0;
+    }
     if (n_partials > 0)
         rf_launch(rope_kv_write_kernel<T, true>, grid, dim3(256), 0, st, src, row_stride, n_partials, partial_stride, bias,
             bias_is_f32, reinterpret_cast<T*>(q_out), q_out_stride, nh, nkv, hd, inv_freq, tok_seq, tok_pos, seq_slot,
