@@ -207,7 +207,7 @@ int rf_gemm_tc(const void* X, int ldx, const void* W, const void* bias, int bias
     if (!rf_gemm_tc_supported(M, N, K, mode) || mode == EPI_PARTIAL) return RF_ERR_UNSUPPORTED;
     CUtensorMap ma, mb;
     int e;
-    TcParams p{out, bias, bias_is_f32, M, N, K, ldo, mode, (K + TC_BK - 1) / TC_BK, 0, status, nullptr, 1};
+    TcParams p{out, bias, bias_is_f32, M, N, K, ldo, mode, (K + TC_BK - 1) / TC_BK, 0, status, 1};
     if (N > 128) {
         if ((e = make_map(&ma, X, M, K, ldx, TC_BM)) || (e = make_map(&mb, W, N, K, K, 256))) return e;
         dim3 grid((N + 255) / 256, (M + TC_BM - 1) / TC_BM, 1);
@@ -227,7 +227,7 @@ int rf_gemm_tc_skinny(const void* X, int ldx, const void* W, const void* bias, i
     const int kb = (K + TC_BK - 1) / TC_BK;
     const int per = (kb + splits - 1) / splits;
     if ((splits - 1) * per >= kb) return RF_ERR_BAD_ARG;          // an empty split would leave its partial unwritten
-    TcParams p{out, bias, bias_is_f32, M, N, K, ldo, mode, per, (long long)M * ldo, status, nullptr, 1};
+    TcParams p{out, bias, bias_is_f32, M, N, K, ldo, mode, per, (long long)M * ldo, status, 1};
     CUtensorMap ma, mb;
     int e;
     const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);

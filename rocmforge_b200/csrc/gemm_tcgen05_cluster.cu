@@ -68,15 +68,23 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 }
 
 // grid.x = n_clusters * CL (cluster dimension CL along x).  Work item w -> row group w % groups_m,
-// column tile (w / groups_m) % tiles_n, K half w / (groups_m * tiles_n); CTA `rank` of the cluster owns
-// row tile group * CL + rank.  With two K halves (p.splits == 2, used when the tiles would fill the last
-// round of clusters less than two thirds) the first half ends in the requested epilogue and the second
-// half stores its 32-bit sums to p.out2, which the caller adds later in a fixed order.
+// column tile (w / groups_m) % tiles_n, K part w / (groups_m * tiles_n); CTA `rank` of the cluster owns
+// row tile group * CL + rank.
+//
+// K parts (p.splits > 1, residual epilogue only).  The persistent clusters work in rounds, and a last round
+// that is half empty costs as much as a full one (2,048 x 3,584 outputs: 112 tiles on 74 clusters).  The
+// host may therefore cut K into P parts: P times as many, shorter work items fill the rounds better
+// (112 x 5 items: 8 rounds of a fifth = 1.6 instead of 2).  Every part adds its sums into the 32-bit
+// stream with TMA's reduce-add, and so that the sum of a tile is formed in ONE order, whatever the timing,
+// part q of a tile waits (bounded) until part q - 1 of that tile has been added: `flags[tile]` counts the
+// parts that are in; the last part sets it back to zero for the next launch.  Parts are scheduled
+// part-major (all first parts, then all second parts, ...), and all clusters of the grid are resident, so a
+// wait is always for work that was handed out earlier: it cannot deadlock, and in practice it never spins.
 template <int CL>
 __global__ void __launch_bounds__(CG_THREADS, 1)
 gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                       const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_out2,
-                       TcParams p, int groups_m, int tiles_n, int bn) {
+                       const __grid_constant__ CUtensorMap map_out, TcParams p, int groups_m, int tiles_n, int bn,
+                       int* __restrict__ flags) {
     // bn: columns of a tile (a multiple of 32, at most CG_BN; the host picks the width that wastes least of the last
     // round of clusters); the ring and the accumulators are laid out for CG_BN
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2;
@@ -101,7 +109,7 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     const int n_tiles = groups_m * tiles_n;
     const int n_work = n_tiles * p.splits;
     const int kb_all = (p.K + TC_BK - 1) / TC_BK;
-    const int kb_half = p.splits == 2 ? (kb_all + 1) / 2 : kb_all;
+    const int kb_part = (kb_all + p.splits - 1) / p.splits;         // k blocks per K part (the host leaves none empty)
     const uint16_t all = (uint16_t)((1u << CL) - 1);
 
     if (threadIdx.x == 0) {
@@ -134,7 +142,7 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             int it = 0;                                  // running k-block count across work items
             for (int w = cluster_id; w < n_work && !abort_flag; w += n_clusters) {
                 const int tile_m = (w % groups_m) * CL + (int)rank, tile_n = (w / groups_m) % tiles_n;
-                const int kb0 = (w / n_tiles) * kb_half, kb1 = (w / n_tiles) ? kb_all : kb_half;
+                const int kb0 = (w / n_tiles) * kb_part, kb1 = min(kb_all, kb0 + kb_part);
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % S;
                     if (!mbar_wait(smem_u32(&bars[S + s]), ((it / S) & 1) ^ 1, &abort_flag)) break;
@@ -157,7 +165,7 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 tcgen05_fence_after();
                 const uint32_t acc = tmem_base + buf * CG_BN;
                 bool ok = true;
-                const int kb_total = (w / n_tiles) ? kb_all - kb_half : kb_half;
+                const int kb_total = min(kb_all, (w / n_tiles + 1) * kb_part) - (w / n_tiles) * kb_part;
                 for (int kb = 0; kb < kb_total; ++kb, ++it) {
                     const int s = it % S;
                     ok = mbar_wait(smem_u32(&bars[s]), (it / S) & 1, &abort_flag);
@@ -182,9 +190,11 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         for (int w = cluster_id; w < n_work; w += n_clusters, ++local) {
             const int buf = local & 1;
             const int tile_m = (w % groups_m) * CL + (int)rank, tile_n = (w / groups_m) % tiles_n;
-            const bool second = (w / n_tiles) != 0;      // second K half: plain 32-bit store to out2
-            const int mode = second ? EPI_F32 : p.mode;
-            const CUtensorMap* omap = second ? &map_out2 : &map_out;
+            const int part = w / n_tiles;                // K part: only the first one adds the bias
+            const int mode = p.mode;
+            const CUtensorMap* omap = &map_out;
+            int* flag = flags + tile_m * tiles_n + tile_n;
+            bool ordered = part == 0;                    // whether the parts before this one are known to be in
             if (!mbar_wait(smem_u32(&bars[2 * S + buf]), (local >> 1) & 1, &abort_flag)) break;
             tcgen05_fence_after();
             const uint32_t taddr = tmem_base + buf * CG_BN + ((uint32_t)(quarter * 32) << 16);
@@ -222,7 +232,7 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
 #pragma unroll
                         for (int j = 0; j < 32; ++j) {
                             v[j] = __uint_as_float(r[j]);
-                            if (!second && p.bias && n0 + j < p.N) v[j] += load_vec(p.bias, p.bias_is_f32, n0 + j);
+                            if (part == 0 && p.bias && n0 + j < p.N) v[j] += load_vec(p.bias, p.bias_is_f32, n0 + j);
                         }
                         if (mode == EPI_STORE) {         // 32 accumulators -> 4 chunks of 8 bfloat16
 #pragma unroll
@@ -246,13 +256,40 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 if (leader) {
                     // output column of the slab's first element, in elements of the output matrix
                     const int oc0 = (mode == EPI_SWIGLU) ? (tile_n * bn + c0) / 2 : tile_n * bn + c0;
-                    if (mode == EPI_RESIDUAL) tma_reduce_add_2d(omap, oc0, tile_m * TC_BM, smem_u32(st));
-                    else tma_store_2d(omap, oc0, tile_m * TC_BM, smem_u32(st));
+                    if (!ordered) {                      // the tile's earlier K parts must have been added
+                        unsigned long long t0 = 0;
+                        for (long long spin = 0; !abort_flag; ++spin) {
+                            int seen;
+                            asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+                            if (seen >= part) { ordered = true; break; }
+                            if ((spin & 63) == 63) {
+                                unsigned long long now;
+                                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+                                if (t0 == 0) t0 = now;
+                                if (now - t0 > 2000000000ull) { abort_flag = 1; break; }
+                            }
+                        }
+                        asm volatile("fence.proxy.async;" ::: "memory");
+                    }
+                    if (ordered) {
+                        if (mode == EPI_RESIDUAL) tma_reduce_add_2d(omap, oc0, tile_m * TC_BM, smem_u32(st));
+                        else tma_store_2d(omap, oc0, tile_m * TC_BM, smem_u32(st));
+                    }
                     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 }
             }
             tcgen05_fence_before();
             mbar_arrive(smem_u32(&bars[2 * S + 2 + buf]));                   // 128 arrivals hand the buffer back
+            if (leader && p.splits > 1) {
+                // this part's additions are complete in memory before the next part of the tile may start
+                asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+                asm volatile("fence.proxy.async;" ::: "memory");
+                __threadfence();
+                if (ordered) {
+                    if (part == p.splits - 1) atomicExch(flag, 0);           // ready for the next launch
+                    else atomicAdd(flag, 1);
+                }
+            }
         }
         if (leader) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // all output has left before the CTA ends
     }
@@ -309,7 +346,8 @@ static int cluster_width() {
 }
 
 template <int CL>
-static int launch_cluster(const void* X, int ldx, const void* W, TcParams p, cudaStream_t st) {
+static int launch_cluster(const void* X, int ldx, const void* W, TcParams p, int parts, int* flags, int n_flags,
+                          cudaStream_t st) {
     constexpr size_t smem = (size_t)CG_STAGES * (TC_BM * TC_BK * 2 + CG_BN * TC_BK * 2) + 2 * 16384 + (2 * CG_STAGES + 4) * 8 + 16 + 1024;
     const int max_clusters = cluster_width<CL>();
     if (max_clusters <= 0) return max_clusters < -100 ? -(max_clusters + 100) : RF_ERR_UNSUPPORTED;
@@ -324,32 +362,59 @@ static int launch_cluster(const void* X, int ldx, const void* W, TcParams p, cud
     cfg.stream = st;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    // Tile width: the persistent clusters work in rounds, and a last round that is half empty costs as much
-    // as a full one (N = 3584 in 256-column tiles on 74 clusters: 112 tiles, 1.5 rounds).  Among the widths
-    // the epilogue can cut into slabs, take the one with the least rounds x width.
+    // Tile width and K parts: the persistent clusters work in rounds, and a last round that is half empty
+    // costs as much as a full one (N = 3584 in 256-column tiles on 74 clusters: 112 tiles, 1.5 rounds).  Among
+    // the widths the epilogue can cut into slabs, and (residual epilogue) 1..5 K parts, take the pair with the
+    // least estimated time: rounds x (blocks per part x time of a block, which goes with the bytes a CTA loads
+    // for it, + 2 us per round when there are parts: their epilogues and restarts).  Parts must keep 48 blocks
+    // (an epilogue, eight slabs through shared memory, hides behind the next part's products only if those
+    // take longer: with parts of 19 blocks the o projection took 66 us instead of 54), the output must stay in
+    // L2 (each part reads and writes it once more: 8,192 x 3,584 outputs got 18 % slower with 5 parts), and the
+    // estimate must promise a twentieth, or K stays whole.  Parts are for a last round that is badly filled
+    // (two or more rounds) or for a GPU that is not half used; one round that nearly fills it is left alone
+    // (1,024 x 3,584 x 18,944: 152 us whole, 156 in parts).  Measured: 2,048 rows 224 -> 205 us, 512 rows 130 -> 108 us.
     const int tiles_m = (p.M + TC_BM - 1) / TC_BM, groups_m = (tiles_m + CL - 1) / CL;
     const int unit = (p.mode == EPI_F32 || p.mode == EPI_RESIDUAL) ? 32 : (p.mode == EPI_STORE ? 64 : 128);
+    const int kb_all = (p.K + TC_BK - 1) / TC_BK;
+    const bool parts_allowed = p.mode == EPI_RESIDUAL && flags && (long long)p.M * p.N * 4 <= (32ll << 20);
     int bn = CG_BN;
-    long long best = -1;
+    double best = -1, best_whole = -1;
+    int bn_whole = CG_BN;
+    p.splits = 1;
     for (int cand = CG_BN; cand >= 128; cand -= unit) {
-        const long long work = (long long)groups_m * ((p.N + cand - 1) / cand) * p.splits;
-        const long long cost = (work + max_clusters - 1) / max_clusters * cand;
-        if (best < 0 || cost < best) { best = cost; bn = cand; }
+        const long long tiles = (long long)groups_m * ((p.N + cand - 1) / cand);
+        for (int P = 1; P <= 5; ++P) {
+            if (parts > 0 && P != parts) continue;                               // the caller's choice
+            if (parts == 0 && P > 1 && (!parts_allowed || kb_all / P < 48)) break;
+            const int per = (kb_all + P - 1) / P;
+            if ((P - 1) * per >= kb_all) continue;                               // a part would be empty
+            if (P > 1 && tiles * CL > n_flags) continue;
+            const long long rounds = (tiles * P + max_clusters - 1) / max_clusters;
+            const double cost = rounds * (per * 0.39 * (TC_BM + cand / CL) / 256.0 + (P > 1 ? 2.0 : 0.0));
+            if (best < 0 || cost < best) { best = cost; bn = cand; p.splits = P; }
+            if (P == 1 && (best_whole < 0 || cost < best_whole)) { best_whole = cost; bn_whole = cand; }
+        }
     }
-    CUtensorMap ma, mb, mo, mo2;
+    if (best < 0) return RF_ERR_BAD_ARG;
+    if (parts == 0 && p.splits > 1) {
+        const long long tiles_whole = (long long)groups_m * ((p.N + CG_BN - 1) / CG_BN);       // in full-width tiles
+        const bool badly_filled = tiles_whole > max_clusters || tiles_whole * 2 <= max_clusters;
+        if (best > 0.95 * best_whole || !badly_filled) { p.splits = 1; bn = bn_whole; }
+    }
+    if (best < 0) return RF_ERR_BAD_ARG;
+    if (p.splits > 1 && (p.mode != EPI_RESIDUAL || !flags)) return RF_ERR_BAD_ARG;
+    CUtensorMap ma, mb, mo;
     int e;
     if ((e = make_map(&ma, X, p.M, p.K, ldx, TC_BM)) || (e = make_map(&mb, W, p.N, p.K, p.K, bn / CL))) return e;
     const bool f32_out = p.mode == EPI_F32 || p.mode == EPI_RESIDUAL;
     const long long out_cols = p.mode == EPI_SWIGLU ? p.N / 2 : p.N;
     if ((e = make_out_map(&mo, p.out, p.M, out_cols, p.ldo, f32_out))) return e;
-    mo2 = mo;
-    if (p.out2 && (e = make_out_map(&mo2, p.out2, p.M, p.N, p.N, true))) return e;
     const int tiles_n = (p.N + bn - 1) / bn;
     int n_clusters = groups_m * tiles_n * p.splits;
     if (n_clusters > max_clusters) n_clusters = max_clusters;
     cfg.gridDim = dim3(n_clusters * CL);
     cfg.numAttrs = g_rf_pdl ? 2 : 1;
-    cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_tc_cluster_kernel<CL>, ma, mb, mo, mo2, p, groups_m, tiles_n, bn);
+    cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_tc_cluster_kernel<CL>, ma, mb, mo, p, groups_m, tiles_n, bn, flags);
     if (le != cudaSuccess) return (int)le;
     RF_LAUNCH_CHECK();
     return 0;
@@ -367,16 +432,19 @@ int rf_gemm_tc_cluster_supported(int M, int N, int K, int mode) {
 }
 
 // Same contract as rf_gemm_tc (tokens as rows), for M >= 256 and N >= 256.  cluster = 2 or 4 CTAs along M.
+// parts: K parts of the residual epilogue (0 = chosen here); flags: n_flags zeroed ints that stay with the
+// device between launches (the kernel leaves them zeroed), or null for no K parts.
 // How many clusters of `cluster` CTAs run at once (what the persistent grid is sized to), or a negative code.
 int rf_gemm_tc_cluster_width(int cluster);
 
 int rf_gemm_tc_cluster(const void* X, int ldx, const void* W, const void* bias, int bias_is_f32, void* out, int ldo,
-                       int M, int N, int K, int mode, int cluster, void* out2, int* status, cudaStream_t st) {
+                       int M, int N, int K, int mode, int cluster, int parts, int* flags, int n_flags, int* status,
+                       cudaStream_t st) {
     if (!rf_gemm_tc_cluster_supported(M, N, K, mode)) return RF_ERR_UNSUPPORTED;
-    if (out2 && (K + TC_BK - 1) / TC_BK < 2) return RF_ERR_BAD_ARG;
-    TcParams p{out, bias, bias_is_f32, M, N, K, ldo, mode, (K + TC_BK - 1) / TC_BK, 0, status, out2, out2 ? 2 : 1};
-    if (cluster == 2) return launch_cluster<2>(X, ldx, W, p, st);
-    if (cluster == 4) return launch_cluster<4>(X, ldx, W, p, st);
+    if (parts < 0 || parts > 5) return RF_ERR_BAD_ARG;
+    TcParams p{out, bias, bias_is_f32, M, N, K, ldo, mode, (K + TC_BK - 1) / TC_BK, 0, status, 1};
+    if (cluster == 2) return launch_cluster<2>(X, ldx, W, p, parts, flags, n_flags, st);
+    if (cluster == 4) return launch_cluster<4>(X, ldx, W, p, parts, flags, n_flags, st);
     return RF_ERR_BAD_ARG;
 }
 

@@ -22,8 +22,7 @@ struct TcParams {
     int k_blocks_per_split; // in units of TC_BK
     long long partial_stride;   // elements between the partial sums of two splits
     int* status;            // device word: 0 = fine
-    void* out2;             // clustered kernel with 2 K-splits: float32 [M, N] that receives the second half's sum
-    int splits;             // clustered kernel: 1 or 2
+    int splits;             // clustered kernel: K parts of the residual epilogue, added in order (1 = none)
 };
 
 // ---------------------------------------------------------------- PTX wrappers

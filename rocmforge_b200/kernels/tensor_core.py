@@ -84,24 +84,23 @@ def cluster_width(cluster: int = 2) -> int:
     return _cluster_width[cluster]
 
 
-def wants_two_k_halves(M: int, N: int, K: int, cluster: int = 2) -> bool:
-    """Whether cutting K in two would fill the last round of clusters better (from the shape alone).
-    The engine does not use it: at the Qwen2.5-7B shapes the halves measured no faster (down 232 -> 238 us,
-    o 53 -> 57 us at 2,048 tokens), the second half's extra pass through the next norm included."""
-    if K < 2048:
-        return False
-    items = ((M + 127) // 128 + cluster - 1) // cluster * ((N + 255) // 256)
-    rounds = items / cluster_width(cluster)
-    frac = rounds - int(rounds)
-    return rounds < 6 and 0.0 < frac <= 0.67
+_part_flags = {}
+
+
+def part_flags(device) -> torch.Tensor:
+    """Counters of the clustered kernel's K parts (one per output tile): zeroed once, left zeroed by every launch."""
+    key = torch.device(device).index or 0
+    if key not in _part_flags:
+        _part_flags[key] = torch.zeros((1 << 16,), dtype=torch.int32, device=device)
+    return _part_flags[key]
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, *, mode: int = STORE,
             out: Optional[torch.Tensor] = None, cluster: Optional[int] = None,
-            out2: Optional[torch.Tensor] = None) -> torch.Tensor:
+            parts: int = 0) -> torch.Tensor:
     """Tokens as accumulator rows (any M).  STORE -> bf16 [M,N]; F32 -> f32 [M,N]; RESIDUAL: out (f32) += x w^T;
-    SWIGLU -> bf16 [M, N/2] from row-interleaved gate/up weights.  With ``out2`` (clustered kernel only) K is cut
-    in two: ``out`` gets the first half in the requested mode, ``out2`` the second half's float32 sums."""
+    SWIGLU -> bf16 [M, N/2] from row-interleaved gate/up weights.  ``parts`` (clustered kernel, RESIDUAL only):
+    K parts whose sums are added one after the other, 0 = the kernel's own choice."""
     _common(x, w, bias, out)
     M, K = x.shape
     N = w.shape[0]
@@ -116,16 +115,15 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = Non
         cluster = 2 if cluster_supported(M, N, K, mode) else 0      # 2 measured at least as fast as 4
     if cluster and not cluster_supported(M, N, K, mode):
         cluster = 0                                   # e.g. an output row stride TMA cannot store to
-    if out2 is not None:
-        need(bool(cluster), "gemm: two K halves need the clustered kernel")
-        need(mode != SWIGLU and out2.shape == (M, N) and out2.dtype == torch.float32 and out2.is_contiguous()
-             and out.stride(0) == N, "gemm: out2 must be a contiguous float32 [M, N] (and not with SwiGLU)")
+    need(parts == 0 or (bool(cluster) and mode == RESIDUAL), "gemm: K parts need the clustered kernel and RESIDUAL")
     if cluster:
         f = fn("gemm_tcgen05_cluster", "rf_gemm_tc_cluster",
                [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                c_void_p, c_void_p, c_void_p])
+                c_int, c_void_p, c_int, c_void_p, c_void_p])
+        flags = part_flags(x.device)
         check(f(ptr(x), x.stride(0), ptr(w), ptr(bias), int(bias is not None and bias.dtype == torch.float32),
-                ptr(out), out.stride(0), M, N, K, mode, cluster, ptr(out2), ptr(status_word(x.device)), stream()),
+                ptr(out), out.stride(0), M, N, K, mode, cluster, parts, ptr(flags), flags.numel(),
+                ptr(status_word(x.device)), stream()),
               f"gemm_tc_cluster ({M}x{N}x{K}, cluster {cluster})")
         return out
     f = _f("rf_gemm_tc", c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,

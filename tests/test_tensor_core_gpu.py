@@ -60,15 +60,19 @@ def test_clustered_persistent_kernel(M, N, K, cluster):
     close(acc, want, "residual")
     close(tc.gemm_tc(x, w, mode=tc.SWIGLU, cluster=cluster), P.silu(ref[:, 0::2]) * ref[:, 1::2], "swiglu")
     assert torch.equal(tc.gemm_tc(x, w, cluster=cluster), tc.gemm_tc(x, w, cluster=0)), "both kernels sum in the same order"
-    if K >= 128:
-        # K cut in two: the first half lands in the residual stream, the second in a buffer of its own
-        acc = rnd(M, N, seed=4, dt=torch.float32)
-        half = torch.full((M, N), float("nan"), device=DEV)
-        tc.gemm_tc(x, w, mode=tc.RESIDUAL, out=acc, cluster=cluster, out2=half)
-        close((acc.double() + half.double()).float(), want, "two K halves")
-        kh = ((K + 63) // 64 + 1) // 2 * 64
-        close(half, x[:, kh:].double() @ w[:, kh:].double().t(), "second half alone")
-    assert isinstance(tc.wants_two_k_halves(2048, 3584, 18944), bool) and not tc.wants_two_k_halves(2048, 3584, 512)
+    for parts in (2, 3, 5):
+        kb = (K + 63) // 64
+        if (parts - 1) * ((kb + parts - 1) // parts) >= kb:      # a part would be empty: the kernel refuses
+            continue
+        # K cut in parts whose sums are added one after the other: the same sums in one fixed order, launch after launch
+        runs = []
+        for rep in range(2):
+            acc = rnd(M, N, seed=4, dt=torch.float32)
+            tc.gemm_tc(x, w, b, mode=tc.RESIDUAL, out=acc, cluster=cluster, parts=parts)
+            close(acc, want + b.double(), f"{parts} K parts")
+            runs.append(acc)
+        assert torch.equal(runs[0], runs[1]), "the order of the parts is fixed"
+        assert int(tc.part_flags(DEV).abs().sum()) == 0, "the counters are left zeroed"
     tc.check_status(DEV)
 
 
