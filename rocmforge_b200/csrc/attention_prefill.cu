@@ -65,8 +65,10 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
     pdl_trigger();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int gid = lane >> 2, tig = lane & 3;
-    const int seq = tiles[2 * blockIdx.x], q0 = tiles[2 * blockIdx.x + 1];
-    const int head = blockIdx.y, kvh = head / (nh / nkv);
+    // heavy tiles first: the table is sorted by the keys a tile sees and walked backwards, heads fastest
+    const int tile_idx = gridDim.y - 1 - blockIdx.y;
+    const int seq = tiles[2 * tile_idx], q0 = tiles[2 * tile_idx + 1];
+    const int head = blockIdx.x, kvh = head / (nh / nkv);
     const int start = seq_start[seq], n_new = seq_nnew[seq];
     const int* bt = block_table + (size_t)seq_slot[seq] * max_pages;
     const int row_base = cu_q[seq] + q0;                // first packed token row of the tile
@@ -323,7 +325,8 @@ static int pf_launch(const CUtensorMap& mk, const CUtensorMap& mv, const void* q
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    dim3 grid(n_tiles, nh);
+    if (n_tiles > 65535) return RF_ERR_UNSUPPORTED;     // tiles are the grid's y dimension
+    dim3 grid(nh, n_tiles);
     rf_launch(attention_prefill_kernel<HD>, grid, dim3(PF_THREADS), smem, st,
         mk, mv, reinterpret_cast<const __nv_bfloat16*>(q), q_stride, reinterpret_cast<__nv_bfloat16*>(out), out_stride,
         tiles, seq_slot, seq_start, seq_nnew, cu_q, block_table, max_pages, nh, nkv, scale, window, status);

@@ -97,10 +97,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // heavy tiles (late rows of long sequences) first: the table is walked backwards
-    const int tile_idx = gridDim.x - 1 - blockIdx.x;
+    // heavy tiles first: the table is sorted by the keys a tile sees and walked backwards, and the heads are the
+    // fast grid dimension, so the tiles with the most keys of ALL heads are handed out before any light one
+    // (tiles fastest, a head after the other, left the heavy tiles of the last heads to the end of the kernel)
+    const int tile_idx = gridDim.y - 1 - blockIdx.y;
     const int seq = tiles[2 * tile_idx], q0 = tiles[2 * tile_idx + 1];
-    const int head = blockIdx.y, kvh = head / (nh / nkv);
+    const int head = blockIdx.x, kvh = head / (nh / nkv);
     const int start = seq_start[seq], n_new = seq_nnew[seq];
     const int* bt = block_table + (size_t)seq_slot[seq] * max_pages;
     const int row_base = cu_q[seq] + q0;
@@ -343,7 +345,7 @@ static int at_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtenso
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    cudaError_t e = rf_launch(attention_prefill_tc_kernel<HD>, dim3(n_tiles, nh), dim3(AT_THREADS), smem, st, mq, mk, mv,
+    cudaError_t e = rf_launch(attention_prefill_tc_kernel<HD>, dim3(nh, n_tiles), dim3(AT_THREADS), smem, st, mq, mk, mv,
                               reinterpret_cast<__nv_bfloat16*>(out), out_stride, tiles, seq_slot, seq_start, seq_nnew, cu_q,
                               block_table, max_pages, nh, nkv, scale, window, status);
     if (e != cudaSuccess) return (int)e;
@@ -366,6 +368,7 @@ int rf_attention_prefill_tc(const void* q, int q_stride, int T, void* out, int o
                             int max_pages, int nh, int nkv, int hd, float scale, int window, int* status,
                             cudaStream_t st) {
     if (n_tiles <= 0) return 0;
+    if (n_tiles > 65535) return RF_ERR_UNSUPPORTED;      // tiles are the grid's y dimension (8 million prompt tokens)
     if (!rf_attention_prefill_tc_supported(nh, nkv, hd)) return RF_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(out) & 15) || (out_stride % 8)) return RF_ERR_BAD_ARG;
     CUtensorMap mq, mk, mv;

@@ -65,9 +65,11 @@ class StepBatch:
         # 64-row tiles of the new tokens, (sequence, first row), for the tiled attention: decided here so
         # that the device never searches
         tiles = [(i, q0) for i in range(self.B) for q0 in range(0, int(self.n_new[i]), Q_TILE)]
+        tiles.sort(key=lambda t: int(self.starts[t[0]]) + t[1])    # by the keys a tile sees: the kernels start at the end
         self.q_tiles = np.asarray(tiles, dtype=np.int32).reshape(-1)
         self.n_tiles = len(tiles)
         big = [(i, q0) for i in range(self.B) for q0 in range(0, int(self.n_new[i]), 2 * Q_TILE)]
+        big.sort(key=lambda t: int(self.starts[t[0]]) + t[1])
         self.q_tiles128 = np.asarray(big, dtype=np.int32).reshape(-1)      # for the kernel with 128-row tiles
         self.n_tiles128 = len(big)
         self.is_decode = bool((self.n_new == 1).all())
