@@ -119,18 +119,28 @@ class DeviceDescriptor:
         self.pinned = torch.zeros((n,), dtype=torch.int32)
         if self.device.type == "cuda":
             self.pinned = self.pinned.pin_memory()
+            if self._done is None:
+                self._done = torch.cuda.Event()
+        self._pinned_np = self.pinned.numpy()          # the same memory, written without a tensor per call
+        self._slices = {}                              # n -> (device slice, pinned slice)
+        self._busy = False
 
     def upload(self, packed: np.ndarray) -> None:
+        """One copy of the packed descriptor to the device, on the current stream.  This sits between a step's
+        result and the next step's launch, so it does as little on the host as it can."""
         n = packed.shape[0]
         if n > self.capacity:
             self._grow(max(n, 2 * self.capacity))
-        if self._done is not None:
+        if self._busy:
             self._done.synchronize()               # the previous copy may still read the staging buffer
-        self.pinned[:n] = torch.from_numpy(packed)
-        self.dev[:n].copy_(self.pinned[:n], non_blocking=True)
-        if self.device.type == "cuda":
-            self._done = torch.cuda.Event()
+        self._pinned_np[:n] = packed
+        pair = self._slices.get(n)
+        if pair is None:
+            pair = self._slices[n] = (self.dev[:n], self.pinned[:n])
+        pair[0].copy_(pair[1], non_blocking=True)
+        if self._done is not None:
             self._done.record()
+            self._busy = True
 
     def views(self, T: int, B: int, R: int, n_tiles: int = 0, n_tiles128: int = 0):
         lay, _ = StepBatch.layout(T, B, R, n_tiles, n_tiles128)

@@ -20,6 +20,7 @@ class ModelEngine(StepEngine):
         self.max_seq_len = cache.max_seq_len
         self.sampler = DeviceSampler(model.device)
         self._calls = 0
+        self._host_ids = None            # pinned buffer for the sampled ids
         self.decode_runner = None
         if model.options.decode_graphs:
             from .graph import DecodeRunner
@@ -37,6 +38,18 @@ class ModelEngine(StepEngine):
             n += 1
         return n
 
+    def _to_host(self, out: torch.Tensor) -> List[int]:
+        """The sampled ids on the host: through a pinned buffer, so that the copy is one call and one wait."""
+        n = out.numel()
+        if self._host_ids is None or self._host_ids.numel() < n or self._host_ids.dtype != out.dtype:
+            self._host_ids = torch.empty((max(n, 64),), dtype=out.dtype).pin_memory()
+            self._host_np = self._host_ids.numpy()
+            self._host_done = torch.cuda.Event()
+        self._host_ids[:n].copy_(out.reshape(-1), non_blocking=True)
+        self._host_done.record()
+        self._host_done.synchronize()
+        return self._host_np[:n].tolist()
+
     def alloc_slot(self) -> int:
         return self.cache.alloc_slot()
 
@@ -53,7 +66,7 @@ class ModelEngine(StepEngine):
             reqs = [StepRequest(s, t, [len(t) - 1]) for s, t in zip(slots, tokens)]
             logits = self.model.step(self.cache, reqs)
             out = self.sampler.sample(logits, sampling, requests, draws)
-        ids = out.cpu().tolist()
+        ids = self._to_host(out)
         self._calls += 1
         if self._calls % 64 == 0:          # a separate small read: not on every step
             kernels.tensor_core.check_status(self.model.device)
