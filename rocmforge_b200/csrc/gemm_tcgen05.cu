@@ -7,7 +7,7 @@
 // Two orientations share the kernel.  "tokens as rows" (prefill): the 128 accumulator lanes
 // are token rows, a CTA owns a 128 x BN tile of D.  "weights as rows" (decode, few tokens):
 // the 128 lanes are weight rows and the tokens are the MMA's N (16..64), so that a step with
-// 1..64 tokens still streams every weight once with full 128-row MMAs; K may be split
+// few tokens (tiles of up to 64) still streams every weight once with full 128-row MMAs; K may be split
 // across CTAs (grid.z), each split writing its own 32-bit partial sums, which the next
 // add+RMSNorm kernel adds in index order (no atomics: the result never depends on timing).
 // Epilogues: + bias, 32-bit output, accumulate into the 32-bit residual stream, and
@@ -218,11 +218,12 @@ int rf_gemm_tc(const void* X, int ldx, const void* W, const void* bias, int bias
     return launch_cfg<128, false, 6>(ma, mb, p, grid, st);
 }
 
-// Weights as rows, for M <= 64 tokens.  splits > 1 requires mode PARTIAL: out is then
+// Weights as rows, for M <= 256 tokens in tiles of up to 64 (the tiles of one weight tile are neighbours in the grid,
+// so the weight comes from memory once and from L2 after that).  splits > 1 requires mode PARTIAL: out is then
 // [splits, M, N] float32 (partial_stride = M * N) and holds the partial sums of each K range.
 int rf_gemm_tc_skinny(const void* X, int ldx, const void* W, const void* bias, int bias_is_f32, void* out, int ldo,
                       int M, int N, int K, int mode, int splits, int* status, cudaStream_t st) {
-    if (!rf_gemm_tc_supported(M, N, K, mode) || M > 64 || splits < 1) return RF_ERR_UNSUPPORTED;
+    if (!rf_gemm_tc_supported(M, N, K, mode) || M > 256 || splits < 1) return RF_ERR_UNSUPPORTED;
     if (splits > 1 && mode != EPI_PARTIAL) return RF_ERR_BAD_ARG;
     const int kb = (K + TC_BK - 1) / TC_BK;
     const int per = (kb + splits - 1) / splits;
@@ -232,7 +233,7 @@ int rf_gemm_tc_skinny(const void* X, int ldx, const void* W, const void* bias, i
     int e;
     const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
     if ((e = make_map(&ma, W, N, K, K, TC_BM)) || (e = make_map(&mb, X, M, K, ldx, bn))) return e;
-    dim3 grid(1, (N + TC_BM - 1) / TC_BM, splits);
+    dim3 grid((M + bn - 1) / bn, (N + TC_BM - 1) / TC_BM, splits);      // token tiles fastest: they share a weight tile in L2
     // stage counts chosen so that two CTAs share an SM: their pipelines overlap each other's
     // start-up and epilogue, and 2 x stages x 16 KB of weight bytes are in flight per SM
     if (bn == 16) return launch_cfg<16, true, 6>(ma, mb, p, grid, st);

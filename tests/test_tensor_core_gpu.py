@@ -45,7 +45,8 @@ def test_tokens_as_rows(M, N, K):
 
 @pytest.mark.parametrize("cluster", [2, 4])
 @pytest.mark.parametrize("M,N,K", [(256, 256, 64), (300, 520, 1000), (2048, 4608, 3584), (1100, 3584, 18944),
-                                   (257, 1000, 3584), (640, 37888, 3584)])
+                                   (257, 1000, 3584), (640, 37888, 3584), (65, 3584, 3584), (128, 4608, 3584),
+                                   (200, 3584, 18944)])
 def test_clustered_persistent_kernel(M, N, K, cluster):
     from rocmforge_b200.kernels import tensor_core as tc
     if not tc.cluster_available():
@@ -76,7 +77,7 @@ def test_clustered_persistent_kernel(M, N, K, cluster):
     tc.check_status(DEV)
 
 
-@pytest.mark.parametrize("M", [1, 3, 8, 16, 17, 33, 64])
+@pytest.mark.parametrize("M", [1, 3, 8, 16, 17, 33, 64, 65, 100, 128])
 @pytest.mark.parametrize("N,K", [(128, 64), (200, 136), (3584, 3584), (1000, 18944), (4608, 3584)])
 def test_weights_as_rows(M, N, K):
     from rocmforge_b200.kernels import tensor_core as tc
@@ -119,6 +120,6 @@ def test_refusals():
     with pytest.raises(KernelError):
         tc.gemm_tc(rnd(4, 12), rnd(8, 12))
     with pytest.raises(KernelError):
-        tc.gemm_tc_skinny(rnd(65, 64), rnd(128, 64))
+        tc.gemm_tc_skinny(rnd(tc.SKINNY_MAX_TOKENS + 1, 64), rnd(128, 64))
     with pytest.raises(KernelError):
         tc.gemm_tc(rnd(4, 64, dt=torch.float32), rnd(8, 64, dt=torch.float32))
