@@ -218,7 +218,7 @@ int rf_gemm_tc(const void* X, int ldx, const void* W, const void* bias, int bias
     return launch_cfg<128, false, 6>(ma, mb, p, grid, st);
 }
 
-// Weights as rows, for M <= 256 tokens in tiles of up to 64 (the tiles of one weight tile are neighbours in the grid,
+// Weights as rows, for M <= 256 tokens in tiles of up to 128 (the tiles of one weight tile are neighbours in the grid,
 // so the weight comes from memory once and from L2 after that).  splits > 1 requires mode PARTIAL: out is then
 // [splits, M, N] float32 (partial_stride = M * N) and holds the partial sums of each K range.
 int rf_gemm_tc_skinny(const void* X, int ldx, const void* W, const void* bias, int bias_is_f32, void* out, int ldo,
@@ -231,14 +231,17 @@ int rf_gemm_tc_skinny(const void* X, int ldx, const void* W, const void* bias, i
     TcParams p{out, bias, bias_is_f32, M, N, K, ldo, mode, per, (long long)M * ldo, status, 1};
     CUtensorMap ma, mb;
     int e;
-    const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
     if ((e = make_map(&ma, W, N, K, K, TC_BM)) || (e = make_map(&mb, X, M, K, ldx, bn))) return e;
     dim3 grid((M + bn - 1) / bn, (N + TC_BM - 1) / TC_BM, splits);      // token tiles fastest: they share a weight tile in L2
     // stage counts chosen so that two CTAs share an SM: their pipelines overlap each other's
-    // start-up and epilogue, and 2 x stages x 16 KB of weight bytes are in flight per SM
+    // start-up and epilogue, and 2 x stages x 16 KB of weight bytes are in flight per SM.  (128 tokens:
+    // two CTAs with three 32 KB stages each, 5.09 ms a decode step of the 7B shape; one CTA with six
+    // stages 6.46 ms; two tiles of 64 tokens sharing the weight tile through L2 5.65 ms.)
     if (bn == 16) return launch_cfg<16, true, 6>(ma, mb, p, grid, st);
     if (bn == 32) return launch_cfg<32, true, 5>(ma, mb, p, grid, st);
-    return launch_cfg<64, true, 4>(ma, mb, p, grid, st);
+    if (bn == 64) return launch_cfg<64, true, 4>(ma, mb, p, grid, st);
+    return launch_cfg<128, true, 3>(ma, mb, p, grid, st);
 }
 
 }

@@ -10,7 +10,7 @@ from ._ffi import KernelError, c_int, c_ll, c_void_p, check, fn, need, need_cuda
 
 STORE, F32, RESIDUAL, SWIGLU, PARTIAL = 0, 1, 2, 3, 4
 SKINNY_MAX_TOKENS = 128     # above it the large-M kernels stream the weights better (7B shape, decode step: 128 tokens
-                            # 5.65 ms skinny / 6.38 ms clustered, 192 tokens 7.78 / 6.73)
+                            # 5.09 ms skinny / 6.38 ms clustered; 192 tokens as tiles of 64: 7.78 / 6.73)
 
 _status = {}
 
@@ -149,7 +149,7 @@ def split_k_for(N: int, K: int, sm_count: int = 148) -> int:
 
 def gemm_tc_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, *, mode: int = STORE,
                    splits: int = 1, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Weights as accumulator rows, for few tokens (tiles of up to 64 tokens share a weight tile through L2).  With ``splits`` > 1 the mode must be PARTIAL and
+    """Weights as accumulator rows, for few tokens (up to 128 in one tile).  With ``splits`` > 1 the mode must be PARTIAL and
     the result is the float32 stack [splits, M, N] of partial sums."""
     _common(x, w, bias, out)
     M, K = x.shape
