@@ -144,22 +144,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     // lane = weight row n, registers = consecutive tokens m
                     const int n = row_a, m0 = tile_b * BN + c0;
                     const float b = (p.bias && n < p.N) ? load_vec(p.bias, p.bias_is_f32, n) : 0.f;
+                    if (m0 >= p.M) break;                // the tile's other columns are padding, not tokens
+                    if (p.mode == EPI_SWIGLU) {
+                        // gate in even lanes, up in the odd lane beside it.  Two tokens at a time: the even lane
+                        // finishes token j (it gets that token's up), the odd lane token j + 1 (it gets its gate),
+                        // so every lane evaluates one silu per pair of tokens and every lane stores.
+                        const bool odd = lane & 1;
 #pragma unroll
-                    for (int j = 0; j < CH; ++j) {
-                        const int m = m0 + j;
-                        float v = __uint_as_float(r[j]) + b;
-                        if (p.mode == EPI_SWIGLU) {
-                            // gate in even lanes, up in the odd lane beside it
-                            const float u = __shfl_down_sync(0xffffffffu, v, 1);
-                            if (!(lane & 1) && m < p.M && n + 1 < p.N)
+                        for (int j = 0; j < CH; j += 2) {
+                            const float v0 = __uint_as_float(r[j]) + b, v1 = __uint_as_float(r[j + 1]) + b;
+                            const float got = __shfl_xor_sync(0xffffffffu, odd ? v0 : v1, 1);
+                            const float g = odd ? got : v0, u = odd ? v1 : got;
+                            const int m = m0 + j + (odd ? 1 : 0);
+                            if (m < p.M && (n | 1) < p.N)
                                 reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + (n >> 1)] =
-                                    __float2bfloat16_rn(v / (1.f + expf(-v)) * u);
-                        } else if (m < p.M && n < p.N) {
-                            const size_t o = (size_t)m * p.ldo + n;
-                            if (p.mode == EPI_STORE) reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(v);
-                            else if (p.mode == EPI_F32) reinterpret_cast<float*>(p.out)[o] = v;
-                            else if (p.mode == EPI_RESIDUAL) reinterpret_cast<float*>(p.out)[o] += v;
-                            else reinterpret_cast<float*>(p.out)[(size_t)split * p.partial_stride + o] = v;
+                                    __float2bfloat16_rn(silu_fast(g) * u);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < CH; ++j) {
+                            const int m = m0 + j;
+                            const float v = __uint_as_float(r[j]) + b;
+                            if (m < p.M && n < p.N) {
+                                const size_t o = (size_t)m * p.ldo + n;
+                                if (p.mode == EPI_STORE) reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(v);
+                                else if (p.mode == EPI_F32) reinterpret_cast<float*>(p.out)[o] = v;
+                                else if (p.mode == EPI_RESIDUAL) reinterpret_cast<float*>(p.out)[o] += v;
+                                else reinterpret_cast<float*>(p.out)[(size_t)split * p.partial_stride + o] = v;
+                            }
                         }
                     }
                 }
