@@ -135,20 +135,38 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     cluster_sync_all();                                  // every CTA's barriers exist before anyone signals them
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    pdl_wait();                                          // activations in, outputs out: both belong to the step's chain
 
     if (warp == 0) {
         if (lane == 0) {
+            // The weights do not depend on the kernel before this one: the ring's first lap gets its weight
+            // tiles at once; the activations follow into the same stages after the dependency wait.
+            int pre = 0;
+            if (cluster_id < n_work) {
+                const int tile_n = (cluster_id / groups_m) % tiles_n;
+                const int kb0 = (cluster_id / n_tiles) * kb_part, kb1 = min(kb_all, kb0 + kb_part);
+                pre = min(S, kb1 - kb0);
+                for (int i = 0; i < pre; ++i) {
+                    const uint32_t full = smem_u32(&bars[i]);
+                    mbar_expect_tx(full, stage_tx);
+                    tma_load_2d_multicast(smem_u32(smem + i * STAGE_BYTES) + A_BYTES + rank * b_part, &map_b,
+                                          (kb0 + i) * TC_BK, tile_n * bn + (int)rank * (bn / CL), full, all);
+                }
+            }
+            pdl_wait();
             int it = 0;                                  // running k-block count across work items
             for (int w = cluster_id; w < n_work && !abort_flag; w += n_clusters) {
                 const int tile_m = (w % groups_m) * CL + (int)rank, tile_n = (w / groups_m) % tiles_n;
                 const int kb0 = (w / n_tiles) * kb_part, kb1 = min(kb_all, kb0 + kb_part);
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % S;
-                    if (!mbar_wait(smem_u32(&bars[S + s]), ((it / S) & 1) ^ 1, &abort_flag)) break;
                     const uint32_t full = smem_u32(&bars[s]);
-                    mbar_expect_tx(full, stage_tx);
                     const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+                    if (it < pre) {                      // armed above, the weights are on their way
+                        tma_load_2d(sa, &map_a, kb * TC_BK, tile_m * TC_BM, full);
+                        continue;
+                    }
+                    if (!mbar_wait(smem_u32(&bars[S + s]), ((it / S) & 1) ^ 1, &abort_flag)) break;
+                    mbar_expect_tx(full, stage_tx);
                     tma_load_2d(sa, &map_a, kb * TC_BK, tile_m * TC_BM, full);
                     tma_load_2d_multicast(sa + A_BYTES + rank * b_part, &map_b, kb * TC_BK,
                                           tile_n * bn + (int)rank * (bn / CL), full, all);
@@ -185,6 +203,7 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     } else {
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;             // this thread's row of the tile
+        pdl_wait();                                      // the output may still be read by the kernel before this one
         const bool leader = (warp == 2 && lane == 0);    // hands the slabs to TMA
         int local = 0, slab = 0;
         for (int w = cluster_id; w < n_work; w += n_clusters, ++local) {
