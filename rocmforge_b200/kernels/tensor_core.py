@@ -28,6 +28,8 @@ def check_status(device) -> None:
     key = str(device)
     if key in _status and int(_status[key].item()) != 0:
         _status[key].zero_()
+        for flags in _part_flags.values():         # a kernel that gave up may have left its K-part counters behind
+            flags.zero_()
         raise KernelError("a tensor-core kernel ran out of its wait limit (a copy or an MMA never completed); "
                           "its results are invalid")
 
