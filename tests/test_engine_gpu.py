@@ -346,3 +346,27 @@ def test_graph_replay_equals_plain_steps(folders, name, dtype):
     rb = b.generate(prompts, max_tokens=70, temperature=0.0, stop_token_ids=[])
     assert a.engine.decode_runner.replays > 0 and b.engine.decode_runner is None
     assert [r.tokens for r in ra] == [r.tokens for r in rb]
+
+
+def test_graph_decode_across_length_buckets(folders):
+    """Replayed decode steps whose graphs are captured per (batch, length bucket): sequences that grow from under 512 keys to
+    over it (a window of 200 in one layer), the shorter ones ending earlier, against the plain model."""
+    from rocmforge_b200 import StepRequest
+    from rocmforge_b200.engine.graph import DecodeRunner
+    m, p = engine(folders, "E", "bfloat16"), plain(folders, "E", "bfloat16")
+    V = CONFIGS["E"]["vocab_size"]
+    lens = [(450, 120), (500, 40), (440, 30)]
+    seqs = [random_tokens(V, a + b, 300 + i) for i, (a, b) in enumerate(lens)]
+    refs = [p.logits(t) for t in seqs]
+    cache = m.new_cache(max_tokens=64 * 40, max_slots=4)
+    poison_free_pages(cache)
+    runner = DecodeRunner(m, cache)
+    slots = [cache.alloc_slot() for _ in lens]
+    m.step(cache, [StepRequest(s, t[:a], []) for s, t, (a, _) in zip(slots, seqs, lens)])
+    live = list(range(len(lens)))
+    for step in range(max(b for _, b in lens)):
+        for i in [i for i in live if lens[i][1] <= step]:
+            cache.free_slot(slots[i]); live.remove(i)
+        got = runner.logits([slots[i] for i in live], [seqs[i][lens[i][0] + step] for i in live]).cpu()
+        assert_logits_close(got, torch.stack([refs[i][lens[i][0] + step] for i in live]), "bfloat16", f"step {step}")
+    assert {k[1] for k in runner.graphs} >= {512, 1024}
