@@ -62,6 +62,15 @@ extern "C" int rf_argmax(const float* logits, int rows, int V, long long row_str
 // position in that order is found through the order-preserving 32-bit key of its bits, eight
 // bits at a time (four passes over the row per search), with probability mass counted in
 // 2^-40 fixed point so that the sums are exact integers and do not depend on thread timing.
+//
+// A row is worked on by a thread-block cluster of 8, 4, 2 or 1 CTAs (the more, the fewer rows), each on its slice of the
+// vocabulary (a step samples a handful of rows while 148 SMs are idle; one CTA per row spent 3.7 ms on 152,064 logits).
+// Every pass ends in a collective: each CTA leaves its histogram (or partial sum, or count) in its own
+// shared memory, one cluster barrier, then EVERY CTA reads all contributions through distributed
+// shared memory, adds them in rank order and takes the same decision; the buffers alternate, so a CTA may
+// start its next pass while a peer still reads the last one.  Inside a CTA the lanes of a warp that hit the
+// same histogram bin are found with match.any and added as one atomic (logits share their upper key bits:
+// without this nearly all atomics of the first passes hit one address).
 #define SMP_THREADS 1024
 
 __device__ __forceinline__ unsigned key_of(float x) {
@@ -69,20 +78,55 @@ __device__ __forceinline__ unsigned key_of(float x) {
     return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
 }
 
-struct SampleShared;
-
 struct SampleShared {
-    unsigned long long mass[256];
-    unsigned cnt[256];
+    unsigned long long mass[2][256];    // this CTA's histograms, two buffers
+    unsigned cnt[2][256];
+    unsigned long long all_mass[256];   // the cluster's, summed by this CTA
+    unsigned all_cnt[256];
+    unsigned long long grp_mass[32];    // ... in groups of eight bins
+    unsigned grp_cnt[32];
+    double part64[2];                   // this CTA's partial sum
+    float part32[2];                    // ... maximum
+    unsigned count[2];                  // ... number of matches
+    int found[2];                       // an index that its owner pushes to every CTA
     float red[34];
     double red64[34];
     unsigned scan[33];
-    // results broadcast by thread 0
-    unsigned prefix, mask;
+    unsigned prefix, mask;              // the descent's state: the same in every CTA
     unsigned long long acc, mass_eq;
     unsigned n_eq;
-    int chosen, index;
+    int index;
 };
+
+__device__ __forceinline__ unsigned smp_rank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ unsigned smp_nranks() {
+    unsigned n;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(n));
+    return n;
+}
+__device__ __forceinline__ void smp_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t smp_remote(const void* local, unsigned rank) {
+    uint32_t a;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"((uint32_t)__cvta_generic_to_shared(local)), "r"(rank));
+    return a;
+}
+__device__ __forceinline__ unsigned smp_ld_u32(const void* local, unsigned rank) {
+    unsigned v;
+    asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(smp_remote(local, rank)) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned long long smp_ld_u64(const void* local, unsigned rank) {
+    unsigned long long v;
+    asm volatile("ld.shared::cluster.u64 %0, [%1];" : "=l"(v) : "r"(smp_remote(local, rank)) : "memory");
+    return v;
+}
 
 // Sum of one double per thread, in a tree fixed by the block size; every thread gets it.
 __device__ __forceinline__ double block_sum_f64(double v, double* red) {
@@ -102,42 +146,125 @@ __device__ __forceinline__ double block_sum_f64(double v, double* red) {
     return red[32];
 }
 
-// n-th (1-based) smallest index i with in-set key(i) == K; every thread returns it.
-__device__ int nth_index_with_key(const float* x, int V, unsigned K, int limit_index, unsigned n, SampleShared& s) {
-    const int chunk = (V + SMP_THREADS - 1) / SMP_THREADS;
-    const int lo = threadIdx.x * chunk, hi = min(V, lo + chunk);
-    unsigned c = 0;
-    for (int i = lo; i < hi; ++i) c += (key_of(x[i]) == K && i <= limit_index);
-    // exclusive scan of c over the block
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    unsigned inc = c;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const unsigned v = __shfl_up_sync(0xffffffffu, inc, o);
-        if (lane >= o) inc += v;
+// ---- collectives of the cluster; `e` counts them and picks the buffer
+__device__ float cluster_max(float v, SampleShared& s, int& e) {
+    const int b = e++ & 1;
+    v = block_max(v, s.red);
+    if (threadIdx.x == 0) s.part32[b] = v;
+    smp_cluster_sync();
+    if (threadIdx.x == 0) {
+        float m = -INFINITY;
+        for (unsigned r = 0; r < smp_nranks(); ++r) m = fmaxf(m, __uint_as_float(smp_ld_u32(&s.part32[b], r)));
+        s.red[33] = m;
     }
     __syncthreads();
-    if (lane == 31) s.scan[warp] = inc;
-    if (threadIdx.x == 0) s.index = -1;
+    return s.red[33];
+}
+__device__ double cluster_sum_f64(double v, SampleShared& s, int& e) {
+    const int b = e++ & 1;
+    v = block_sum_f64(v, s.red64);
+    if (threadIdx.x == 0) s.part64[b] = v;
+    smp_cluster_sync();
+    if (threadIdx.x == 0) {
+        double t = 0.0;
+        for (unsigned r = 0; r < smp_nranks(); ++r) t += __longlong_as_double((long long)smp_ld_u64(&s.part64[b], r));   // rank order
+        s.red64[33] = t;
+    }
     __syncthreads();
-    if (warp == 0) {
-        unsigned w = s.scan[lane];
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const unsigned v = __shfl_up_sync(0xffffffffu, w, o);
-            if (lane >= o) w += v;
+    return s.red64[33];
+}
+// the CTAs' histograms of buffer b (complete in each CTA) -> all_cnt / all_mass in every CTA
+__device__ void cluster_histogram(SampleShared& s, int b, bool with_mass) {
+    __syncthreads();
+    smp_cluster_sync();
+    if (threadIdx.x < 256) {
+        unsigned c = 0;
+        unsigned long long m = 0;
+        for (unsigned r = 0; r < smp_nranks(); ++r) {
+            c += smp_ld_u32(&s.cnt[b][threadIdx.x], r);
+            if (with_mass) m += smp_ld_u64(&s.mass[b][threadIdx.x], r);
         }
-        s.scan[lane] = w - s.scan[lane];           // exclusive per-warp offset
+        s.all_cnt[threadIdx.x] = c;
+        s.all_mass[threadIdx.x] = m;
+        // sums of groups of eight bins, so that the one thread that walks the histogram takes 32 + 8 steps, not 256
+        unsigned gc = c;
+        unsigned long long gm = m;
+#pragma unroll
+        for (int o = 1; o < 8; o <<= 1) {
+            gc += __shfl_xor_sync(0xffffffffu, gc, o);
+            gm += __shfl_xor_sync(0xffffffffu, gm, o);
+        }
+        if ((threadIdx.x & 7) == 0) { s.grp_cnt[threadIdx.x >> 3] = gc; s.grp_mass[threadIdx.x >> 3] = gm; }
     }
     __syncthreads();
-    const unsigned before = s.scan[warp] + inc - c;
-    if (c > 0 && before < n && n <= before + c) {
-        unsigned seen = before;
-        for (int i = lo; i < hi; ++i)
-            if (key_of(x[i]) == K && i <= limit_index && ++seen == n) { s.index = i; break; }
+}
+// one element into buffer b's histogram: the lanes of a warp with the same bin add as one
+__device__ __forceinline__ void histogram_add(SampleShared& s, int b, bool valid, int bin, unsigned long long w, bool with_mass) {
+    const unsigned act = __ballot_sync(0xffffffffu, valid);
+    if (!valid) return;
+    const unsigned peers = __match_any_sync(act, bin);
+    // a weight is below 2^40 (+ rounding): halves of 20 and 21 bits, 32 of which add up inside 32 bits
+    const unsigned lo = __reduce_add_sync(peers, (unsigned)(w & 0xfffffu));
+    const unsigned hi = __reduce_add_sync(peers, (unsigned)(w >> 20));
+    if ((threadIdx.x & 31) == __ffs(peers) - 1) {
+        atomicAdd(&s.cnt[b][bin], (unsigned)__popc(peers));
+        if (with_mass) atomicAdd(&s.mass[b][bin], ((unsigned long long)hi << 20) + lo);
+    }
+}
+
+// n-th (1-based) smallest index i of the row with key(i) == K and i <= limit_index; every thread of every CTA returns it.
+__device__ int nth_index_with_key(const float* x, int lo, int hi, unsigned K, int limit_index, unsigned n,
+                                  SampleShared& s, int& e) {
+    const int b = e++ & 1;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = SMP_THREADS / 32;
+    // a warp owns a contiguous piece of the CTA's slice, in steps of 32 indices
+    const int seg = ((hi - lo + nwarp - 1) / nwarp + 31) / 32 * 32;
+    const int wlo = lo + warp * seg, whi = min(hi, wlo + seg);
+    unsigned c = 0;
+    for (int i = wlo + lane; i < whi; i += 32) c += (key_of(x[i]) == K && i <= limit_index);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+    __syncthreads();
+    if (lane == 0) s.scan[warp] = c;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned t = 0;
+        for (int w = 0; w < nwarp; ++w) { const unsigned v = s.scan[w]; s.scan[w] = t; t += v; }     // exclusive
+        s.count[b] = t;
+        s.found[b] = -1;
     }
     __syncthreads();
-    return s.index;
+    smp_cluster_sync();
+    // matches in the CTAs before this one
+    unsigned before_cta = 0, mine = 0;
+    const unsigned rank = smp_rank();
+    for (unsigned r = 0; r < smp_nranks(); ++r) {
+        const unsigned v = smp_ld_u32(&s.count[b], r);
+        if (r < rank) before_cta += v;
+        if (r == rank) mine = v;
+    }
+    if (before_cta < n && n <= before_cta + mine) {      // the n-th lies in this CTA: which warp, which index
+        const unsigned before = before_cta + s.scan[warp];
+        if (c > 0 && before < n && n <= before + c) {
+            unsigned seen = before;
+            for (int base = wlo; base < whi; base += 32) {
+                const int i = base + lane;
+                const bool m = i < whi && key_of(x[i]) == K && i <= limit_index;
+                const unsigned bal = __ballot_sync(0xffffffffu, m);
+                const unsigned k = __popc(bal);
+                if (seen + k >= n) {
+                    const int idx = base + __fns(bal, 0, n - seen);
+                    if (lane == 0)
+                        for (unsigned r = 0; r < smp_nranks(); ++r)
+                            asm volatile("st.shared::cluster.s32 [%0], %1;" ::"r"(smp_remote(&s.found[b], r)), "r"(idx) : "memory");
+                    break;
+                }
+                seen += k;
+            }
+        }
+    }
+    smp_cluster_sync();
+    return s.found[b];
 }
 
 __global__ void __launch_bounds__(SMP_THREADS)
@@ -147,13 +274,19 @@ sample_kernel(const float* __restrict__ logits, int V, long long row_stride, flo
     pdl_trigger();
     pdl_wait();
     __shared__ SampleShared s;
-    const float* x = logits + (size_t)blockIdx.x * row_stride;
+    const int cl = (int)smp_nranks();
+    const int row = blockIdx.x / cl;
+    const unsigned rank = smp_rank();
+    const float* x = logits + (size_t)row * row_stride;
     const int tid = threadIdx.x;
     const float t = fmaxf(temperature, 1e-6f);
+    const int slice = (V + cl - 1) / cl;
+    const int lo = min(V, (int)rank * slice), hi = min(V, lo + slice);       // this CTA's indices
+    int e = 0;                                                               // collectives so far
 
     float mx = -INFINITY;
-    for (int i = tid; i < V; i += SMP_THREADS) mx = fmaxf(mx, x[i]);
-    mx = block_max(mx, s.red);
+    for (int i = lo + tid; i < hi; i += SMP_THREADS) mx = fmaxf(mx, x[i]);
+    mx = cluster_max(mx, s, e);
     const float mx_t = mx / t;
 
     // ---- top-k: key Kk of the k-th largest logit and the largest index Ik still inside among its equals
@@ -162,24 +295,29 @@ sample_kernel(const float* __restrict__ logits, int V, long long row_stride, flo
     if (top_k > 0 && top_k < V) {
         if (tid == 0) { s.prefix = 0; s.mask = 0; s.acc = (unsigned long long)top_k; }
         for (int pass = 0; pass < 4; ++pass) {
-            const int shift = 24 - 8 * pass;
-            if (tid < 256) s.cnt[tid] = 0;
+            const int shift = 24 - 8 * pass, b = e++ & 1;
+            if (tid < 256) s.cnt[b][tid] = 0;
             __syncthreads();
             const unsigned prefix = s.prefix, mask = s.mask;
-            for (int i = tid; i < V; i += SMP_THREADS) {
-                const unsigned k = key_of(x[i]);
-                if ((k & mask) == prefix) atomicAdd(&s.cnt[(k >> shift) & 255], 1u);
+            for (int i0 = lo; i0 < hi; i0 += SMP_THREADS) {
+                const int i = i0 + tid;
+                const unsigned k = i < hi ? key_of(x[i]) : 0u;
+                histogram_add(s, b, i < hi && (k & mask) == prefix, (k >> shift) & 255, 0, false);
             }
-            __syncthreads();
+            cluster_histogram(s, b, false);
             if (tid == 0) {
                 unsigned long long remaining = s.acc;
                 int chosen = 0;
-                for (int b = 255; b >= 0; --b) {
-                    if (s.cnt[b] >= remaining) { chosen = b; break; }
-                    remaining -= s.cnt[b];
+                for (int g = 31; g >= 0; --g) {                  // bins from 255 down, a group of eight at a time
+                    if (s.grp_cnt[g] < remaining) { remaining -= s.grp_cnt[g]; continue; }
+                    for (int bin = g * 8 + 7; bin >= g * 8; --bin) {
+                        if (s.all_cnt[bin] >= remaining) { chosen = bin; break; }
+                        remaining -= s.all_cnt[bin];
+                    }
+                    break;
                 }
                 s.acc = remaining;
-                s.n_eq = s.cnt[chosen];
+                s.n_eq = s.all_cnt[chosen];
                 s.prefix = prefix | ((unsigned)chosen << shift);
                 s.mask = mask | (0xffu << shift);
             }
@@ -188,34 +326,43 @@ sample_kernel(const float* __restrict__ logits, int V, long long row_stride, flo
         Kk = s.prefix;
         const unsigned need = (unsigned)s.acc, n_eq = s.n_eq;
         __syncthreads();
-        if (need < n_eq) Ik = nth_index_with_key(x, V, Kk, V, need, s);
+        if (need < n_eq) Ik = nth_index_with_key(x, lo, hi, Kk, V, need, s, e);
     }
 #define IN_SET(k, i) ((k) > Kk || ((k) == Kk && (i) <= Ik))
 
     // ---- softmax denominator over the set
     double part = 0.0;
-    for (int i = tid; i < V; i += SMP_THREADS) {
+    for (int i = lo + tid; i < hi; i += SMP_THREADS) {
         const unsigned k = key_of(x[i]);
         if (IN_SET(k, i)) part += (double)expf(x[i] / t - mx_t);
     }
-    const double total = block_sum_f64(part, s.red64);
-#define WEIGHT(i) ((unsigned long long)((double)expf(x[i] / t - mx_t) / total * 1099511627776.0))
+    const double total = cluster_sum_f64(part, s, e);
+    const double to_fixed = 1099511627776.0 / total;                         // probabilities in units of 2^-40
+#define WEIGHT(i) ((unsigned long long)((double)expf(x[i] / t - mx_t) * to_fixed))
 
     // descent: the key at which the running mass (descending order) reaches `target`
-    unsigned long long target, C;
+    unsigned long long target, C = 0;
     unsigned Kp = Kk;
     int Ip = Ik;
     for (int phase = 0; phase < 2; ++phase) {
         if (phase == 0) {
             if (top_p >= 1.f) {                      // the nucleus is the whole set: C = its mass
+                const int b = e++ & 1;
                 unsigned long long m = 0;
-                for (int i = tid; i < V; i += SMP_THREADS) {
+                for (int i = lo + tid; i < hi; i += SMP_THREADS) {
                     const unsigned k = key_of(x[i]);
                     if (IN_SET(k, i)) m += WEIGHT(i);
                 }
-                if (tid == 0) s.acc = 0;
+                if (tid == 0) s.mass[b][0] = 0;
                 __syncthreads();
-                atomicAdd(&s.acc, m);
+                atomicAdd(&s.mass[b][0], m);
+                __syncthreads();
+                smp_cluster_sync();
+                if (tid == 0) {
+                    unsigned long long c = 0;
+                    for (unsigned r = 0; r < smp_nranks(); ++r) c += smp_ld_u64(&s.mass[b][0], r);
+                    s.acc = c;
+                }
                 __syncthreads();
                 C = s.acc;
                 __syncthreads();
@@ -223,7 +370,7 @@ sample_kernel(const float* __restrict__ logits, int V, long long row_stride, flo
             }
             target = (unsigned long long)((double)top_p * 1099511627776.0);
         } else {
-            unsigned long long seed = seeds[blockIdx.x];
+            unsigned long long seed = seeds[row];
             if (draw_counter) seed += (unsigned long long)(*draw_counter);
             const unsigned long long v = seed * 6364136223846793005ULL + 1442695040888963407ULL;
             const float u = (float)(v >> 11) / 9007199254740992.0f;
@@ -232,32 +379,39 @@ sample_kernel(const float* __restrict__ logits, int V, long long row_stride, flo
         }
         if (tid == 0) { s.prefix = 0; s.mask = 0; s.acc = 0; }
         for (int pass = 0; pass < 4; ++pass) {
-            const int shift = 24 - 8 * pass;
-            if (tid < 256) { s.cnt[tid] = 0; s.mass[tid] = 0; }
+            const int shift = 24 - 8 * pass, b = e++ & 1;
+            if (tid < 256) { s.cnt[b][tid] = 0; s.mass[b][tid] = 0; }
             __syncthreads();
             const unsigned prefix = s.prefix, mask = s.mask;
-            for (int i = tid; i < V; i += SMP_THREADS) {
-                const unsigned k = key_of(x[i]);
-                if ((k & mask) == prefix && IN_SET(k, i)) {
-                    const int b = (k >> shift) & 255;
-                    atomicAdd(&s.cnt[b], 1u);
-                    atomicAdd(&s.mass[b], WEIGHT(i));
-                }
+            for (int i0 = lo; i0 < hi; i0 += SMP_THREADS) {
+                const int i = i0 + tid;
+                const unsigned k = i < hi ? key_of(x[i]) : 0u;
+                const bool valid = i < hi && (k & mask) == prefix && IN_SET(k, i);
+                histogram_add(s, b, valid, (k >> shift) & 255, valid ? WEIGHT(i) : 0ull, true);
             }
-            __syncthreads();
+            cluster_histogram(s, b, true);
             if (tid == 0) {
                 unsigned long long acc = s.acc;
                 int chosen = -1, last = -1;
-                for (int b = 255; b >= 0; --b) {
-                    if (s.cnt[b] == 0) continue;
-                    last = b;
-                    if (acc + s.mass[b] >= target) { chosen = b; break; }
-                    acc += s.mass[b];
+                for (int g = 31; g >= 0 && chosen < 0; --g) {    // bins from 255 down, a group of eight at a time
+                    if (s.grp_cnt[g] == 0) continue;
+                    if (acc + s.grp_mass[g] < target) {          // the whole group lies before the target
+                        acc += s.grp_mass[g];
+                        for (int bin = g * 8; bin < g * 8 + 8; ++bin)
+                            if (s.all_cnt[bin]) { last = bin; break; }       // its lowest bin in use
+                        continue;
+                    }
+                    for (int bin = g * 8 + 7; bin >= g * 8; --bin) {
+                        if (s.all_cnt[bin] == 0) continue;
+                        last = bin;
+                        if (acc + s.all_mass[bin] >= target) { chosen = bin; break; }
+                        acc += s.all_mass[bin];
+                    }
                 }
-                if (chosen < 0) { chosen = last < 0 ? 0 : last; acc -= (last < 0 ? 0 : s.mass[chosen]); }
+                if (chosen < 0) { chosen = last < 0 ? 0 : last; acc -= (last < 0 ? 0 : s.all_mass[chosen]); }
                 s.acc = acc;
-                s.n_eq = s.cnt[chosen];
-                s.mass_eq = s.mass[chosen];
+                s.n_eq = s.all_cnt[chosen];
+                s.mass_eq = s.all_mass[chosen];
                 s.prefix = prefix | ((unsigned)chosen << shift);
                 s.mask = mask | (0xffu << shift);
             }
@@ -274,15 +428,16 @@ sample_kernel(const float* __restrict__ logits, int V, long long row_stride, flo
         if (phase == 0) {
             C = acc + n * w;
             Kp = K;
-            Ip = (n < n_eq) ? nth_index_with_key(x, V, K, (K == Kk) ? Ik : V, (unsigned)n, s) : ((K == Kk) ? Ik : V);
+            Ip = (n < n_eq) ? nth_index_with_key(x, lo, hi, K, (K == Kk) ? Ik : V, (unsigned)n, s, e) : ((K == Kk) ? Ik : V);
             // the nucleus narrows the set for the draw
             Kk = Kp;
             Ik = Ip;
         } else {
-            const int idx = nth_index_with_key(x, V, K, (K == Kk) ? Ik : V, (unsigned)n, s);
-            if (tid == 0) out[blockIdx.x] = idx < 0 ? 0 : idx;
+            const int idx = nth_index_with_key(x, lo, hi, K, (K == Kk) ? Ik : V, (unsigned)n, s, e);
+            if (tid == 0 && rank == 0) out[row] = idx < 0 ? 0 : idx;
         }
     }
+    smp_cluster_sync();                              // no CTA leaves while a peer may still read its shared memory
 #undef IN_SET
 #undef WEIGHT
 }
@@ -292,8 +447,23 @@ extern "C" int rf_sample(const float* logits, int rows, int V, long long row_str
                          int* out, cudaStream_t st) {
     if (rows <= 0) return 0;
     if (V <= 0 || !seeds) return RF_ERR_BAD_ARG;
-    rf_launch(sample_kernel, dim3(rows), dim3(SMP_THREADS), 0, st, logits, V, row_stride, temperature, top_p, top_k, seeds,
-              draw_counter, out);
+    // CTAs per row: as many as keep the whole batch resident at once (two CTAs of 1,024 threads fit an SM)
+    int cl = 8;
+    while (cl > 1 && (long long)rows * cl > 160) cl >>= 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(rows * cl);
+    cfg.blockDim = dim3(SMP_THREADS);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cl; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_rf_pdl ? 2 : 1;
+    cudaError_t err = cudaLaunchKernelEx(&cfg, sample_kernel, logits, V, row_stride, temperature, top_p, top_k, seeds,
+                                         draw_counter, out);
+    if (err != cudaSuccess) return (int)err;
     RF_LAUNCH_CHECK();
     return 0;
 }

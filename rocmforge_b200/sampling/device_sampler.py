@@ -16,12 +16,35 @@ class DeviceSampler:
 
     def __init__(self, device):
         self.device = torch.device(device)
+        self._pinned = None            # seeds on their way to the device: one pinned buffer, one copy a step
+        self._pinned_np = None
+        self._dev = None
+        self._copied = None
+
+    def _seeds(self, values) -> torch.Tensor:
+        n = len(values)
+        if self._pinned is None or self._pinned.numel() < n:
+            cap = max(64, 2 * n)
+            self._pinned = torch.zeros((cap,), dtype=torch.int64)
+            if self.device.type == "cuda":
+                self._pinned = self._pinned.pin_memory()
+                self._copied = torch.cuda.Event()
+            self._pinned_np = self._pinned.numpy()
+            self._dev = torch.zeros((cap,), dtype=torch.int64, device=self.device)
+            self._busy = False
+        if self._copied is not None and self._busy:
+            self._copied.synchronize()                     # the last copy may still read the pinned buffer
+        self._pinned_np[:n] = values
+        self._dev[:n].copy_(self._pinned[:n], non_blocking=True)
+        if self._copied is not None:
+            self._copied.record()
+            self._busy = True
+        return self._dev[:n]
 
     def sample(self, logits: torch.Tensor, params: SamplingParams, requests: Sequence[int],
                draws: Sequence[int], out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``requests[i]`` / ``draws[i]``: index of row i's request and of its draw, for the seed."""
         if params.greedy:
             return kernels.argmax(logits, out=out)
-        seeds = torch.tensor([as_int64(draw_seed(params.seed, r, d)) for r, d in zip(requests, draws)],
-                             dtype=torch.int64).to(self.device, non_blocking=True)
+        seeds = self._seeds([as_int64(draw_seed(params.seed, r, d)) for r, d in zip(requests, draws)])
         return kernels.sample(logits, params.temperature, params.top_p, params.top_k, seeds, out=out)
