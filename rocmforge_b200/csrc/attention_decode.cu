@@ -651,11 +651,15 @@ static int launch_warps(const void* q, int q_stride, void* out, int out_stride, 
                         int window, int B, int splits, int* status, cudaStream_t st) {
     constexpr int HD = EPL * 32;
     const size_t smem = (size_t)WARPS * 2 * ROWS * HD * 2 +
-                        (size_t)(WARPS * DEC_GP + 2 * DEC_GP + 8 * 2 * DEC_GP + DEC_GP * HD) * sizeof(float) + WARPS * 2 * 8 + 16 + 1024;
+                        (size_t)(WARPS * DEC_GP + 2 * DEC_GP + 16 * 2 * DEC_GP + DEC_GP * HD) * sizeof(float) + WARPS * 2 * 8 + 16 + 1024;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_decode_warps_kernel<EPL, ROWS, WARPS>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        // clusters of 16 (one sequence with a long context: 4 kv heads x 16 CTAs) are beyond the portable size
+        e = cudaFuncSetAttribute(attention_decode_warps_kernel<EPL, ROWS, WARPS>,
+                                 cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
@@ -741,7 +745,7 @@ int rf_attention_decode_warps(const void* q, int q_stride, void* out, int out_st
     if (B <= 0) return 0;
     if (!rf_attention_decode_supported(nh, nkv, hd)) return RF_ERR_UNSUPPORTED;
     if (nkv > 65535 || B > 65535) return RF_ERR_UNSUPPORTED;
-    if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return RF_ERR_BAD_ARG;
+    if (splits != 1 && splits != 2 && splits != 4 && splits != 8 && splits != 16) return RF_ERR_BAD_ARG;
     if (warps != 4 && warps != 8) return RF_ERR_BAD_ARG;
     if ((reinterpret_cast<uintptr_t>(q) & 15) || (q_stride * 2) % 16) return RF_ERR_BAD_ARG;
 #define GOW(EPL, ROWS, WARPS) return launch_warps<EPL, ROWS, WARPS>(q, q_stride, out, out_stride, k_pages, v_pages, n_pages, tok_seq, \

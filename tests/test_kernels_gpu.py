@@ -264,7 +264,7 @@ def test_attention_decode(nh, nkv, hd, window):
                                     scale, window)
     torch.testing.assert_close(out.float(), gen.float(), atol=2e-2, rtol=2e-2)
     # the clustered kernel: every cluster size and both CTA widths, the same answers
-    for splits, warps in ((1, 4), (1, 8), (2, 8), (4, 4), (8, 8)):
+    for splits, warps in ((1, 4), (1, 8), (2, 8), (4, 4), (8, 8), (16, 8)):
         out = kernels.attention_decode_warps(q.to(DEV), nh, nkv, hd, k_pages, v_pages, tok_seq, tok_pos, seq_slot,
                                              table, scale, window, splits=splits, warps=warps)
         assert torch.isfinite(out.float()).all()
@@ -272,6 +272,7 @@ def test_attention_decode(nh, nkv, hd, window):
             torch.testing.assert_close(out[b].cpu().double().view(nh, hd), refs[b], atol=2e-2, rtol=2e-2)
     assert kernels.decode_splits(1, 4) == 8 and kernels.decode_splits(8, 4) == 4 and kernels.decode_splits(64, 4) == 1
     assert kernels.decode_splits(1, 4, longest=100) == 2 and kernels.decode_splits(1, 4, 4096, window=128) == 2
+    assert kernels.decode_splits(1, 4, longest=4096) == 16 and kernels.decode_splits(2, 4, longest=4096) == 8
     assert kernels.decode_pages(1 << 20, 1024) == 17            # a window bounds the pages whatever the length
 
 
