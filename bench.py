@@ -152,6 +152,85 @@ def decode_rate(model, batch, steps, warmup, seed):
             "mean_ctx": mean_ctx, "t0": t0, "t1": t1}
 
 
+def ablation(model, batch, steps=32):
+    """Where a replayed decode step's time goes: every kind of kernel in turn is replaced by a stand-in that launches
+    nothing and returns a buffer of the right shape, the step's graph is captured anew and timed.  The difference to
+    the whole step is what that kernel costs inside the chain (with its overlaps), which a profiler's serialised,
+    cold-cache replay does not show.  Results are garbage while a stand-in is in place; only the time is read."""
+    import torch
+    from rocmforge_b200 import kernels
+    from rocmforge_b200.kernels import tensor_core as tc
+    from rocmforge_b200.engine.graph import DecodeRunner
+    cfg = model.config
+    L = cfg.num_hidden_layers
+    buffers = {}
+
+    def buffer(key, shape, dtype):
+        if key not in buffers:
+            buffers[key] = torch.zeros(shape, dtype=dtype, device=model.device)
+        return buffers[key]
+
+    def run():
+        cache = model.new_cache(max_tokens=batch * (PROMPT_LEN + 256), max_slots=batch)
+        runner = DecodeRunner(model, cache)
+        slots = [cache.alloc_slot() for _ in range(batch)]
+        for s in slots:                                  # PROMPT_LEN cached positions (their content does not matter)
+            cache.prepare([s], [PROMPT_LEN])
+            cache.commit([s], [PROMPT_LEN])
+        runner.greedy_loop(slots, [1] * batch, 4)
+        torch.cuda.synchronize()
+        _, start, end, _ = runner.greedy_loop(slots, [1] * batch, steps)
+        torch.cuda.synchronize()
+        return start.elapsed_time(end) / steps * 1e3     # us a step
+
+    def no_norm(h, weight, eps, dt, pending=None, rows=None, out=None):
+        return buffer(("norm", rows is None), (h.shape[0] if rows is None else rows.shape[0], h.shape[1]), dt)
+
+    def no_rope(qkv, nh, nkv, hd, inv, *a, **kw):
+        return buffer("q", (qkv.shape[1] if qkv.dim() == 3 else qkv.shape[0], nh * hd), torch.bfloat16)
+
+    def no_attention(q, nh, nkv, hd, *a, **kw):
+        return buffer("o", (q.shape[0], nh * hd), torch.bfloat16)
+
+    real_skinny = tc.gemm_tc_skinny
+
+    def without(pred):
+        def f(x, w, bias=None, *, mode=tc.STORE, splits=1, out=None):
+            if not pred(w, mode):
+                return real_skinny(x, w, bias, mode=mode, splits=splits, out=out)
+            if out is not None:
+                return out
+            M, N = x.shape[0], w.shape[0]
+            shape = (splits, M, N) if mode == tc.PARTIAL else (M, N // 2 if mode == tc.SWIGLU else N)
+            return buffer(("gemm", shape, mode), shape, torch.bfloat16 if mode in (tc.STORE, tc.SWIGLU) else torch.float32)
+        return f
+
+    H, I, V = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
+    QKV = (cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * cfg.head_dim
+    cases = [("the two norms of a layer", kernels, "add_rmsnorm", no_norm),
+             ("rotation + cache write", kernels, "rope_kv_write", no_rope),
+             ("attention", kernels, "attention_decode_warps", no_attention),
+             ("q|k|v product", tc, "gemm_tc_skinny", without(lambda w, m: w.shape[0] == QKV and m == tc.PARTIAL)),
+             ("o product", tc, "gemm_tc_skinny", without(lambda w, m: tuple(w.shape) == (H, cfg.num_attention_heads * cfg.head_dim))),
+             ("gate/up product", tc, "gemm_tc_skinny", without(lambda w, m: m == tc.SWIGLU)),
+             ("down product", tc, "gemm_tc_skinny", without(lambda w, m: tuple(w.shape) == (H, I))),
+             ("output matrix (per step)", tc, "gemm_tc_skinny", without(lambda w, m: w.shape[0] == V)),
+             ("all products", tc, "gemm_tc_skinny", without(lambda w, m: True))]
+    whole = run()
+    rows = [{"kernel": "whole step", "us_per_step": round(whole, 1)}]
+    for name, module, attr, stand_in in cases:
+        real = getattr(module, attr)
+        setattr(module, attr, stand_in)
+        try:
+            t = run()
+        finally:
+            setattr(module, attr, real)
+        per_step = "per step" in name or name == "all products"
+        rows.append({"kernel": name, "us_per_step": round(whole - t, 1),
+                     "us_per_layer": None if per_step else round((whole - t) / L, 2)})
+    return rows
+
+
 def e2e_rate(llm, batch, steps, seed, temperature=0.0, top_p=1.0):
     """The same through LLM.generate: token ids from the host in, sampled ids back to the host, every step."""
     import torch
@@ -212,7 +291,7 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (quick check)")
-    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
+    ap.add_argument("--only", choices=["decode", "prefill", "ablate"], default=None,
                     help="run one phase only and print a short line (small cases for profilers)")
     ap.add_argument("--seed", type=int, default=0)
     args = ap.parse_args()
@@ -239,6 +318,10 @@ def main():
         r = decode_rate(model, args.batch, args.steps, warmup, args.seed)
         print(json.dumps({"only": "decode", "layers": cfg.num_hidden_layers, "batch": args.batch,
                           "ms_per_step": round(r["ms_per_step"], 4), "tok_s": round(r["tok_s"], 1)}))
+        return 0
+    if args.only == "ablate":
+        for row in ablation(model, args.batch):
+            print(json.dumps(row))
         return 0
     if args.only == "prefill":
         ms = prefill_rate(model, PREFILL_TOKENS, 2, args.seed + 2)
