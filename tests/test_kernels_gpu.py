@@ -444,6 +444,22 @@ def test_sample_kernel_follows_the_plain_sampler(V):
     assert got == [S.sample(cpu[r], 0.9, 0.9, 0, draw_seed(99, r, 5)) for r in range(R)]
 
 
+@pytest.mark.parametrize("R", [1, 3, 8, 24, 60, 100])
+def test_sample_kernel_with_every_cluster_size(R):
+    """The CTAs per row go with the number of rows (16, 8, 4, 2, 1); small vocabularies leave some CTAs without an element."""
+    from rocmforge_b200 import kernels
+    from rocmforge_b200.sampling import as_int64, draw_seed
+    for V in (5, 97, 3001):
+        logits = rnd(R, V, seed=R + V, scale=2.0)
+        logits[:, V // 2] = logits[:, 0]
+        cpu = logits.cpu()
+        for temperature, top_p, top_k in ((0.8, 0.9, 0), (1.0, 1.0, 3), (1.3, 0.6, 0)):
+            seeds = [draw_seed(77, r, 1) for r in range(R)]
+            got = kernels.sample(logits, temperature, top_p, top_k,
+                                 torch.tensor([as_int64(s) for s in seeds], dtype=torch.int64, device=DEV)).cpu().tolist()
+            assert got == [S.sample(cpu[r], temperature, top_p, top_k, seeds[r]) for r in range(R)], (R, V, temperature, top_p, top_k)
+
+
 def test_kernels_refuse_what_they_cannot_do():
     from rocmforge_b200 import kernels
     from rocmforge_b200.kernels import KernelError
