@@ -33,7 +33,7 @@ MODULES: Dict[str, List[str]] = {
     "attention_generic": ["attention_generic.cu", "common.cuh"],
     "sampling": ["sampling.cu", "common.cuh"],
     "gemm_tcgen05": ["gemm_tcgen05.cu", "tcgen05_common.cuh", "common.cuh"],
-    # uses TMA multicast inside a cluster (this GPU's memory only): a file of its own, left out of
+    # has one CTA load a tile for its whole cluster (this GPU's memory only): a file of its own, left out of
     # multi-GPU runs; the package works without it
     "gemm_tcgen05_cluster": ["gemm_tcgen05_cluster.cu", "tcgen05_common.cuh", "common.cuh"],
     "attention_decode": ["attention_decode.cu", "common.cuh"],

@@ -59,7 +59,7 @@ _cluster_ok = None
 
 
 def cluster_available() -> bool:
-    """The clustered kernel lives in an optional module (it uses TMA multicast, which multi-GPU runs exclude)."""
+    """The clustered kernel lives in an optional module (its cluster-wide tile loads are kept out of runs on several GPUs)."""
     global _cluster_ok
     if _cluster_ok is None:
         from ..csrc import build
