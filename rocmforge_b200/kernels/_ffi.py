@@ -48,7 +48,15 @@ def ptr(t) -> c_void_p:
     return c_void_p(0) if t is None else c_void_p(t.data_ptr())
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def stream() -> c_void_p:
+    """torch's current stream of the current device as a raw handle.  Asked at every launch (the current
+    stream changes under ``torch.cuda.stream`` and during graph capture), so through the cheapest call there is:
+    ``torch.cuda.current_stream()`` builds a Stream object and costs about 15 us, a third of a launch's host time."""
+    if _raw_stream is not None:
+        return c_void_p(_raw_stream(torch.cuda.current_device()))
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 

@@ -17,15 +17,19 @@ _status = {}
 
 def status_word(device) -> torch.Tensor:
     """Device word that a kernel sets when one of its bounded waits runs out."""
-    key = str(device)
-    if key not in _status:
-        _status[key] = torch.zeros((1,), dtype=torch.int32, device=device)
-    return _status[key]
+    word = _status.get(device)                       # asked at every launch: no string is built on this path
+    if word is None:
+        key = str(torch.device(device))
+        word = _status.get(key)
+        if word is None:
+            word = _status[key] = torch.zeros((1,), dtype=torch.int32, device=device)
+        _status[device] = word
+    return word
 
 
 def check_status(device) -> None:
     """Raise if a tensor-core kernel gave up waiting since the last check (synchronises)."""
-    key = str(device)
+    key = str(torch.device(device))
     if key in _status and int(_status[key].item()) != 0:
         _status[key].zero_()
         for flags in _part_flags.values():         # a kernel that gave up may have left its K-part counters behind
@@ -39,6 +43,7 @@ def _f(name, *argtypes):
     return fn("gemm_tcgen05", name, list(argtypes))
 
 
+@functools.lru_cache(None)
 def supported(M: int, N: int, K: int, mode: int = STORE) -> bool:
     f = _f("rf_gemm_tc_supported", c_int, c_int, c_int, c_int)
     return bool(f(M, N, K, mode))
@@ -67,6 +72,7 @@ def cluster_available() -> bool:
     return _cluster_ok
 
 
+@functools.lru_cache(None)
 def cluster_supported(M: int, N: int, K: int, mode: int = STORE) -> bool:
     if not cluster_available():
         return False
