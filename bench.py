@@ -26,14 +26,23 @@ sys.path.insert(0, ROOT)
 
 METRIC = "Qwen2.5-7B bf16 decode tok/s at batch 1/8/64; prefill tok/s at 2,048 tokens"
 
-# BASELINE.json configs[2]
+# BASELINE.json configs[2] (the headline), configs[3] and configs[4]
 SHAPE_7B = dict(architectures=["Qwen2ForCausalLM"], num_hidden_layers=28, hidden_size=3584,
                 num_attention_heads=28, num_key_value_heads=4, head_dim=128, intermediate_size=18944,
                 vocab_size=152064, rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=False,
                 use_sliding_window=False, max_position_embeddings=4096)
+SHAPE_05B = dict(architectures=["Qwen2ForCausalLM"], num_hidden_layers=24, hidden_size=896,
+                 num_attention_heads=14, num_key_value_heads=2, head_dim=64, intermediate_size=4864,
+                 vocab_size=151936, rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=True,
+                 use_sliding_window=False, max_position_embeddings=32768)
+SHAPE_14B = dict(architectures=["Qwen2ForCausalLM"], num_hidden_layers=48, hidden_size=5120,
+                 num_attention_heads=40, num_key_value_heads=8, head_dim=128, intermediate_size=13824,
+                 vocab_size=152064, rope_theta=1e6, rms_norm_eps=1e-5, tie_word_embeddings=False,
+                 use_sliding_window=False, max_position_embeddings=32768)
 CONTEXT = 4096
 PROMPT_LEN = 512
 PREFILL_TOKENS = 2048
+PREFILL_CHUNK = 16384          # most prompt tokens run in one step when a batch of prompts is brought into the cache
 
 
 def peaks():
@@ -101,43 +110,101 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def step_bytes(cfg, model, batch, mean_ctx):
-    """Bytes a decode step has to read: every weight it uses once, and the cache of the live requests."""
+def step_bytes(cfg, batch, mean_ctx, elem=2):
+    """Bytes a decode step has to read: every weight it uses once, and the cache of the live requests
+    (``mean_ctx`` positions per request on average); ``elem`` bytes per weight and cache element."""
     L, H, V = cfg.num_hidden_layers, cfg.hidden_size, cfg.vocab_size
     Q, KV, I = cfg.num_attention_heads * cfg.head_dim, cfg.num_key_value_heads * cfg.head_dim, cfg.intermediate_size
-    per_layer = (H * (Q + 2 * KV) + Q * H + 3 * H * I) * 2 + (Q + 2 * KV + 2 * H) * 2
-    weights = L * per_layer + V * H * 2 + H * 2
-    kv = batch * mean_ctx * 2 * KV * 2 * L
+    per_layer = (H * (Q + 2 * KV) + Q * H + 3 * H * I) * elem + (Q + 2 * KV + 2 * H) * elem
+    weights = L * per_layer + V * H * elem + H * elem          # a tied output matrix is read once, as the head
+    kv = batch * mean_ctx * 2 * KV * elem * L
     return weights + kv
 
 
-def prefill_flops(cfg, T):
+def prefill_flops(cfg, lengths):
+    """Products and causal attention of whole prompts of the given lengths, logits for the last row of each."""
     L, H, V = cfg.num_hidden_layers, cfg.hidden_size, cfg.vocab_size
     Q, KV, I = cfg.num_attention_heads * cfg.head_dim, cfg.num_key_value_heads * cfg.head_dim, cfg.intermediate_size
+    if isinstance(lengths, int):
+        lengths = [lengths]
+    T = float(sum(lengths))
     linear = 2.0 * T * (H * (Q + 2 * KV) + Q * H + 3 * H * I)
-    attn = 2.0 * 2.0 * (T * (T + 1) / 2.0) * cfg.head_dim * cfg.num_attention_heads
-    return L * (linear + attn) + 2.0 * V * H
+    attn = sum(2.0 * 2.0 * (t * (t + 1) / 2.0) * cfg.head_dim * cfg.num_attention_heads for t in lengths)
+    return L * (linear + attn) + 2.0 * V * H * len(lengths)
 
 
 def random_prompts(n, length, vocab, seed):
+    """``length``: one length for all, or (low, high) for lengths drawn uniformly from that range (seeded)."""
     import torch
     g = torch.Generator().manual_seed(seed)
-    return [torch.randint(0, vocab, (length,), generator=g).tolist() for _ in range(n)]
+    if isinstance(length, tuple):
+        lens = torch.randint(length[0], length[1] + 1, (n,), generator=g).tolist()
+    else:
+        lens = [length] * n
+    return [torch.randint(0, vocab, (m,), generator=g).tolist() for m in lens]
 
 
-def decode_rate(model, batch, steps, warmup, seed):
-    """Device-timed decode: prefill `batch` prompts of PROMPT_LEN tokens, then `steps` replayed steps."""
-    import torch
+def prefill_prompts(model, cache, slots, prompts):
+    """Bring the prompts into the cache, at most PREFILL_CHUNK tokens a step; the argmax of each last row."""
     from rocmforge_b200 import StepRequest, kernels
-    from rocmforge_b200.engine.graph import DecodeRunner
-    cache = model.new_cache(max_tokens=batch * (PROMPT_LEN + warmup + steps + 64), max_slots=batch)
-    runner = DecodeRunner(model, cache)
-    prompts = random_prompts(batch, PROMPT_LEN, model.spec.vocab_size, seed)
-    slots = [cache.alloc_slot() for _ in range(batch)]
-    first = []
-    for i in range(0, batch, 8):                       # prompts in steps of 8 sequences
-        logits = model.step(cache, [StepRequest(s, p, [len(p) - 1]) for s, p in zip(slots[i:i + 8], prompts[i:i + 8])])
+    first, i = [], 0
+    while i < len(prompts):
+        j, t = i, 0
+        while j < len(prompts) and (j == i or t + len(prompts[j]) <= PREFILL_CHUNK):
+            t += len(prompts[j])
+            j += 1
+        logits = model.step(cache, [StepRequest(s, p, [len(p) - 1]) for s, p in zip(slots[i:j], prompts[i:j])])
         first += kernels.argmax(logits).cpu().tolist()
+        i = j
+    return first
+
+
+class LoopMismatch(RuntimeError):
+    pass
+
+
+def check_loop(model, prompts, first, ids, n_check):
+    """The ids that the device loop produced, compared with a second, untimed run of the same requests in which
+    the host feeds every step (``DecodeRunner.logits`` + argmax): each of the first ``n_check`` steps gets the loop's
+    own ids as input and must pick the loop's next ids, or differ only where the two best logits are a rounding
+    error apart.  A position that did not advance or a page that was not reserved shows here."""
+    import torch
+    from rocmforge_b200 import kernels
+    from rocmforge_b200.engine.graph import DecodeRunner
+    B = len(prompts)
+    n_check = min(n_check, ids.shape[0])
+    cache = model.new_cache(max_tokens=sum((len(p) + n_check + 64) // 64 * 64 for p in prompts), max_slots=B)
+    runner = DecodeRunner(model, cache)
+    slots = [cache.alloc_slot() for _ in range(B)]
+    again = prefill_prompts(model, cache, slots, prompts)
+    if again != first:
+        raise LoopMismatch("the prompts gave other first tokens on a second run")
+    host_ids = ids[:n_check].cpu()
+    feed = first
+    for k in range(n_check):
+        logits = runner.logits(slots, feed)
+        got = kernels.argmax(logits).cpu()
+        bad = torch.nonzero(got != host_ids[k]).flatten().tolist()
+        for b in bad:
+            row = logits[b]
+            margin = abs(float(row[int(got[b])]) - float(row[int(host_ids[k][b])]))
+            if margin > 2e-2 * float(row.abs().max()):
+                raise LoopMismatch(f"step {k}, sequence {b}: the device loop picked {int(host_ids[k][b])}, "
+                                   f"the checked step {int(got[b])} (logits {margin:.4g} apart)")
+        feed = host_ids[k].tolist()
+    return n_check
+
+
+def decode_rate(model, prompts, steps, warmup, check=16):
+    """Device-timed decode: the prompts in steps of at most PREFILL_CHUNK tokens, then ``steps`` replayed steps
+    whose sampled ids feed the next step on the device.  The loop's ids are checked afterwards (``check`` steps)."""
+    import torch
+    from rocmforge_b200.engine.graph import DecodeRunner
+    batch = len(prompts)
+    cache = model.new_cache(max_tokens=sum((len(p) + warmup + steps + 64) // 64 * 64 for p in prompts), max_slots=batch)
+    runner = DecodeRunner(model, cache)
+    slots = [cache.alloc_slot() for _ in range(batch)]
+    first = prefill_prompts(model, cache, slots, prompts)
     ids, _, _, _ = runner.greedy_loop(slots, first, warmup)
     torch.cuda.synchronize()
     t0 = time.time()
@@ -145,11 +212,14 @@ def decode_rate(model, batch, steps, warmup, seed):
     torch.cuda.synchronize()
     t1 = time.time()
     ms = start.elapsed_time(end)
-    mean_ctx = PROMPT_LEN + warmup + steps / 2.0
+    mean_ctx = sum(len(p) for p in prompts) / batch + warmup + steps / 2.0
+    all_ids = torch.cat([ids, ids2])
     del runner, cache
     torch.cuda.empty_cache()
+    checked = check_loop(model, prompts, first, all_ids, check) if check else 0
+    torch.cuda.empty_cache()
     return {"tok_s": batch * steps / (ms / 1e3), "ms_per_step": ms / steps, "launches": launches * steps,
-            "mean_ctx": mean_ctx, "t0": t0, "t1": t1}
+            "mean_ctx": mean_ctx, "t0": t0, "t1": t1, "checked_steps": checked}
 
 
 def ablation(model, batch, steps=32):
@@ -231,10 +301,10 @@ def ablation(model, batch, steps=32):
     return rows
 
 
-def e2e_rate(llm, batch, steps, seed, temperature=0.0, top_p=1.0):
+def e2e_rate(llm, prompts, steps, temperature=0.0, top_p=1.0):
     """The same through LLM.generate: token ids from the host in, sampled ids back to the host, every step."""
     import torch
-    prompts = random_prompts(batch, PROMPT_LEN, llm.model.spec.vocab_size, seed)
+    batch = len(prompts)
     stamps = []
 
     def on_token(i, tok):
@@ -253,6 +323,7 @@ def e2e_rate(llm, batch, steps, seed, temperature=0.0, top_p=1.0):
 
 
 def prefill_rate(model, tokens, repeats, seed):
+    """Median time in ms of one step that runs a prompt of ``tokens`` tokens and gives the last row's logits."""
     import torch
     from rocmforge_b200 import StepRequest
     cache = model.new_cache(max_tokens=tokens + 64, max_slots=2)
@@ -270,7 +341,51 @@ def prefill_rate(model, tokens, repeats, seed):
             times.append(start.elapsed_time(end))
         cache.free_slot(s)
     times.sort()
+    del cache
+    torch.cuda.empty_cache()
     return times[len(times) // 2]
+
+
+def other_shapes(pk, seed, only=None):
+    """BASELINE.json's two further configurations, as flat numbers for ``points``: the 0.5B shape in bfloat16 and in
+    true 32-bit (a batch of 64 with prompt lengths uniform in 16..1,024, 256 decode steps; device-timed, its share of
+    the HBM bandwidth, and end to end), and the 14B shape (a prompt of 8,192 tokens; decoding at batch 1 and 16 at
+    that context)."""
+    import torch
+    import rocmforge_b200 as rf
+    from rocmforge_b200.config import Qwen2Config
+    out = {}
+    hbm, tf = pk["hbm_gbs"], pk["bf16_tflops"]
+    if only in (None, "0.5b"):
+        cfg = Qwen2Config.from_dict(SHAPE_05B)
+        prompts = random_prompts(64, (16, 1024), cfg.vocab_size, seed + 10)
+        for dtype, tag, elem in ((torch.bfloat16, "bf16", 2), (torch.float32, "fp32", 4)):
+            model = rf.Model.random(cfg, seed=seed, dtype=dtype)
+            r = decode_rate(model, prompts, 256, 8)
+            key = f"qwen0.5b_{tag}_b64_ragged"
+            out[key + "_tok_s"] = round(r["tok_s"], 1)
+            out[key + "_ms_per_step"] = round(r["ms_per_step"], 4)
+            out[key + "_hbm_frac"] = round(step_bytes(cfg, 64, r["mean_ctx"], elem) / (r["ms_per_step"] / 1e3) / 1e9 / hbm, 4)
+            llm = rf.LLM(model, cache_tokens=sum((len(p) + 256 + 80) // 64 * 64 for p in prompts), max_batch=64)
+            out[key + "_e2e_tok_s"] = round(e2e_rate(llm, prompts, 128 if elem == 2 else 32)["value"], 1)
+            del llm, model
+            torch.cuda.empty_cache()
+    if only in (None, "14b"):
+        cfg = Qwen2Config.from_dict(SHAPE_14B)
+        model = rf.Model.random(cfg, seed=seed, dtype=torch.bfloat16)
+        ms = prefill_rate(model, 8192, 2, seed + 11)
+        out["qwen14b_prefill8192_tok_s"] = round(8192 / (ms / 1e3), 1)
+        out["qwen14b_prefill8192_ms"] = round(ms, 2)
+        out["qwen14b_prefill8192_frac"] = round(prefill_flops(cfg, 8192) / (ms / 1e3) / (tf * 1e12), 4)
+        for batch in (1, 16):
+            prompts = random_prompts(batch, 8192 - 48, cfg.vocab_size, seed + 12 + batch)
+            r = decode_rate(model, prompts, 32, 8, check=4)
+            key = f"qwen14b_decode_b{batch}_ctx8192"
+            out[key + "_tok_s"] = round(r["tok_s"], 1)
+            out[key + "_hbm_frac"] = round(step_bytes(cfg, batch, r["mean_ctx"]) / (r["ms_per_step"] / 1e3) / 1e9 / hbm, 4)
+        del model
+        torch.cuda.empty_cache()
+    return out
 
 
 def reference_arm():
@@ -291,7 +406,7 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (quick check)")
-    ap.add_argument("--only", choices=["decode", "prefill", "ablate"], default=None,
+    ap.add_argument("--only", choices=["decode", "prefill", "ablate", "0.5b", "14b"], default=None,
                     help="run one phase only and print a short line (small cases for profilers)")
     ap.add_argument("--seed", type=int, default=0)
     args = ap.parse_args()
@@ -306,18 +421,22 @@ def main():
     import rocmforge_b200 as rf
     from rocmforge_b200.config import Qwen2Config
 
+    pk = peaks()
+    if args.only in ("0.5b", "14b"):
+        print(json.dumps({"only": args.only, **other_shapes(pk, args.seed, args.only)}))
+        return 0
     raw = dict(SHAPE_7B)
     if args.layers:
         raw["num_hidden_layers"] = args.layers
     cfg = Qwen2Config.from_dict(raw)
-    pk = peaks()
+    V = cfg.vocab_size
     model = rf.Model.random(cfg, seed=args.seed, dtype=torch.bfloat16)
-    llm = rf.LLM(model, cache_tokens=args.batch * (PROMPT_LEN + args.steps + 80), max_batch=args.batch)
 
     if args.only == "decode":
-        r = decode_rate(model, args.batch, args.steps, warmup, args.seed)
+        r = decode_rate(model, random_prompts(args.batch, PROMPT_LEN, V, args.seed), args.steps, warmup)
         print(json.dumps({"only": "decode", "layers": cfg.num_hidden_layers, "batch": args.batch,
-                          "ms_per_step": round(r["ms_per_step"], 4), "tok_s": round(r["tok_s"], 1)}))
+                          "ms_per_step": round(r["ms_per_step"], 4), "tok_s": round(r["tok_s"], 1),
+                          "checked_steps": r["checked_steps"]}))
         return 0
     if args.only == "ablate":
         for row in ablation(model, args.batch):
@@ -332,22 +451,33 @@ def main():
     pre_ms = prefill_rate(model, PREFILL_TOKENS, 3, args.seed + 2)
     sampler = ClockSampler()
     sampler.start()
-    main_run = decode_rate(model, args.batch, args.steps, warmup, args.seed)
+    main_run = decode_rate(model, random_prompts(args.batch, PROMPT_LEN, V, args.seed), args.steps, warmup)
     clocks = sampler.summary(main_run["t0"], main_run["t1"])
-    e2e = e2e_rate(llm, args.batch, args.steps, args.seed + 1)
+    llm = rf.LLM(model, cache_tokens=args.batch * (PROMPT_LEN + args.steps + 80), max_batch=args.batch)
+    e2e = e2e_rate(llm, random_prompts(args.batch, PROMPT_LEN, V, args.seed + 1), args.steps)
     # the reference's own default is sampled decoding (temperature 1.0, top-p 0.9): the same loop with the device sampler
-    sampled = e2e_rate(llm, args.batch, max(args.steps // 2, 16), args.seed + 5, temperature=1.0, top_p=0.9)
+    sampled = e2e_rate(llm, random_prompts(args.batch, PROMPT_LEN, V, args.seed + 5), max(args.steps // 2, 16),
+                       temperature=1.0, top_p=0.9)
     llm.cache = llm.engine = None
+    del llm
     torch.cuda.empty_cache()
     points = {}
     if not args.skip_points:
-        points["decode_b1"] = round(decode_rate(model, 1, args.steps, warmup, args.seed + 3)["tok_s"], 1)
-        points["decode_b64"] = round(decode_rate(model, 64, max(args.steps // 2, 16), warmup, args.seed + 4)["tok_s"], 1)
-    sampler.stop()
-
-    nbytes = step_bytes(cfg, model, args.batch, main_run["mean_ctx"])
+        for b, st in ((1, args.steps), (64, max(args.steps // 2, 16))):
+            r = decode_rate(model, random_prompts(b, PROMPT_LEN, V, args.seed + 3 + b), st, warmup)
+            points[f"decode_b{b}"] = round(r["tok_s"], 1)
+            points[f"decode_b{b}_hbm_frac"] = round(step_bytes(cfg, b, r["mean_ctx"]) / (r["ms_per_step"] / 1e3) / 1e9
+                                                   / pk["hbm_gbs"], 4)
+    points["e2e_sampled_t1.0_p0.9"] = round(sampled["value"], 1)
+    nbytes = step_bytes(cfg, args.batch, main_run["mean_ctx"])
     achieved = nbytes / (main_run["ms_per_step"] / 1e3) / 1e9
     flops = prefill_flops(cfg, PREFILL_TOKENS)
+    del model
+    torch.cuda.empty_cache()
+    if not args.skip_points:
+        points.update(other_shapes(pk, args.seed))
+    sampler.stop()
+
     line = {
         "metric": METRIC, "value": round(main_run["tok_s"], 1), "unit": "tok/s", "n_gpus": 1,
         "steps": args.steps, "warmup": warmup, "ms_per_step": round(main_run["ms_per_step"], 4),
@@ -359,9 +489,14 @@ def main():
                    "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": PROMPT_LEN,
                    "context_at_timing": int(main_run["mean_ctx"]), "parallelism": "none (1 GPU)",
                    "cache_page": 64, "l2": "inputs larger than L2 (15 GB of weights per step)",
-                   "peaks": pk["source"]},
+                   "peaks": pk["source"],
+                   "points_qwen0.5b": "Qwen2.5-0.5B shape, 24 layers, hidden 896, 14/2 heads of 64, intermediate 4864, "
+                                      "vocab 151936 tied; batch 64, prompts uniform 16..1024 (seeded), 256 steps; bf16 and fp32",
+                   "points_qwen14b": "Qwen2.5-14B shape, 48 layers, hidden 5120, 40/8 heads of 128, intermediate 13824, "
+                                     "vocab 152064; prefill 8192 at batch 1, decode batch 1 and 16 at context 8192, 32 steps"},
         "e2e": e2e,
         "gpu_launches": main_run["launches"],
+        "loop_ids_checked_steps": main_run["checked_steps"],
         "clocks": clocks,
         "prefill": {"value": round(PREFILL_TOKENS / (pre_ms / 1e3), 1), "tokens": PREFILL_TOKENS,
                     "ms": round(pre_ms, 3), "frac": round(flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)},
@@ -369,7 +504,6 @@ def main():
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": points,
     }
-    line["points"]["e2e_sampled_t1.0_p0.9"] = round(sampled["value"], 1)
     print(json.dumps(line))
     return 0
 

@@ -87,12 +87,23 @@ class KVGroup:
                 break                                   # everything below was trimmed earlier
             self.pool.give_back(int(row[p]))
             row[p] = -1
+            self._mark(slot, p)                         # the device table must not name a free page either
 
     def release(self, slot: int) -> None:
         row = self.table[slot]
         for p in np.nonzero(row >= 0)[0]:
             self.pool.give_back(int(row[p]))
             row[p] = -1
+            self._mark(slot, int(p))                    # the next upload clears the device entry as well
+
+    def drop_beyond(self, slot: int, length: int) -> None:
+        """Give back the pages that lie wholly beyond ``length`` positions (taken for a step that did not happen)."""
+        row = self.table[slot]
+        for p in range(pages_for(length), self.max_pages_per_seq):
+            if row[p] >= 0:
+                self.pool.give_back(int(row[p]))
+                row[p] = -1
+                self._mark(slot, p)
 
     def held_pages(self, slot: int) -> List[int]:
         row = self.table[slot]
@@ -176,6 +187,9 @@ class SequenceCache:
         self.max_seq_len = self.max_pages_per_seq * PAGE if not max_seq_len else min(max_seq_len, self.max_pages_per_seq * PAGE)
         self.slots = FreeList(self.max_slots, "slot")
         self.lengths = np.zeros((self.max_slots,), dtype=np.int64)
+        # grows whenever a slot is handed out or given back: whoever prepared a step ahead of time (pages taken,
+        # descriptor built) compares it and drops what it prepared when the set of sequences has changed
+        self.epoch = 0
 
         by_key: Dict[tuple, List[int]] = {}
         self._kv_request: Dict[tuple, KVRequest] = {}
@@ -202,6 +216,7 @@ class SequenceCache:
     # ------------------------------------------------------------------ slots
     def alloc_slot(self) -> int:
         slot = self.slots.take()
+        self.epoch += 1
         self.lengths[slot] = 0
         for view in self.states.values():
             for t in view.tensors.values():
@@ -215,6 +230,7 @@ class SequenceCache:
             g.release(slot)
         self.lengths[slot] = 0
         self.slots.give_back(slot)
+        self.epoch += 1
 
     def length(self, slot: int) -> int:
         return int(self.lengths[slot])
@@ -255,11 +271,30 @@ class SequenceCache:
             g.upload()
         return starts
 
-    def reserve(self, slot: int, upto_len: int) -> None:
-        """Take the pages for positions < upto_len now (steps replayed without host work need them)."""
+    def reserve(self, slots: Sequence[int], upto_len: Sequence[int]) -> None:
+        """Take the pages for positions < upto_len[i] of slots[i] now (steps replayed without host work need
+        them).  Nothing is taken if not all of it fits."""
+        for s, n in zip(slots, upto_len):
+            if not self.slots.is_held(s):
+                raise CacheError(f"slot {s} is not held by any sequence")
+            if n > self.max_seq_len:
+                raise CacheError(f"slot {s}: {n} tokens exceed the longest sequence the cache holds "
+                                 f"({self.max_seq_len})")
         for g in self.groups:
-            g.ensure(slot, int(self.lengths[slot]), upto_len)
+            need = sum(g.pages_missing(s, int(self.lengths[s]), int(n)) for s, n in zip(slots, upto_len))
+            if need > g.pool.n_free:
+                raise CacheError(f"reserving needs {need} more cache pages, {g.pool.n_free} of {g.n_pages} are free")
+        for g in self.groups:
+            for s, n in zip(slots, upto_len):
+                g.ensure(s, int(self.lengths[s]), int(n))
             g.upload()
+
+    def rollback(self, slots: Sequence[int]) -> None:
+        """Undo ``prepare``/``reserve`` for a step that failed: every slot keeps the pages of its committed length only."""
+        for s in slots:
+            if self.slots.is_held(s):
+                for g in self.groups:
+                    g.drop_beyond(s, int(self.lengths[s]))
 
     def commit(self, slots: Sequence[int], n_new: Sequence[int]) -> None:
         for s, n in zip(slots, n_new):

@@ -53,6 +53,10 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_
     const int pos = tok_pos[b];
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     const int c_lo = lo / DEC_CHUNK, c_hi = pos / DEC_CHUNK;
+    if (c_hi >= max_chunks) {           // the launch has no CTA for the sequence's last chunk: say so, touch nothing
+        if (c == 0 && tid == 0 && status) atomicExch(status, 3);
+        return;
+    }
     if (c < c_lo || c > c_hi) return;
     const int n_act = c_hi - c_lo + 1;
     const int slot = seq_slot[tok_seq[b]];
@@ -372,6 +376,9 @@ attention_decode_warps_kernel(const __grid_constant__ CUtensorMap map_k, const _
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
     }
     __syncthreads();
+    // a store into a peer's shared memory needs that peer to have started: arrive here, wait just before the first
+    // push (every CTA has long arrived by then, so the wait costs nothing)
+    if (splits > 1) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
 
     // tile u of this CTA: page p_lo + rank + (u / UPP) * splits, rows (u % UPP) * ROWS ... of it
     auto first_key = [&](int u) { return (p_lo + rank + (u / UPP) * splits) * RF_PAGE + (u % UPP) * ROWS; };
@@ -574,6 +581,7 @@ attention_decode_warps_kernel(const __grid_constant__ CUtensorMap map_k, const _
     __syncthreads();
     const int DS = HD / splits;                          // output dimensions per CTA of the cluster
     const int slot_floats = 2 * DEC_GP + DEC_GP * DS;
+    if (splits > 1) asm volatile("barrier.cluster.wait.aligned;" ::: "memory");      // all peers run (see the arrive above)
     for (int i = tid; i < G * HD; i += NT) {
         const int g = i / HD, d = i - g * HD;
         float O = 0.f;

@@ -22,6 +22,10 @@
 //     counters are cleared at the start of every call (on the given stream); the rest is fully
 //     rewritten before it is read.  Two calls that overlap on the GPU (different streams without
 //     an ordering between them) race on the array: order them.
+//   * max_chunks must cover the longest sequence of the call: ceil(length / 128) chunks, counted from
+//     position 0 also for a layer with a window (partials are indexed by absolute chunk).  The lengths
+//     live on the device, so the host cannot check this; a sequence that needs more chunks is left
+//     alone by the kernel (its output rows stay as they were) and the status word is set to 3.
 //   * Same arguments and same result as rf_attention_decode, without its three scratch pointers.
 //     Returns 0, a cudaError_t (> 0), or RF_ERR_BAD_ARG (-1) / RF_ERR_UNSUPPORTED (-2).
 #pragma once

@@ -103,8 +103,11 @@ class StepBatch:
 class DeviceDescriptor:
     """The device copy of a step descriptor, with one pinned staging buffer for the upload."""
 
-    def __init__(self, device, capacity: int = 4096):
+    def __init__(self, device, capacity: int = 4096, fixed: bool = False):
+        """``fixed``: the device buffer is never replaced (captured graphs hold views of it); a descriptor
+        larger than ``capacity`` is then an error instead of a reason to grow."""
         self.device = torch.device(device)
+        self.fixed = fixed
         self.capacity = 0
         self.dev: Optional[torch.Tensor] = None
         self.pinned: Optional[torch.Tensor] = None
@@ -130,6 +133,9 @@ class DeviceDescriptor:
         result and the next step's launch, so it does as little on the host as it can."""
         n = packed.shape[0]
         if n > self.capacity:
+            if self.fixed:
+                raise BatchError(f"a step descriptor of {n} words does not fit the {self.capacity} this runner "
+                                 "was sized for")
             self._grow(max(n, 2 * self.capacity))
         if self._busy:
             self._done.synchronize()               # the previous copy may still read the staging buffer

@@ -148,7 +148,7 @@ class StepContext:
                     q, nh, nkv, hd, view.k_pages, view.v_pages, self.tok_seq, self.tok_pos, self.seq_slot,
                     view.block_table, mixer.scale, view.window, max_chunks,
                     scratch("attn_decode_o", n_o, torch.float32), scratch("attn_decode_ml", n_ml, torch.float32),
-                    scratch("attn_decode_counters", n_c, torch.int32))
+                    kernels.tensor_core.register_counters(scratch("attn_decode_counters", n_c, torch.int32)))
         if (not self.is_decode and self.compute_dtype == torch.bfloat16 and self.options.tuned_attention
                 and self.options.tcgen05_attention and self.q_tiles128.numel() > 0
                 and kernels.attention_prefill_tc_supported(nh, nkv, hd)

@@ -33,13 +33,20 @@ class DecodeRunner:
     def __init__(self, model, cache, max_batch: int = 1024):
         self.model = model
         self.cache = cache
-        self.desc = DeviceDescriptor(model.device, capacity=StepBatch.layout(max_batch, max_batch, max_batch)[1])
+        # sized for the largest packed decode batch (tile tables included) and never moved: graphs keep its address
+        self.desc = DeviceDescriptor(model.device, fixed=True, capacity=self.descriptor_words(max_batch))
         self.max_batch = max_batch
         self.graphs: Dict[tuple, _Captured] = {}
         from ..sampling import DeviceSampler
         self.sampler = DeviceSampler(model.device)
         self.replays = 0
-        self._ready = None             # (slots, starts, packed descriptor without token ids, longest) of the next step
+        self._ready = None             # (slots, starts, packed descriptor without token ids, longest, cache epoch) of the next step
+
+    @staticmethod
+    def descriptor_words(max_batch: int) -> int:
+        """int32 words of the largest packed decode descriptor (one token, one wanted row and one tile of each
+        kind per sequence)."""
+        return StepBatch.layout(max_batch, max_batch, max_batch, max_batch, max_batch)[1]
 
     @staticmethod
     def length_bucket(longest: int) -> int:
@@ -94,7 +101,9 @@ class DecodeRunner:
         starts = [self.cache.length(s) for s in slots]
         ready = self._ready
         self._ready = None
-        if ready is not None and ready[0] == slots and ready[1] == starts:
+        # what was prepared ahead holds only while no slot was handed out or given back since: a slot that was
+        # freed and filled again has the same number and may have the same length, but other pages
+        if ready is not None and ready[4] == self.cache.epoch and ready[0] == slots and ready[1] == starts:
             packed, longest = ready[2], ready[3]
             toks = np.asarray(tokens, dtype=np.int64)
             if ((toks < 0) | (toks >= self.model.spec.vocab_size)).any():
@@ -121,7 +130,7 @@ class DecodeRunner:
             for name in ("tok_pos", "seq_start"):
                 o, n = lay[name]
                 nxt[o:o + n] += 1
-            self._ready = (slots, [x + 1 for x in starts], nxt, longest + 1)
+            self._ready = (slots, [x + 1 for x in starts], nxt, longest + 1, self.cache.epoch)
         except CacheError:
             self._ready = None                     # no room for a further token: the next call will say so if it comes
         return cap.ids if greedy else cap.logits
@@ -135,8 +144,8 @@ class DecodeRunner:
         """
         from .. import kernels
         B = len(slots)
-        for s in slots:
-            self.cache.reserve(s, self.cache.length(s) + steps)
+        self._ready = None
+        self.cache.reserve(slots, [self.cache.length(s) + steps for s in slots])
         requests = [StepRequest(s, [int(t)], [0]) for s, t in zip(slots, tokens)]
         batch = StepBatch(requests, [self.cache.length(s) for s in slots], self.model.spec.vocab_size)
         self.desc.upload(batch.pack())

@@ -165,11 +165,15 @@ class Model:
         starts_now = [cache.length(s) if cache.slots.is_held(s) else 0 for s in slots]
         batch = StepBatch(requests, starts_now, self.spec.vocab_size)
         cache.prepare(slots, n_new)
-        self._desc.upload(batch.pack())
-        views = self._desc.views(batch.T, batch.B, batch.R, batch.n_tiles, batch.n_tiles128)
-        ctx = StepContext(self, views, T=batch.T, B=batch.B, R=batch.R, is_decode=batch.is_decode,
-                          max_new=batch.max_new, max_end=batch.max_end, host=batch)
-        logits = self.forward(ctx, cache)
+        try:
+            self._desc.upload(batch.pack())
+            views = self._desc.views(batch.T, batch.B, batch.R, batch.n_tiles, batch.n_tiles128)
+            ctx = StepContext(self, views, T=batch.T, B=batch.B, R=batch.R, is_decode=batch.is_decode,
+                              max_new=batch.max_new, max_end=batch.max_end, host=batch)
+            logits = self.forward(ctx, cache)
+        except BaseException:
+            cache.rollback(slots)          # a step that did not happen keeps no pages
+            raise
         cache.commit(slots, n_new)
         return logits
 

@@ -27,15 +27,27 @@ def status_word(device) -> torch.Tensor:
     return word
 
 
+_counters = {}
+
+
+def register_counters(t: torch.Tensor) -> torch.Tensor:
+    """Arrival counters that kernels leave at zero when they finish; a kernel that gave up may not have, so
+    ``check_status`` clears every registered buffer when it finds the status word set."""
+    _counters[t.data_ptr()] = t
+    return t
+
+
 def check_status(device) -> None:
-    """Raise if a tensor-core kernel gave up waiting since the last check (synchronises)."""
+    """Raise if a kernel gave up since the last check (synchronises): a bounded wait ran out (a copy or an MMA
+    never completed), or a launch did not cover a sequence's length."""
     key = str(torch.device(device))
     if key in _status and int(_status[key].item()) != 0:
+        code = int(_status[key].item())
         _status[key].zero_()
-        for flags in _part_flags.values():         # a kernel that gave up may have left its K-part counters behind
-            flags.zero_()
-        raise KernelError("a tensor-core kernel ran out of its wait limit (a copy or an MMA never completed); "
-                          "its results are invalid")
+        for flags in list(_part_flags.values()) + list(_counters.values()):
+            flags.zero_()                          # what the kernel that gave up may have left behind
+        raise KernelError(f"a kernel gave up (status {code}: a wait ran out of its limit, or a launch did not cover "
+                          "a sequence's length); its results are invalid")
 
 
 @functools.lru_cache(None)

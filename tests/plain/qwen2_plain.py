@@ -91,7 +91,7 @@ def rope_neox(x: torch.Tensor, positions: torch.Tensor, theta: float) -> torch.T
     half = hd // 2
     i = torch.arange(half, dtype=torch.float64)
     freq = (1.0 / torch.pow(torch.tensor(float(theta), dtype=torch.float64), 2.0 * i / hd)).to(torch.float32)
-    angle32 = positions.to(torch.float32)[:, None] * freq[None, :]           # 32-bit product
+    angle32 = positions.to(torch.float32)[:, None] * freq.to(positions.device)[None, :]      # 32-bit product
     angle = angle32.to(torch.float64)
     cos = torch.cos(angle).to(x.dtype)[:, None, :]
     sin = torch.sin(angle).to(x.dtype)[:, None, :]
@@ -113,7 +113,7 @@ def causal_attention(q, k, v, window=None):
     group = nh // nkv
     scale = 1.0 / math.sqrt(hd)
     out = torch.zeros_like(q)
-    pos = torch.arange(T)
+    pos = torch.arange(T, device=q.device)
     allowed = pos[None, :] <= pos[:, None]
     if window is not None:
         allowed = allowed & (pos[None, :] > pos[:, None] - window)
@@ -167,15 +167,38 @@ def decoder_layer(x, positions, p, cfg, layer):
     return x
 
 
-def forward_logits(cfg, tensors, token_ids, dtype=torch.float64) -> torch.Tensor:
+class _AsStored(dict):
+    """Tensors kept as the file stores them and widened one at a time when a function asks for one:
+    a model of real layer widths in float64 all at once would not fit the host's memory."""
+
+    def __init__(self, tensors, dtype):
+        super().__init__(tensors)
+        self.dtype = dtype
+
+    def __getitem__(self, name):
+        return super().__getitem__(name).to(self.dtype)
+
+    def get(self, name, default=None):
+        return self[name] if name in self else default
+
+    def stored(self, name):
+        return super().__getitem__(name)
+
+
+def forward_logits(cfg, tensors, token_ids, dtype=torch.float64, rows=None) -> torch.Tensor:
     """Logits [T, vocab] of one whole sequence, no cache
-    (src/gpu/forward.rs:1198-1393; the reference keeps the last row only)."""
-    p = {k: v.to(dtype) for k, v in tensors.items()}
-    ids = torch.as_tensor(token_ids, dtype=torch.long)
-    positions = torch.arange(len(ids))
-    x = embedding(p["model.embed_tokens.weight"], ids)
+    (src/gpu/forward.rs:1198-1393; the reference keeps the last row only).  ``rows``: only these
+    positions go through the final norm and the output matrix (the reference's last-row case, for any rows)."""
+    p = tensors if isinstance(tensors, _AsStored) else {k: v.to(dtype) for k, v in tensors.items()}
+    device = next(iter(dict.values(p))).device
+    ids = torch.as_tensor(token_ids, dtype=torch.long).to(device)
+    positions = torch.arange(len(ids), device=device)
+    table = p.stored("model.embed_tokens.weight") if isinstance(p, _AsStored) else p["model.embed_tokens.weight"]
+    x = embedding(table, ids).to(dtype)          # a row gather: widening the gathered rows is widening the table
     for layer in range(cfg["num_hidden_layers"]):
         x = decoder_layer(x, positions, p, cfg, layer)
+    if rows is not None:
+        x = x[torch.as_tensor(list(rows), dtype=torch.long).to(device)]
     x = rms_norm(x, p["model.norm.weight"], cfg["rms_norm_eps"])
     # src/gpu/weights.rs:868-886 — no output matrix means the embedding serves as one
     head = p["lm_head.weight"] if "lm_head.weight" in p else p["model.embed_tokens.weight"]
@@ -185,10 +208,13 @@ def forward_logits(cfg, tensors, token_ids, dtype=torch.float64) -> torch.Tensor
 class PlainModel:
     """Convenience holder: folder -> logits of whole sequences."""
 
-    def __init__(self, folder: str, dtype=torch.float64):
+    def __init__(self, folder: str, dtype=torch.float64, as_stored: bool = False, device="cpu"):
+        """``as_stored``: keep the tensors as the file has them and widen each when it is used; ``device``: where
+        this plain arithmetic runs (the formulas are the same; models of real layer widths take minutes on a CPU)."""
         self.cfg, tensors = read_folder(folder)
         self.dtype = dtype
-        self.tensors = {k: v.to(dtype) for k, v in tensors.items()}
+        tensors = {k: v.to(device) for k, v in tensors.items()}
+        self.tensors = _AsStored(tensors, dtype) if as_stored else {k: v.to(dtype) for k, v in tensors.items()}
 
-    def logits(self, token_ids) -> torch.Tensor:
-        return forward_logits(self.cfg, self.tensors, token_ids, self.dtype)
+    def logits(self, token_ids, rows=None) -> torch.Tensor:
+        return forward_logits(self.cfg, self.tensors, token_ids, self.dtype, rows).cpu()

@@ -196,3 +196,74 @@ def test_random_walk_keeps_the_books():
     for s in list(live):
         c.free_slot(s)
     assert all(g.pool.n_free == g.n_pages for g in c.groups) and c.live_slots == 0
+
+
+def test_epoch_grows_with_every_slot_handed_out_or_given_back():
+    c = make()
+    e0 = c.epoch
+    s = c.alloc_slot()
+    assert c.epoch > e0
+    e1 = c.epoch
+    c.prepare([s], [10]); c.commit([s], [10])
+    assert c.epoch == e1, "steps do not change the set of sequences"
+    c.free_slot(s)
+    assert c.epoch > e1
+
+
+def test_device_table_names_no_free_page_after_free_and_refill():
+    """A sequence ends exactly on a page border after the page for its next position was taken; the slot is
+    freed and filled again with a prompt of the same length while another slot stays alive (so the free list
+    hands out other pages): wherever the device table still names a page, it is the host table's page, and
+    entries of pages given back are cleared with the next upload."""
+    c = make(max_tokens=64 * 12, windows=(None, 24))
+    keep = c.alloc_slot()
+    c.prepare([keep], [70]); c.commit([keep], [70])
+    s = c.alloc_slot()
+    c.prepare([s], [64]); c.commit([s], [64])
+    c.prepare([s], [1])                       # a runner takes the page for position 64 ahead of time
+    ahead = [g.table[s, 1] for g in c.groups]
+    assert all(p >= 0 for p in ahead)
+    c.free_slot(s)
+    other = c.alloc_slot()                    # takes the lowest pages, among them the ones just freed
+    c.prepare([other], [130]); c.commit([other], [130])
+    s2 = c.alloc_slot()
+    c.prepare([s2], [64]); c.commit([s2], [64])
+    for g in c.groups:
+        dev = g.table_dev.numpy()
+        for slot in range(c.max_slots):
+            for p in range(g.max_pages_per_seq):
+                if g.table[slot, p] >= 0:
+                    assert dev[slot, p] == g.table[slot, p]
+                elif dev[slot, p] > 0:
+                    # a page the host no longer lists for this slot must not stay named on the device
+                    raise AssertionError(f"device table of slot {slot} still names page {dev[slot, p]} at {p}")
+    invariant(c)
+
+
+def test_reserve_takes_nothing_when_not_everything_fits():
+    c = make(max_tokens=64 * 6, windows=(None,), max_slots=3)
+    a, b = c.alloc_slot(), c.alloc_slot()
+    c.prepare([a, b], [10, 10]); c.commit([a, b], [10, 10])
+    free = c.free_pages()
+    with pytest.raises(CacheError):
+        c.reserve([a, b], [64 * 3, 64 * 4])          # 2 + 3 more pages, 4 are free
+    assert c.free_pages() == free and [g.held_pages(a) for g in c.groups] == [[0]]
+    with pytest.raises(CacheError):
+        c.reserve([a], [64 * 7])                     # beyond the longest sequence the cache holds
+    assert c.free_pages() == free
+    c.reserve([a, b], [64 * 3, 64 * 3])
+    assert c.free_pages() == [0]
+    invariant(c)
+
+
+def test_rollback_gives_back_what_a_failed_step_took():
+    c = make(max_tokens=64 * 8, windows=(None, 24))
+    s = c.alloc_slot()
+    c.prepare([s], [70]); c.commit([s], [70])
+    free = c.free_pages()
+    c.prepare([s], [200])
+    assert c.free_pages() != free
+    c.rollback([s])
+    assert c.free_pages() == free and c.length(s) == 70
+    c.prepare([s], [1]); c.commit([s], [1])           # the slot goes on as if nothing had happened
+    invariant(c)

@@ -39,3 +39,14 @@ def test_pages_a_new_token_reads():
     assert basic.decode_pages(1, None) == 1 and basic.decode_pages(64, None) == 1 and basic.decode_pages(65, None) == 2
     assert basic.decode_pages(1 << 20, 1024) == 17      # a window of 1,024 keys touches at most 17 pages of 64
     assert basic.decode_pages(100, 1024) == 2
+
+
+def test_decode_descriptor_fits_the_runner_at_its_largest_batch():
+    """A runner's device descriptor is sized once and never moved (captured graphs keep its address): the packed
+    descriptor of the largest decode batch, tile tables included, must fit it."""
+    from rocmforge_b200.engine.batch import StepBatch, StepRequest
+    from rocmforge_b200.engine.graph import DecodeRunner
+    for max_batch in (1, 64, 683, 1024):
+        reqs = [StepRequest(i, [1], [0]) for i in range(max_batch)]
+        packed = StepBatch(reqs, [5] * max_batch, vocab_size=10).pack()
+        assert packed.size <= DecodeRunner.descriptor_words(max_batch)
