@@ -222,7 +222,7 @@ def decode_rate(model, prompts, steps, warmup, check=16):
             "mean_ctx": mean_ctx, "t0": t0, "t1": t1, "checked_steps": checked}
 
 
-def ablation(model, batch, steps=32):
+def ablation(model, batch, steps=32, prompt_len=PROMPT_LEN):
     """Where a replayed decode step's time goes: every kind of kernel in turn is replaced by a stand-in that launches
     nothing and returns a buffer of the right shape, the step's graph is captured anew and timed.  The difference to
     the whole step is what that kernel costs inside the chain (with its overlaps), which a profiler's serialised,
@@ -241,12 +241,12 @@ def ablation(model, batch, steps=32):
         return buffers[key]
 
     def run():
-        cache = model.new_cache(max_tokens=batch * (PROMPT_LEN + 256), max_slots=batch)
+        cache = model.new_cache(max_tokens=batch * (prompt_len + 256), max_slots=batch)
         runner = DecodeRunner(model, cache)
         slots = [cache.alloc_slot() for _ in range(batch)]
-        for s in slots:                                  # PROMPT_LEN cached positions (their content does not matter)
-            cache.prepare([s], [PROMPT_LEN])
-            cache.commit([s], [PROMPT_LEN])
+        for s in slots:                                  # prompt_len cached positions (their content does not matter)
+            cache.prepare([s], [prompt_len])
+            cache.commit([s], [prompt_len])
         runner.greedy_loop(slots, [1] * batch, 4)
         torch.cuda.synchronize()
         _, start, end, _ = runner.greedy_loop(slots, [1] * batch, steps)
@@ -262,42 +262,58 @@ def ablation(model, batch, steps=32):
     def no_attention(q, nh, nkv, hd, *a, **kw):
         return buffer("o", (q.shape[0], nh * hd), torch.bfloat16)
 
-    real_skinny = tc.gemm_tc_skinny
+    real_skinny, real_resnorm = tc.gemm_tc_skinny, tc.gemm_tc_skinny_resnorm
 
     def without(pred):
-        def f(x, w, bias=None, *, mode=tc.STORE, splits=1, out=None):
+        def f(x, w, bias=None, *, mode=tc.STORE, splits=1, out=None, row_ss=None):
             if not pred(w, mode):
-                return real_skinny(x, w, bias, mode=mode, splits=splits, out=out)
+                return real_skinny(x, w, bias, mode=mode, splits=splits, out=out, row_ss=row_ss)
             if out is not None:
                 return out
             M, N = x.shape[0], w.shape[0]
             shape = (splits, M, N) if mode == tc.PARTIAL else (M, N // 2 if mode == tc.SWIGLU else N)
             return buffer(("gemm", shape, mode), shape, torch.bfloat16 if mode in (tc.STORE, tc.SWIGLU) else torch.float32)
-        return f
+
+        def g(x, w, bias, h, norm_weight, splits=1, row_ss=None):
+            if not pred(w, tc.RESNORM):
+                return real_resnorm(x, w, bias, h, norm_weight, splits=splits, row_ss=row_ss)
+            M, N = x.shape[0], w.shape[0]
+            return (buffer(("normed", M, N), (M, N), torch.bfloat16),
+                    buffer(("ss", M, N), ((N + 127) // 128, M), torch.float32))
+        return [(tc, "gemm_tc_skinny", f), (tc, "gemm_tc_skinny_resnorm", g)]
 
     H, I, V = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
     QKV = (cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * cfg.head_dim
-    cases = [("the two norms of a layer", kernels, "add_rmsnorm", no_norm),
-             ("rotation + cache write", kernels, "rope_kv_write", no_rope),
-             ("attention", kernels, "attention_decode_warps", no_attention),
-             ("q|k|v product", tc, "gemm_tc_skinny", without(lambda w, m: w.shape[0] == QKV and m == tc.PARTIAL)),
-             ("o product", tc, "gemm_tc_skinny", without(lambda w, m: tuple(w.shape) == (H, cfg.num_attention_heads * cfg.head_dim))),
-             ("gate/up product", tc, "gemm_tc_skinny", without(lambda w, m: m == tc.SWIGLU)),
-             ("down product", tc, "gemm_tc_skinny", without(lambda w, m: tuple(w.shape) == (H, I))),
-             ("output matrix (per step)", tc, "gemm_tc_skinny", without(lambda w, m: w.shape[0] == V)),
-             ("all products", tc, "gemm_tc_skinny", without(lambda w, m: True))]
+    cases = [("norm kernels (first layer and final norm when the others are fused)", [(kernels, "add_rmsnorm", no_norm)]),
+             ("rotation + cache write", [(kernels, "rope_kv_write", no_rope)]),
+             ("attention", [(kernels, "attention_decode_warps", no_attention)]),
+             ("q|k|v product", without(lambda w, m: w.shape[0] == QKV and m == tc.PARTIAL)),
+             ("o product", without(lambda w, m: tuple(w.shape) == (H, cfg.num_attention_heads * cfg.head_dim))),
+             ("gate/up product", without(lambda w, m: m == tc.SWIGLU)),
+             ("down product", without(lambda w, m: tuple(w.shape) == (H, I))),
+             ("output matrix (per step)", without(lambda w, m: w.shape[0] == V)),
+             ("all products", without(lambda w, m: True))]
     whole = run()
     rows = [{"kernel": "whole step", "us_per_step": round(whole, 1)}]
-    for name, module, attr, stand_in in cases:
-        real = getattr(module, attr)
-        setattr(module, attr, stand_in)
+    for name, patches in cases:
+        saved = [(module, attr, getattr(module, attr)) for module, attr, _ in patches]
+        for module, attr, stand_in in patches:
+            setattr(module, attr, stand_in)
         try:
             t = run()
         finally:
-            setattr(module, attr, real)
+            for module, attr, real in saved:
+                setattr(module, attr, real)
         per_step = "per step" in name or name == "all products"
         rows.append({"kernel": name, "us_per_step": round(whole - t, 1),
                      "us_per_layer": None if per_step else round((whole - t) / L, 2)})
+    if model.options.fused_norm:
+        # what fusing the norms into the products before them is worth: the same step with the norms as kernels
+        model.options.fused_norm = False
+        try:
+            rows.append({"kernel": "whole step with the norms as kernels of their own", "us_per_step": round(run(), 1)})
+        finally:
+            model.options.fused_norm = True
     return rows
 
 
@@ -408,6 +424,11 @@ def main():
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (quick check)")
     ap.add_argument("--only", choices=["decode", "prefill", "ablate", "0.5b", "14b"], default=None,
                     help="run one phase only and print a short line (small cases for profilers)")
+    ap.add_argument("--shape", choices=["7b", "0.5b", "14b"], default="7b",
+                    help="layer sizes for --only decode / prefill / ablate (the full run always measures all three)")
+    ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prompt length of --only decode / ablate")
+    ap.add_argument("--fused-norm-max", type=int, default=None,
+                    help="--only runs: most tokens of a step for which products prepare the norm that follows them")
     ap.add_argument("--seed", type=int, default=0)
     args = ap.parse_args()
     if args.impl == "reference":
@@ -425,21 +446,23 @@ def main():
     if args.only in ("0.5b", "14b"):
         print(json.dumps({"only": args.only, **other_shapes(pk, args.seed, args.only)}))
         return 0
-    raw = dict(SHAPE_7B)
+    raw = dict({"7b": SHAPE_7B, "0.5b": SHAPE_05B, "14b": SHAPE_14B}[args.shape if args.only else "7b"])
     if args.layers:
         raw["num_hidden_layers"] = args.layers
     cfg = Qwen2Config.from_dict(raw)
     V = cfg.vocab_size
     model = rf.Model.random(cfg, seed=args.seed, dtype=torch.bfloat16)
+    if args.only and args.fused_norm_max is not None:
+        model.options.fused_norm_max_tokens = args.fused_norm_max
 
     if args.only == "decode":
-        r = decode_rate(model, random_prompts(args.batch, PROMPT_LEN, V, args.seed), args.steps, warmup)
-        print(json.dumps({"only": "decode", "layers": cfg.num_hidden_layers, "batch": args.batch,
+        r = decode_rate(model, random_prompts(args.batch, args.prompt_len, V, args.seed), args.steps, warmup)
+        print(json.dumps({"only": "decode", "shape": args.shape, "layers": cfg.num_hidden_layers, "batch": args.batch,
                           "ms_per_step": round(r["ms_per_step"], 4), "tok_s": round(r["tok_s"], 1),
                           "checked_steps": r["checked_steps"]}))
         return 0
     if args.only == "ablate":
-        for row in ablation(model, args.batch):
+        for row in ablation(model, args.batch, prompt_len=args.prompt_len):
             print(json.dumps(row))
         return 0
     if args.only == "prefill":

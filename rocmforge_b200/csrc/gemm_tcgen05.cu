@@ -39,6 +39,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);     // full[S], empty[S], tmem_full
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
     __shared__ int abort_flag;
+    __shared__ float rstd_s[SWAP ? BN : 1];                    // 1 / RMS of this tile's tokens (deferred norm of the input)
+    __shared__ int last_split;
 
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -126,6 +128,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // ---------------- epilogue: four warps, one quarter of the 128 lanes each
         const int quarter = warp & 3;
         pdl_wait();                                      // the output may still be read by the kernel before us
+        if (SWAP && p.norm.ss_in) {
+            // the input's norm was left unfinished by the product before us: 1 / RMS of each token of this tile, from
+            // the tiles' sums of squares in index order
+            const int t = threadIdx.x - 64;
+            if (t < BN) {
+                const int m = tile_b * BN + t;
+                float ss = 0.f;
+                if (m < p.M)
+                    for (int i = 0; i < p.norm.ss_in_tiles; ++i) ss += p.norm.ss_in[(size_t)i * p.norm.ss_in_stride + m];
+                rstd_s[t] = rsqrtf(ss * p.norm.ss_inv_width + p.norm.ss_eps);
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
         const bool ok = mbar_wait(smem_u32(&bars[2 * STAGES]), 0, &abort_flag);
         tcgen05_fence_after();
         if (ok && n_kb > 0) {
@@ -143,8 +158,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 } else {
                     // lane = weight row n, registers = consecutive tokens m
                     const int n = row_a, m0 = tile_b * BN + c0;
-                    const float b = (p.bias && n < p.N) ? load_vec(p.bias, p.bias_is_f32, n) : 0.f;
+                    const float b = (p.bias && n < p.N && p.mode != EPI_RESNORM) ? load_vec(p.bias, p.bias_is_f32, n) : 0.f;
                     if (m0 >= p.M) break;                // the tile's other columns are padding, not tokens
+                    if (p.norm.ss_in) {
+#pragma unroll
+                        for (int j = 0; j < CH; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * rstd_s[c0 + j]);
+                    }
                     if (p.mode == EPI_SWIGLU) {
                         // gate in even lanes, up in the odd lane beside it.  Two tokens at a time: the even lane
                         // finishes token j (it gets that token's up), the odd lane token j + 1 (it gets its gate),
@@ -170,9 +189,108 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                 if (p.mode == EPI_STORE) reinterpret_cast<__nv_bfloat16*>(p.out)[o] = __float2bfloat16_rn(v);
                                 else if (p.mode == EPI_F32) reinterpret_cast<float*>(p.out)[o] = v;
                                 else if (p.mode == EPI_RESIDUAL) reinterpret_cast<float*>(p.out)[o] += v;
-                                else reinterpret_cast<float*>(p.out)[(size_t)split * p.partial_stride + o] = v;
+                                else reinterpret_cast<float*>(p.out)[(size_t)split * p.partial_stride + o] = v;     // PARTIAL, RESNORM
                             }
                         }
+                    }
+                }
+            }
+        }
+        if (SWAP && p.mode == EPI_RESNORM) {
+            // ---- the split that arrives last at this output tile finishes the residual update and prepares the norm
+            __threadfence();                                             // this split's partial sums are visible device-wide
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (threadIdx.x == 64) {
+                int* ctr = p.norm.counters + tile_a * gridDim.x + tile_b;
+                const int seen = atomicAdd(ctr, 1);
+                last_split = (seen == (int)gridDim.z - 1) && !abort_flag;
+                if (seen == (int)gridDim.z - 1) *ctr = 0;                // zero again for the next launch
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (last_split) {
+                __threadfence();
+                // a warp takes whole tokens: lane l owns columns 4l .. 4l+3 of the tile, so a token's 128 columns are
+                // one 16-byte load per lane and per addend, all of them in flight before the first is used
+                const int m0 = tile_b * BN, n4 = tile_a * TC_BM + 4 * lane, S = (int)gridDim.z;
+                const float* part = reinterpret_cast<const float*>(p.out);
+                const bool vec = n4 + 3 < p.N && (p.ldo & 3) == 0;
+                float bv[4], wv[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const bool okq = n4 + q < p.N;
+                    bv[q] = (p.bias && okq) ? load_vec(p.bias, p.bias_is_f32, n4 + q) : 0.f;
+                    wv[q] = okq ? load_vec(p.norm.norm_w, p.norm.norm_w_is_f32, n4 + q) : 0.f;
+                }
+                constexpr int TOK = 2;                                   // tokens of a warp in flight at once
+                for (int j0 = quarter * TOK; j0 < BN && m0 + j0 < p.M; j0 += 4 * TOK) {
+                    float4 acc[TOK];
+                    if (vec) {
+#pragma unroll
+                        for (int t = 0; t < TOK; ++t) {
+                            const int m = m0 + j0 + t;
+                            acc[t] = m < p.M ? *reinterpret_cast<const float4*>(p.norm.resid + (size_t)m * p.ldo + n4)
+                                             : make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
+                        for (int s0 = 0; s0 < S; s0 += 8) {              // eight splits of each token in flight at once
+                            float4 add[TOK][8];
+#pragma unroll
+                            for (int t = 0; t < TOK; ++t) {
+                                const size_t o = (size_t)(m0 + j0 + t) * p.ldo + n4;
+                                if (m0 + j0 + t < p.M) {
+#pragma unroll
+                                    for (int s2 = 0; s2 < 8; ++s2)
+                                        if (s0 + s2 < S)
+                                            add[t][s2] = __ldcg(reinterpret_cast<const float4*>(part + (size_t)(s0 + s2) * p.partial_stride + o));
+                                }
+                            }
+#pragma unroll
+                            for (int t = 0; t < TOK; ++t)
+                                if (m0 + j0 + t < p.M) {
+#pragma unroll
+                                    for (int s2 = 0; s2 < 8; ++s2)       // splits in index order, whoever comes last
+                                        if (s0 + s2 < S) {
+                                            acc[t].x += add[t][s2].x; acc[t].y += add[t][s2].y;
+                                            acc[t].z += add[t][s2].z; acc[t].w += add[t][s2].w;
+                                        }
+                                }
+                        }
+                    } else {
+#pragma unroll
+                        for (int t = 0; t < TOK; ++t) {
+                            const int m = m0 + j0 + t;
+                            float a[4] = {0.f, 0.f, 0.f, 0.f};
+                            if (m < p.M)
+                                for (int q = 0; q < 4; ++q)
+                                    if (n4 + q < p.N) {
+                                        const size_t o = (size_t)m * p.ldo + n4 + q;
+                                        a[q] = p.norm.resid[o];
+                                        for (int s2 = 0; s2 < S; ++s2) a[q] += __ldcg(part + (size_t)s2 * p.partial_stride + o);
+                                    }
+                            acc[t] = make_float4(a[0], a[1], a[2], a[3]);
+                        }
+                    }
+#pragma unroll
+                    for (int t = 0; t < TOK; ++t) {
+                        const int m = m0 + j0 + t;
+                        if (m >= p.M) break;                             // uniform over the warp
+                        const float v[4] = {acc[t].x + bv[0], acc[t].y + bv[1], acc[t].z + bv[2], acc[t].w + bv[3]};
+                        const size_t o = (size_t)m * p.ldo + n4;
+                        float sq = 0.f;
+                        if (vec) {
+                            *reinterpret_cast<float4*>(p.norm.resid + o) = make_float4(v[0], v[1], v[2], v[3]);
+                            *reinterpret_cast<uint2*>(p.norm.normed + o) =
+                                make_uint2(pack_bf16x2(v[0] * wv[0], v[1] * wv[1]), pack_bf16x2(v[2] * wv[2], v[3] * wv[3]));
+                            sq = (v[0] * v[0] + v[1] * v[1]) + (v[2] * v[2] + v[3] * v[3]);
+                        } else {
+                            for (int q = 0; q < 4; ++q)
+                                if (n4 + q < p.N) {
+                                    p.norm.resid[o + q] = v[q];
+                                    p.norm.normed[o + q] = __float2bfloat16_rn(v[q] * wv[q]);
+                                    sq += v[q] * v[q];
+                                }
+                        }
+                        sq = warp_sum(sq);
+                        if (lane == 0) p.norm.ss_out[(size_t)tile_a * p.norm.ss_out_stride + m] = sq;
                     }
                 }
             }
@@ -216,10 +334,10 @@ int rf_gemm_tc_supported(int M, int N, int K, int mode) {
 // Tokens as rows: out[M, N] (mode STORE / F32 / RESIDUAL) or out[M, N/2] (SWIGLU).
 int rf_gemm_tc(const void* X, int ldx, const void* W, const void* bias, int bias_is_f32, void* out, int ldo,
                int M, int N, int K, int mode, int* status, cudaStream_t st) {
-    if (!rf_gemm_tc_supported(M, N, K, mode) || mode == EPI_PARTIAL) return RF_ERR_UNSUPPORTED;
+    if (!rf_gemm_tc_supported(M, N, K, mode) || mode == EPI_PARTIAL || mode == EPI_RESNORM) return RF_ERR_UNSUPPORTED;
     CUtensorMap ma, mb;
     int e;
-    TcParams p{out, bias, bias_is_f32, M, N, K, ldo, mode, (K + TC_BK - 1) / TC_BK, 0, status, 1};
+    TcParams p{out, bias, bias_is_f32, M, N, K, ldo, mode, (K + TC_BK - 1) / TC_BK, 0, status, 1, {}};
     if (N > 128) {
         if ((e = make_map(&ma, X, M, K, ldx, TC_BM)) || (e = make_map(&mb, W, N, K, K, 256))) return e;
         dim3 grid((N + 255) / 256, (M + TC_BM - 1) / TC_BM, 1);
@@ -231,16 +349,30 @@ int rf_gemm_tc(const void* X, int ldx, const void* W, const void* bias, int bias
 }
 
 // Weights as rows, for M <= 256 tokens in tiles of up to 128 (the tiles of one weight tile are neighbours in the grid,
-// so the weight comes from memory once and from L2 after that).  splits > 1 requires mode PARTIAL: out is then
+// so the weight comes from memory once and from L2 after that).  splits > 1 requires mode PARTIAL or RESNORM: out is then
 // [splits, M, N] float32 (partial_stride = M * N) and holds the partial sums of each K range.
-int rf_gemm_tc_skinny(const void* X, int ldx, const void* W, const void* bias, int bias_is_f32, void* out, int ldo,
-                      int M, int N, int K, int mode, int splits, int* status, cudaStream_t st) {
+//
+// ss_in (optional): the activations X are (residual stream * norm weight) of a norm that the product before left
+// unfinished; ss_in [ss_in_tiles][ss_in_stride] holds the tiles' sums of squares of the stream, and every output row m
+// is scaled by rsqrt(sum_t ss_in[t][m] / K + ss_eps).
+// Mode RESNORM: out is the [splits, M, N] scratch for the partial sums; resid [M, N] += their sum (+ bias), normed
+// [M, N] = resid * norm_w in bfloat16, ss_out [ceil(N/128)][ss_out_stride] = each weight tile's sum of resid^2 per
+// token; counters: ceil(N/128) * ceil(M/tile) ints, zero before the first launch and left zero.
+int rf_gemm_tc_skinny_ex(const void* X, int ldx, const void* W, const void* bias, int bias_is_f32, void* out, int ldo,
+                         int M, int N, int K, int mode, int splits, const float* ss_in, int ss_in_tiles,
+                         int ss_in_stride, float ss_eps, float* resid, const void* norm_w, int norm_w_is_f32,
+                         void* normed, float* ss_out, int ss_out_stride, int* counters, int* status, cudaStream_t st) {
     if (!rf_gemm_tc_supported(M, N, K, mode) || M > 256 || splits < 1) return RF_ERR_UNSUPPORTED;
-    if (splits > 1 && mode != EPI_PARTIAL) return RF_ERR_BAD_ARG;
+    if (splits > 1 && mode != EPI_PARTIAL && mode != EPI_RESNORM) return RF_ERR_BAD_ARG;
+    if (mode == EPI_RESNORM && (!resid || !norm_w || !normed || !ss_out || !counters || ldo != N || ss_out_stride < M))
+        return RF_ERR_BAD_ARG;
+    if (ss_in && (ss_in_tiles <= 0 || ss_in_stride < M)) return RF_ERR_BAD_ARG;
     const int kb = (K + TC_BK - 1) / TC_BK;
     const int per = (kb + splits - 1) / splits;
     if ((splits - 1) * per >= kb) return RF_ERR_BAD_ARG;          // an empty split would leave its partial unwritten
-    TcParams p{out, bias, bias_is_f32, M, N, K, ldo, mode, per, (long long)M * ldo, status, 1};
+    TcParams p{out, bias, bias_is_f32, M, N, K, ldo, mode, per, (long long)M * ldo, status, 1, {}};
+    p.norm = TcNorm{resid, norm_w, norm_w_is_f32, reinterpret_cast<__nv_bfloat16*>(normed), ss_out, ss_out_stride,
+                    counters, ss_in, ss_in_tiles, ss_in_stride, ss_eps, 1.0f / (float)K};
     CUtensorMap ma, mb;
     int e;
     const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
@@ -254,6 +386,13 @@ int rf_gemm_tc_skinny(const void* X, int ldx, const void* W, const void* bias, i
     if (bn == 32) return launch_cfg<32, true, 5>(ma, mb, p, grid, st);
     if (bn == 64) return launch_cfg<64, true, 4>(ma, mb, p, grid, st);
     return launch_cfg<128, true, 3>(ma, mb, p, grid, st);
+}
+
+int rf_gemm_tc_skinny(const void* X, int ldx, const void* W, const void* bias, int bias_is_f32, void* out, int ldo,
+                      int M, int N, int K, int mode, int splits, int* status, cudaStream_t st) {
+    if (mode == EPI_RESNORM) return RF_ERR_BAD_ARG;
+    return rf_gemm_tc_skinny_ex(X, ldx, W, bias, bias_is_f32, out, ldo, M, N, K, mode, splits, nullptr, 0, 0, 0.f,
+                                nullptr, nullptr, 0, nullptr, nullptr, 0, nullptr, status, st);
 }
 
 }

@@ -10,7 +10,27 @@
 #define TC_THREADS 192
 #define TC_WAIT_LIMIT_NS 2000000000ULL      // 2 s
 
-enum { EPI_STORE = 0, EPI_F32 = 1, EPI_RESIDUAL = 2, EPI_SWIGLU = 3, EPI_PARTIAL = 4 };
+enum { EPI_STORE = 0, EPI_F32 = 1, EPI_RESIDUAL = 2, EPI_SWIGLU = 3, EPI_PARTIAL = 4, EPI_RESNORM = 5 };
+
+// What the weights-as-rows kernel needs to finish a residual update and prepare the norm that follows it
+// (mode EPI_RESNORM), and to apply a norm that was prepared that way to its own input (ss_in).
+struct TcNorm {
+    // EPI_RESNORM: of the K splits of an output tile the one that arrives last adds their partial sums (in index
+    // order) and the bias into the residual stream, writes stream * norm weight in bfloat16 for the next product
+    // and the tile's share of every token's sum of squares
+    float* resid;               // [M, N] 32-bit residual stream, updated in place
+    const void* norm_w;         // [N] weight of the norm that follows
+    int norm_w_is_f32;
+    __nv_bfloat16* normed;      // [M, N] out: (stream after the update) * norm weight, not yet divided by the RMS
+    float* ss_out;              // [ceil(N/128)][ss_out_stride] out: sum over the tile's columns of stream^2
+    int ss_out_stride;
+    int* counters;              // one per (weight tile, token tile): zero between launches
+    // input side: this product's activations are stream * norm weight of a norm prepared as above; row m is
+    // scaled by rsqrt(sum_t ss_in[t][m] * ss_inv_width + ss_eps) in the epilogue (the product is linear in it)
+    const float* ss_in;         // null: the activations are already normalised
+    int ss_in_tiles, ss_in_stride;
+    float ss_eps, ss_inv_width;
+};
 
 struct TcParams {
     void* out;              // see the epilogue
@@ -23,6 +43,7 @@ struct TcParams {
     long long partial_stride;   // elements between the partial sums of two splits
     int* status;            // device word: 0 = fine
     int splits;             // clustered kernel: K parts of the residual epilogue, added in order (1 = none)
+    TcNorm norm;            // weights-as-rows kernel only; zero elsewhere
 };
 
 // ---------------------------------------------------------------- PTX wrappers

@@ -14,6 +14,7 @@ from typing import Optional
 import torch
 
 from .. import kernels
+from .stream import ScaledRows
 
 
 @dataclass
@@ -24,6 +25,12 @@ class Options:
     tcgen05_attention: bool = True       # prefill attention with tcgen05.mma (else the mma.sync kernel)
     clustered_decode: bool = True        # decode attention by clusters of CTAs (else one CTA per 128-key chunk)
     decode_graphs: bool = True           # replay decode steps from CUDA graphs in the generation loop
+    # few tokens: the product that updates the stream also prepares the norm that follows (no norm kernel).  Off: at
+    # the 7B shape the split that finishes an output tile last needs as long for the fence, the counter and the partial
+    # sums of its tile (o product 6.3 -> 11.0 us, down 22.9 -> 25.9 us at batch 8) as the two norm kernels took
+    # (7.6 us a layer): 2.92 ms a step against 2.91 ms; with 64 tokens, or the 19 splits of the 0.5B shape, it loses
+    fused_norm: bool = False
+    fused_norm_max_tokens: int = 32
 
 
 class StepContext:
@@ -57,13 +64,24 @@ class StepContext:
                 and kernels.tensor_core.supported(x.shape[0], w.shape[0], w.shape[1], mode)
                 and x.data_ptr() % 16 == 0 and (x.stride(0) * 2) % 16 == 0)
 
+    def _rows(self, x, w, mode):
+        """(tensor, row_ss) of an activation: the sums of squares go along where the product scales rows itself,
+        else the rows are normalised first."""
+        if not isinstance(x, ScaledRows):
+            return x, None
+        tc = kernels.tensor_core
+        if x.x.shape[0] <= tc.SKINNY_MAX_TOKENS and self._tensor_cores(x.x, w, mode):
+            return x.x, x.row_ss
+        return x.materialize(), None
+
     def matmul(self, x, w, bias=None, *, out_f32=False):
         """x [M,K] @ w[N,K]^T (+ bias) -> [M,N] in the compute dtype, or in float32."""
         tc = kernels.tensor_core
         mode = tc.F32 if out_f32 else tc.STORE
+        x, row_ss = self._rows(x, w, mode)
         if self._tensor_cores(x, w, mode):
             if x.shape[0] <= tc.SKINNY_MAX_TOKENS:
-                return tc.gemm_tc_skinny(x, w, bias, mode=mode)
+                return tc.gemm_tc_skinny(x, w, bias, mode=mode, row_ss=row_ss)
             return tc.gemm_tc(x, w, bias, mode=mode)
         return kernels.gemm_simt(x, w, bias, out_f32=out_f32)
 
@@ -71,14 +89,25 @@ class StepContext:
         """stream += x w^T (+ bias), summed in 32-bit: into ``h`` directly, or left pending as the
         32-bit partial sums of a K-split product (the next norm adds them in index order)."""
         tc = kernels.tensor_core
+        follows = stream.take_hint()                 # the norm that reads the stream after this update, if we were told
+        x, row_ss = self._rows(x, w, tc.RESIDUAL)
         if self._tensor_cores(x, w, tc.RESIDUAL):
             if x.shape[0] <= tc.SKINNY_MAX_TOKENS:
+                deferred = (follows.deferred_params() if (follows is not None and self.options.fused_norm
+                                                          and x.shape[0] <= self.options.fused_norm_max_tokens) else None)
+                if deferred is not None and deferred[0].shape == (w.shape[0],) and stream.h.is_contiguous():
+                    # the split that finishes last adds all partial sums into the stream and prepares the norm
+                    stream.flush()
+                    normed, ss = tc.gemm_tc_skinny_resnorm(x, w, bias, stream.h, deferred[0],
+                                                           splits=tc.split_k_for(w.shape[0], w.shape[1]), row_ss=row_ss)
+                    stream.prepared = (follows, ScaledRows(normed, ss, deferred[1], w.shape[0]))
+                    return
                 splits = tc.split_k_for(w.shape[0], w.shape[1]) if bias is None else 1
                 if splits > 1:
-                    stream.add_pending(tc.gemm_tc_skinny(x, w, mode=tc.PARTIAL, splits=splits))
+                    stream.add_pending(tc.gemm_tc_skinny(x, w, mode=tc.PARTIAL, splits=splits, row_ss=row_ss))
                     return
                 stream.flush()
-                tc.gemm_tc_skinny(x, w, bias, mode=tc.RESIDUAL, out=stream.h)
+                tc.gemm_tc_skinny(x, w, bias, mode=tc.RESIDUAL, out=stream.h, row_ss=row_ss)
                 return
             stream.flush()
             tc.gemm_tc(x, w, bias, mode=tc.RESIDUAL, out=stream.h)
@@ -90,10 +119,13 @@ class StepContext:
         """silu(gate) * up from the fused, row-interleaved gate/up matrix."""
         tc = kernels.tensor_core
         w = gate_up.weight
+        y, row_ss = self._rows(y, w, tc.SWIGLU)
         if gate_up.bias is None and self._tensor_cores(y, w, tc.SWIGLU):
             if y.shape[0] <= tc.SKINNY_MAX_TOKENS:
-                return tc.gemm_tc_skinny(y, w, mode=tc.SWIGLU)
+                return tc.gemm_tc_skinny(y, w, mode=tc.SWIGLU, row_ss=row_ss)
             return tc.gemm_tc(y, w, mode=tc.SWIGLU)
+        if row_ss is not None:
+            y = ScaledRows(y, row_ss[0], row_ss[1], w.shape[1]).materialize()
         gu = self.matmul(y, w, gate_up.bias)
         return kernels.swiglu(gu)
 
@@ -107,15 +139,18 @@ class StepContext:
         """
         tc = kernels.tensor_core
         w, bias = mixer.qkv.weight, mixer.qkv.bias
+        y, row_ss = self._rows(y, w, tc.PARTIAL)
         rope = dict(tok_seq=self.tok_seq, tok_pos=self.tok_pos, seq_slot=self.seq_slot,
                     block_table=view.block_table, k_pages=view.k_pages, v_pages=view.v_pages, write_kv=view.writes)
         if y.shape[0] <= tc.SKINNY_MAX_TOKENS and self._tensor_cores(y, w, tc.PARTIAL):
             splits = tc.split_k_for(w.shape[0], w.shape[1])
             if splits > 1:
-                parts = tc.gemm_tc_skinny(y, w, mode=tc.PARTIAL, splits=splits)
+                parts = tc.gemm_tc_skinny(y, w, mode=tc.PARTIAL, splits=splits, row_ss=row_ss)
                 return kernels.rope_kv_write(parts, mixer.n_heads, mixer.n_kv_heads, mixer.head_dim,
                                              mixer.position.inv_freq, bias=bias, compute_dtype=self.compute_dtype,
                                              **rope)
+        if row_ss is not None:
+            y = ScaledRows(y, row_ss[0], row_ss[1], w.shape[1])
         qkv = self.matmul(y, w, bias)
         return kernels.rope_kv_write(qkv, mixer.n_heads, mixer.n_kv_heads, mixer.head_dim,
                                      mixer.position.inv_freq, **rope)

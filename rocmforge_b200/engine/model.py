@@ -184,7 +184,12 @@ class Model:
         for i, entry in enumerate(spec.schedule):
             owner = i if entry.kv_from is None else entry.kv_from
             view = cache.view(owner, writes=entry.kv_from is None)
+            # the norm that reads the stream after this block: the next execution's first norm (the final norm gathers
+            # rows and runs as a kernel of its own)
+            nxt = spec.schedule[i + 1] if i + 1 < len(spec.schedule) else None
+            stream.after_block = spec.blocks[nxt.layer].entry_norm() if nxt is not None else None
             spec.blocks[entry.layer].forward(ctx, stream, view)
+        stream.next_norm = stream.after_block = None
         if ctx.R == 0:
             return None
         y = spec.final_norm.forward(ctx, stream, rows=ctx.want_rows)

@@ -6,9 +6,9 @@ from typing import Optional
 
 import torch
 
-from ._ffi import KernelError, c_int, c_ll, c_void_p, check, fn, need, need_cuda, ptr, stream
+from ._ffi import KernelError, c_float, c_int, c_ll, c_void_p, check, fn, need, need_cuda, ptr, stream
 
-STORE, F32, RESIDUAL, SWIGLU, PARTIAL = 0, 1, 2, 3, 4
+STORE, F32, RESIDUAL, SWIGLU, PARTIAL, RESNORM = 0, 1, 2, 3, 4, 5
 SKINNY_MAX_TOKENS = 128     # above it the large-M kernels stream the weights better (7B shape, decode step: 128 tokens
                             # 5.09 ms skinny / 6.38 ms clustered; 192 tokens as tiles of 64: 7.78 / 6.73)
 
@@ -167,15 +167,33 @@ def split_k_for(N: int, K: int, sm_count: int = 148) -> int:
     return (kb + per - 1) // per                   # no empty split
 
 
+_EX_ARGS = (c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+            c_void_p, c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p)
+
+
+def _row_ss_args(row_ss, M):
+    """(pointer, tiles, stride, eps) of a deferred norm's sums of squares, or zeros."""
+    if row_ss is None:
+        return ptr(None), 0, 0, 0.0
+    ss, eps = row_ss
+    need(ss.dtype == torch.float32 and ss.dim() == 2 and ss.stride(1) == 1 and ss.shape[1] >= M and ss.is_cuda,
+         "skinny gemm: sums of squares must be a float32 [tiles, >= M] tensor on the device")
+    return ptr(ss), ss.shape[0], ss.stride(0), float(eps)
+
+
 def gemm_tc_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, *, mode: int = STORE,
-                   splits: int = 1, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                   splits: int = 1, out: Optional[torch.Tensor] = None, row_ss=None) -> torch.Tensor:
     """Weights as accumulator rows, for few tokens (up to 128 in one tile).  With ``splits`` > 1 the mode must be PARTIAL and
-    the result is the float32 stack [splits, M, N] of partial sums."""
+    the result is the float32 stack [splits, M, N] of partial sums.
+
+    ``row_ss`` = (ss [tiles, >= M] float32, eps): ``x`` holds rows that still have to be divided by their RMS
+    (see ``gemm_tc_skinny_resnorm``); output row m is scaled by rsqrt(sum_t ss[t, m] / K + eps)."""
     _common(x, w, bias, out)
     M, K = x.shape
     N = w.shape[0]
     need(M <= SKINNY_MAX_TOKENS, f"skinny gemm takes at most {SKINNY_MAX_TOKENS} tokens, got {M}")
     need(supported(M, N, K, mode), f"tensor-core gemm: shape {M}x{N}x{K} is not supported")
+    need(mode != RESNORM, "skinny gemm: the fused residual + norm epilogue has its own function")
     need(splits == 1 or mode == PARTIAL, "skinny gemm: several K splits need mode PARTIAL")
     cols = N // 2 if mode == SWIGLU else N
     odt = torch.bfloat16 if mode in (STORE, SWIGLU) else torch.float32
@@ -184,8 +202,60 @@ def gemm_tc_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor
         need(mode != RESIDUAL, "gemm: RESIDUAL needs the tensor to add into")
         out = torch.empty(shape, dtype=odt, device=x.device)
     need(tuple(out.shape) == shape and out.dtype == odt and out.is_contiguous(), "gemm: output has the wrong shape or dtype")
-    f = _f("rf_gemm_tc_skinny", c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
-           c_int, c_int, c_void_p, c_void_p)
+    if row_ss is None:
+        f = _f("rf_gemm_tc_skinny", c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
+               c_int, c_int, c_void_p, c_void_p)
+        check(f(ptr(x), x.stride(0), ptr(w), ptr(bias), int(bias is not None and bias.dtype == torch.float32), ptr(out),
+                cols, M, N, K, mode, splits, ptr(status_word(x.device)), stream()), f"gemm_tc_skinny ({M}x{N}x{K})")
+        return out
+    f = _f("rf_gemm_tc_skinny_ex", *_EX_ARGS)
+    ss_ptr, ss_tiles, ss_stride, eps = _row_ss_args(row_ss, M)
     check(f(ptr(x), x.stride(0), ptr(w), ptr(bias), int(bias is not None and bias.dtype == torch.float32), ptr(out),
-            cols, M, N, K, mode, splits, ptr(status_word(x.device)), stream()), f"gemm_tc_skinny ({M}x{N}x{K})")
+            cols, M, N, K, mode, splits, ss_ptr, ss_tiles, ss_stride, eps, ptr(None), ptr(None), 0, ptr(None), ptr(None), 0,
+            ptr(None), ptr(status_word(x.device)), stream()), f"gemm_tc_skinny ({M}x{N}x{K}, rows scaled)")
     return out
+
+
+_tile_counters = {}
+
+
+def tile_counters(device, n: int) -> torch.Tensor:
+    """Arrival counters of the fused residual + norm epilogue (one per output tile): zeroed once, left zeroed by every launch."""
+    need(n <= 1 << 16, f"resnorm: {n} output tiles exceed the counters of this library")
+    key = torch.device(device).index or 0
+    t = _tile_counters.get(key)
+    if t is None:              # one buffer of fixed size per device, never replaced: captured graphs keep its address
+        t = _tile_counters[key] = register_counters(torch.zeros((1 << 16,), dtype=torch.int32, device=device))
+    return t
+
+
+def gemm_tc_skinny_resnorm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], h: torch.Tensor,
+                           norm_weight: torch.Tensor, splits: int = 1, row_ss=None):
+    """h += x w^T (+ bias) for few tokens, and the next RMS norm prepared in the same launch.
+
+    The product is split over K as in mode PARTIAL; of the splits of an output tile the one that finishes last adds all
+    partial sums (in index order, so the result does not depend on which one that is) and the bias into the 32-bit
+    stream ``h`` [M, N], and writes ``normed`` [M, N] = h * norm_weight in bfloat16 and ``ss`` [ceil(N/128), M], each
+    weight tile's sum of h^2 per token.  Whoever multiplies ``normed`` by a matrix next scales its output rows by
+    rsqrt(sum_t ss[t, m] / N + eps) (``row_ss`` of ``gemm_tc_skinny``), which completes the norm.  Returns (normed, ss)."""
+    _common(x, w, bias, None)
+    need_cuda(h, norm_weight)
+    M, K = x.shape
+    N = w.shape[0]
+    need(M <= SKINNY_MAX_TOKENS, f"skinny gemm takes at most {SKINNY_MAX_TOKENS} tokens, got {M}")
+    need(supported(M, N, K, RESNORM), f"tensor-core gemm: shape {M}x{N}x{K} is not supported")
+    need(h.dtype == torch.float32 and tuple(h.shape) == (M, N) and h.is_contiguous(), "resnorm: h must be float32 [M, N]")
+    need(norm_weight.shape == (N,) and norm_weight.dtype in (torch.float32, torch.bfloat16), "resnorm: norm weight must be [N]")
+    tiles = (N + 127) // 128
+    bn = 16 if M <= 16 else (32 if M <= 32 else (64 if M <= 64 else 128))
+    parts = torch.empty((splits, M, N), dtype=torch.float32, device=x.device)
+    normed = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    ss = torch.empty((tiles, M), dtype=torch.float32, device=x.device)
+    counters = tile_counters(x.device, tiles * ((M + bn - 1) // bn))
+    f = _f("rf_gemm_tc_skinny_ex", *_EX_ARGS)
+    ss_ptr, ss_tiles, ss_stride, eps = _row_ss_args(row_ss, M)
+    check(f(ptr(x), x.stride(0), ptr(w), ptr(bias), int(bias is not None and bias.dtype == torch.float32), ptr(parts),
+            N, M, N, K, RESNORM, splits, ss_ptr, ss_tiles, ss_stride, eps, ptr(h), ptr(norm_weight),
+            int(norm_weight.dtype == torch.float32), ptr(normed), ptr(ss), ss.stride(0), ptr(counters),
+            ptr(status_word(x.device)), stream()), f"gemm_tc_skinny_resnorm ({M}x{N}x{K})")
+    return normed, ss

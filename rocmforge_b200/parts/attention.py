@@ -26,6 +26,8 @@ class GQAAttention(Mixer):
     in its decode kernels, src/gpu/ops.rs:748-880).
     """
 
+    accepts_scaled_rows = True
+
     def __init__(self, hidden: int, n_heads: int, n_kv_heads: int, head_dim: int, *, qkv_bias: bool,
                  o_bias: bool = False, window: Optional[int] = None, position=None,
                  scale: Optional[float] = None):

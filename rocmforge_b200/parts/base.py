@@ -38,10 +38,19 @@ class Part:
 
 
 class Norm(Part):
-    """y = norm(h + pending).  See engine.stream.ResidualStream for ``stream``."""
+    """y = norm(h + pending).  See engine.stream.ResidualStream for ``stream``.
 
-    def forward(self, ctx, stream, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    ``deferred_ok``: the caller's consumer takes ``engine.stream.ScaledRows`` (rows not yet divided by their RMS)
+    as well as a tensor; a norm that was prepared by the product before it may then hand those on.
+    ``deferred_params`` returns (weight, eps) if the norm is y = x * rsqrt(mean(x^2) + eps) * weight, so that a
+    product can prepare it in its epilogue, else None.
+    """
+
+    def forward(self, ctx, stream, rows: Optional[torch.Tensor] = None, deferred_ok: bool = False):
         raise NotImplementedError
+
+    def deferred_params(self):
+        return None
 
 
 class PositionEncoding(Part):
@@ -59,6 +68,8 @@ class Mixer(Part):
     of the step's tokens, the view of its cache, and adds its result to ``stream``.
     """
 
+    accepts_scaled_rows = False      # True: ``y`` may be an engine.stream.ScaledRows (passed on to ctx's products)
+
     def cache_request(self):
         return None
 
@@ -68,6 +79,8 @@ class Mixer(Part):
 
 class FeedForward(Part):
     """Position-wise transformation (dense here; routed experts would live behind the same face)."""
+
+    accepts_scaled_rows = False      # as for Mixer
 
     def forward(self, ctx, y: torch.Tensor, stream) -> None:
         raise NotImplementedError
@@ -80,6 +93,11 @@ class Block(Part):
 
     def forward(self, ctx, stream, cache_view) -> None:
         raise NotImplementedError
+
+    def entry_norm(self):
+        """The norm that reads the stream first when this block runs, if the block lets the product before it
+        prepare that norm (see ResidualStream.next_norm); None otherwise."""
+        return None
 
     def sub_parts(self) -> Dict[str, Part]:
         """{prefix relative to the block: part}."""

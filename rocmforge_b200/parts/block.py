@@ -23,8 +23,15 @@ class PreNormBlock(Block):
         return {self.names["norm1"]: self.norm1, self.names["mixer"]: self.mixer,
                 self.names["norm2"]: self.norm2, self.names["ffn"]: self.ffn}
 
+    def entry_norm(self):
+        return self.norm1 if self.mixer.accepts_scaled_rows else None
+
     def forward(self, ctx, stream, cache_view):
-        y = self.norm1.forward(ctx, stream)
+        after = stream.after_block                   # the norm that follows this block (the model knows the order)
+        y = self.norm1.forward(ctx, stream, deferred_ok=self.mixer.accepts_scaled_rows)
+        stream.next_norm = self.norm2 if self.ffn.accepts_scaled_rows else None
         self.mixer.forward(ctx, y, cache_view, stream)
-        y = self.norm2.forward(ctx, stream)
+        y = self.norm2.forward(ctx, stream, deferred_ok=self.ffn.accepts_scaled_rows)
+        stream.next_norm = after
         self.ffn.forward(ctx, y, stream)
+        stream.next_norm = None

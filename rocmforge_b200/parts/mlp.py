@@ -22,6 +22,8 @@ class GatedMLP(FeedForward):
     decode kernels, src/gpu/forward.rs:2485-2500).
     """
 
+    accepts_scaled_rows = True
+
     def __init__(self, hidden: int, intermediate: int, activation: str = "silu"):
         if activation != "silu":
             raise ValueError(f"gated_mlp: activation {activation!r} has no kernel")

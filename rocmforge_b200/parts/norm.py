@@ -32,7 +32,14 @@ class RMSNorm(Norm):
     def cuda_modules(self, compute_dtype):
         return ["elementwise"]
 
-    def forward(self, ctx, stream, rows=None):
+    def deferred_params(self):
+        return (self.weight, self.eps)
+
+    def forward(self, ctx, stream, rows=None, deferred_ok=False):
+        prepared, stream.prepared = stream.prepared, None
+        if prepared is not None and prepared[0] is self and rows is None and stream.pending is None:
+            # the product that updated the stream has multiplied by this norm's weight and left the sums of squares
+            return prepared[1] if deferred_ok else prepared[1].materialize()
         y = kernels.add_rmsnorm(stream.h, self.weight, self.eps, self.compute_dtype,
                                 pending=stream.pending, rows=rows)
         if rows is None:

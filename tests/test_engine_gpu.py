@@ -77,13 +77,17 @@ def test_tuned_kernel_paths_prompt_chunk_decode_and_batch(folders, name, dtype):
                             f"{name} batch decode step {step}")
 
 
-@pytest.mark.parametrize("option", ["clustered_decode", "tcgen05_attention", "tuned_attention", "tensor_core_gemm"])
+@pytest.mark.parametrize("option", ["clustered_decode", "tcgen05_attention", "tuned_attention", "tensor_core_gemm",
+                                    "fused_norm"])
 @pytest.mark.parametrize("name", ["D", "E"])
 def test_every_switch_of_the_engine_keeps_the_results(folders, name, option):
-    """Each option set to False takes another kernel for the same step (the chunked decode attention, the
-    mma.sync prefill attention, the generic attention, the CUDA-core products): same logits as the plain model."""
+    """Each option flipped takes another kernel for the same step (the chunked decode attention, the mma.sync
+    prefill attention, the generic attention, the CUDA-core products; norms prepared by the product before them):
+    same logits as the plain model."""
+    import rocmforge_b200 as rf
     from rocmforge_b200 import StepRequest
-    m, p = engine(folders, name, "bfloat16", **{option: False}), plain(folders, name, "bfloat16")
+    m = engine(folders, name, "bfloat16", **{option: not getattr(rf.Options(), option)})
+    p = plain(folders, name, "bfloat16")
     V = CONFIGS[name]["vocab_size"]
     cache = m.new_cache(max_tokens=64 * 12, max_slots=2)
     seqs = [random_tokens(V, 330, 71), random_tokens(V, 150, 72)]

@@ -114,6 +114,31 @@ def test_real_widths_in_the_three_cuttings(name, tmp_path_factory):
 
 
 @pytest.mark.parametrize("name", ["7B", "0.5B"])
+def test_real_widths_with_norms_prepared_by_the_product_before_them(name, tmp_path_factory):
+    """``Options.fused_norm``: the o and down products of few tokens add their K splits into the stream themselves and
+    leave the next norm half done; q|k|v and gate/up finish it by scaling their output rows.  Decoding and a short
+    appended chunk at real widths (10 and 19 splits) against the plain model."""
+    from rocmforge_b200 import StepRequest
+    m, p = pair(name, tmp_path_factory)
+    V = WIDTHS[name]["vocab_size"]
+    m.options.fused_norm = True
+    try:
+        cache = m.new_cache(max_tokens=64 * 16, max_slots=4)
+        poison_free_pages(cache)
+        seqs = [random_tokens(V, n, 800 + n) for n in (150, 90, 33)]
+        refs = [p.logits(t, rows=range(len(t) - 25, len(t))) for t in seqs]
+        slots = [cache.alloc_slot() for _ in seqs]
+        m.step(cache, [StepRequest(s, t[:-25], []) for s, t in zip(slots, seqs)])
+        got = m.step(cache, [StepRequest(s, t[-25:-20], range(5)) for s, t in zip(slots, seqs)])       # 15 tokens a step
+        assert_logits_close(got.cpu(), torch.cat([r[:5] for r in refs]), "bfloat16", f"{name} fused norm, chunks")
+        for k in range(20):
+            got = m.step(cache, [StepRequest(s, [t[len(t) - 20 + k]], [0]) for s, t in zip(slots, seqs)])
+            assert_logits_close(got.cpu(), torch.stack([r[5 + k] for r in refs]), "bfloat16", f"{name} fused norm, step {k}")
+    finally:
+        m.options.fused_norm = False
+
+
+@pytest.mark.parametrize("name", ["7B", "0.5B"])
 def test_real_widths_device_loop_follows_the_plain_loop(name, tmp_path_factory):
     """The replayed greedy loop (graph per step, ids fed back on the device) at real widths: its tokens are the
     plain loop's up to the first near tie of bfloat16."""

@@ -103,6 +103,47 @@ def test_weights_as_rows(M, N, K):
     tc.check_status(DEV)
 
 
+@pytest.mark.parametrize("M,N,K,splits,bias", [(1, 256, 320, 1, False), (8, 3584, 18944, 10, False), (37, 896, 4864, 5, True),
+                                               (100, 1000, 512, 2, True), (128, 3584, 3584, 8, False), (16, 5120, 13824, 7, False)])
+def test_fused_residual_update_and_norm_preparation(M, N, K, splits, bias):
+    """The product whose split that finishes last adds all partial sums into the 32-bit stream and leaves
+    stream * norm weight and the tiles' sums of squares; then the products that finish the norm by scaling their
+    output rows.  Against float64: the stream, the RMS, and y = rmsnorm(stream) * weight through each epilogue."""
+    from rocmforge_b200.kernels import tensor_core as tc
+    eps = 1e-5
+    x, w = rnd(M, K, seed=1), rnd(N, K, seed=2, scale=0.05)
+    b = rnd(N, seed=3, dt=torch.float32) if bias else None
+    nw = (1.0 + 0.3 * rnd(N, seed=4, dt=torch.float32))
+    h0 = rnd(M, N, seed=5, dt=torch.float32, scale=2.0)
+    want_h = h0.double() + x.double() @ w.double().t() + (b.double() if bias else 0.0)
+    outs = []
+    for call in range(2):                      # the second launch finds the tile counters as the first one left them
+        h = h0.clone()
+        normed, ss = tc.gemm_tc_skinny_resnorm(x, w, b, h, nw, splits=splits)
+        close(h, want_h, "stream after the update")
+        close(normed, want_h * nw.double(), "stream * norm weight")
+        assert tuple(ss.shape) == ((N + 127) // 128, M)
+        close(ss.sum(0), (want_h ** 2).sum(1), "sum of squares")
+        outs.append((h, normed, ss))
+    assert all(torch.equal(a, c) for a, c in zip(outs[0], outs[1])), "the result depends on which split came last"
+    h, normed, ss = outs[1]
+    # the finished norm, from the bfloat16 operand that the next product really reads
+    y = normed.double() * torch.rsqrt((want_h ** 2).mean(1, keepdim=True) + eps)
+    close((y.float()).bfloat16(), want_h * torch.rsqrt((want_h ** 2).mean(1, keepdim=True) + eps) * nw.double(), "finished norm")
+    w2, b2 = rnd(384, N, seed=6, scale=0.05), rnd(384, seed=7, dt=torch.float32)
+    ref = y @ w2.double().t()
+    close(tc.gemm_tc_skinny(normed, w2, mode=tc.F32, row_ss=(ss, eps)), ref, "rows scaled, f32")
+    close(tc.gemm_tc_skinny(normed, w2, b2, mode=tc.STORE, row_ss=(ss, eps)), ref + b2.double(), "rows scaled, bias after")
+    close(tc.gemm_tc_skinny(normed, w2, mode=tc.SWIGLU, row_ss=(ss, eps)), P.silu(ref[:, 0::2]) * ref[:, 1::2], "rows scaled, swiglu")
+    parts = tc.gemm_tc_skinny(normed, w2, mode=tc.PARTIAL, splits=2, row_ss=(ss, eps))
+    close(parts.double().sum(0).float(), ref, "rows scaled, partial sums")
+    acc = rnd(M, 384, seed=8, dt=torch.float32)
+    want = acc.double() + ref
+    tc.gemm_tc_skinny(normed, w2, mode=tc.RESIDUAL, out=acc, row_ss=(ss, eps))
+    close(acc, want, "rows scaled, residual")
+    tc.check_status(DEV)
+
+
 def test_split_rule_depends_on_the_weight_only():
     from rocmforge_b200.kernels import tensor_core as tc
     assert tc.split_k_for(3584, 3584) > 1 and tc.split_k_for(152064, 3584) == 1
