@@ -56,6 +56,8 @@ def peaks():
             out["bf16_tflops"] = float(raw.get("bf16_tflops", out["bf16_tflops"]))
             if "bf16_tflops_sustained" in raw:
                 out["bf16_tflops_sustained"] = float(raw["bf16_tflops_sustained"])
+            if "sm_max_mhz" in raw:
+                out["sm_max_mhz"] = float(raw["sm_max_mhz"])
             out["source"] = "measured"
         except Exception:
             pass
@@ -384,7 +386,14 @@ def other_shapes(pk, seed, only=None):
             out[key + "_hbm_frac"] = round(step_bytes(cfg, 64, r["mean_ctx"], elem) / (r["ms_per_step"] / 1e3) / 1e9 / hbm, 4)
             llm = rf.LLM(model, cache_tokens=sum((len(p) + 256 + 80) // 64 * 64 for p in prompts), max_batch=64)
             out[key + "_e2e_tok_s"] = round(e2e_rate(llm, prompts, 128 if elem == 2 else 32)["value"], 1)
-            del llm, model
+            del llm
+            if elem == 4:
+                # the 32-bit products run on the CUDA cores: 148 SMs x 128 lanes x 2 flops at the highest SM clock
+                ffma = 148 * 128 * 2 * pk.get("sm_max_mhz", 1965.0) * 1e6
+                ms = prefill_rate(model, PREFILL_TOKENS, 2, seed + 13)
+                out["qwen0.5b_fp32_prefill2048_tok_s"] = round(PREFILL_TOKENS / (ms / 1e3), 1)
+                out["qwen0.5b_fp32_prefill2048_ffma_frac"] = round(prefill_flops(cfg, PREFILL_TOKENS) / (ms / 1e3) / ffma, 4)
+            del model
             torch.cuda.empty_cache()
     if only in (None, "14b"):
         cfg = Qwen2Config.from_dict(SHAPE_14B)

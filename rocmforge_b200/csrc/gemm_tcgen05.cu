@@ -26,7 +26,10 @@
 
 // ---------------------------------------------------------------- the kernel
 // SWAP = false: map A = X (rows are tokens), map B = W;  SWAP = true: map A = W, map B = X.
-template <int BN, bool SWAP, int STAGES>
+// NORM = true (weights-as-rows only): the variant that applies a deferred norm to its input rows (p.norm.ss_in)
+// and/or finishes the residual update and prepares the next norm (EPI_RESNORM); it needs more registers, so the
+// ordinary products do not carry it.
+template <int BN, bool SWAP, int STAGES, bool NORM = false>
 __global__ void __launch_bounds__(TC_THREADS, SWAP ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p) {
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2;
@@ -39,7 +42,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);     // full[S], empty[S], tmem_full
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
     __shared__ int abort_flag;
-    __shared__ float rstd_s[SWAP ? BN : 1];                    // 1 / RMS of this tile's tokens (deferred norm of the input)
+    __shared__ float rstd_s[NORM ? BN : 1];                    // 1 / RMS of this tile's tokens (deferred norm of the input)
     __shared__ int last_split;
 
     pdl_trigger();
@@ -128,7 +131,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // ---------------- epilogue: four warps, one quarter of the 128 lanes each
         const int quarter = warp & 3;
         pdl_wait();                                      // the output may still be read by the kernel before us
-        if (SWAP && p.norm.ss_in) {
+        if (NORM && p.norm.ss_in) {
             // the input's norm was left unfinished by the product before us: 1 / RMS of each token of this tile, from
             // the tiles' sums of squares in index order
             const int t = threadIdx.x - 64;
@@ -160,7 +163,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const int n = row_a, m0 = tile_b * BN + c0;
                     const float b = (p.bias && n < p.N && p.mode != EPI_RESNORM) ? load_vec(p.bias, p.bias_is_f32, n) : 0.f;
                     if (m0 >= p.M) break;                // the tile's other columns are padding, not tokens
-                    if (p.norm.ss_in) {
+                    if (NORM && p.norm.ss_in) {
 #pragma unroll
                         for (int j = 0; j < CH; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * rstd_s[c0 + j]);
                     }
@@ -196,7 +199,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
             }
         }
-        if (SWAP && p.mode == EPI_RESNORM) {
+        if (NORM && p.mode == EPI_RESNORM) {
             // ---- the split that arrives last at this output tile finishes the residual update and prepares the norm
             __threadfence();                                             // this split's partial sums are visible device-wide
             asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -306,17 +309,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 }
 
 // ---------------------------------------------------------------- host side
-template <int BN, bool SWAP, int STAGES>
+template <int BN, bool SWAP, int STAGES, bool NORM = false>
 static int launch_cfg(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, dim3 grid, cudaStream_t st) {
     constexpr size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + (2 * STAGES + 1) * 8 + 16 + 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, SWAP, STAGES>,
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, SWAP, STAGES, NORM>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    rf_launch(gemm_tc_kernel<BN, SWAP, STAGES>, grid, dim3(TC_THREADS), smem, st, ma, mb, p);
+    rf_launch(gemm_tc_kernel<BN, SWAP, STAGES, NORM>, grid, dim3(TC_THREADS), smem, st, ma, mb, p);
     RF_LAUNCH_CHECK();
     return 0;
 }
@@ -382,6 +385,12 @@ int rf_gemm_tc_skinny_ex(const void* X, int ldx, const void* W, const void* bias
     // start-up and epilogue, and 2 x stages x 16 KB of weight bytes are in flight per SM.  (128 tokens:
     // two CTAs with three 32 KB stages each, 5.09 ms a decode step of the 7B shape; one CTA with six
     // stages 6.46 ms; two tiles of 64 tokens sharing the weight tile through L2 5.65 ms.)
+    if (ss_in || mode == EPI_RESNORM) {
+        if (bn == 16) return launch_cfg<16, true, 6, true>(ma, mb, p, grid, st);
+        if (bn == 32) return launch_cfg<32, true, 5, true>(ma, mb, p, grid, st);
+        if (bn == 64) return launch_cfg<64, true, 4, true>(ma, mb, p, grid, st);
+        return launch_cfg<128, true, 3, true>(ma, mb, p, grid, st);
+    }
     if (bn == 16) return launch_cfg<16, true, 6>(ma, mb, p, grid, st);
     if (bn == 32) return launch_cfg<32, true, 5>(ma, mb, p, grid, st);
     if (bn == 64) return launch_cfg<64, true, 4>(ma, mb, p, grid, st);

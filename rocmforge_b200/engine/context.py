@@ -112,6 +112,11 @@ class StepContext:
             stream.flush()
             tc.gemm_tc(x, w, bias, mode=tc.RESIDUAL, out=stream.h)
             return
+        if x.shape[0] <= tc.SKINNY_MAX_TOKENS and bias is None:
+            splits = kernels.split_k_for_simt(w.shape[0], w.shape[1])
+            if splits > 1:                           # few tokens: K ranges in parallel, summed by the next norm
+                stream.add_pending(kernels.gemm_simt(x, w, splits=splits))
+                return
         stream.flush()
         kernels.gemm_simt(x, w, bias, out=stream.h, accumulate=True)
 
@@ -151,6 +156,13 @@ class StepContext:
                                              **rope)
         if row_ss is not None:
             y = ScaledRows(y, row_ss[0], row_ss[1], w.shape[1])
+        elif y.shape[0] <= tc.SKINNY_MAX_TOKENS and not self._tensor_cores(y, w, tc.STORE):
+            splits = kernels.split_k_for_simt(w.shape[0], w.shape[1])
+            if splits > 1:                           # CUDA-core product of few tokens: the same scheme
+                parts = kernels.gemm_simt(y, w, splits=splits)
+                return kernels.rope_kv_write(parts, mixer.n_heads, mixer.n_kv_heads, mixer.head_dim,
+                                             mixer.position.inv_freq, bias=bias, compute_dtype=self.compute_dtype,
+                                             **rope)
         qkv = self.matmul(y, w, bias)
         return kernels.rope_kv_write(qkv, mixer.n_heads, mixer.n_kv_heads, mixer.head_dim,
                                      mixer.position.inv_freq, **rope)

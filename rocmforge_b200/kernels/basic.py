@@ -136,11 +136,25 @@ def swiglu(gu: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     return out
 
 
+def split_k_for_simt(N: int, K: int, sm_count: int = 148) -> int:
+    """K splits of a CUDA-core product of few tokens, from N and K alone (never from the batch): about two CTAs
+    per SM, every split at least 4 blocks of 16."""
+    tiles = (N + 127) // 128
+    kb = (K + 15) // 16
+    if tiles >= 2 * sm_count or kb < 8:
+        return 1
+    splits = max(1, min((2 * sm_count) // tiles, kb // 4))
+    per = (kb + splits - 1) // splits
+    return (kb + per - 1) // per                   # no empty split
+
+
 def gemm_simt(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, *,
-              out: torch.Tensor | None = None, out_f32: bool = False, accumulate: bool = False) -> torch.Tensor:
+              out: torch.Tensor | None = None, out_f32: bool = False, accumulate: bool = False,
+              splits: int = 0) -> torch.Tensor:
     """y = x @ w.T (+ bias) on CUDA cores with 32-bit sums.
 
-    out_f32: the result is float32 whatever the inputs; accumulate: added into ``out`` (float32).
+    out_f32: the result is float32 whatever the inputs; accumulate: added into ``out`` (float32);
+    splits >= 1: the result is the float32 stack [splits, M, N] of partial sums over K ranges (no bias).
     """
     need_cuda(x, w, bias, out)
     need(x.dim() == 2 and w.dim() == 2 and x.dtype == w.dtype and x.stride(1) == 1 and w.is_contiguous(),
@@ -150,16 +164,22 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None
     need(w.shape[1] == K, f"gemm: inner sizes differ ({K} vs {w.shape[1]})")
     if bias is not None:
         need(bias.shape == (N,) and bias.dtype in (torch.float32, torch.bfloat16), "gemm: bias must be [N]")
+    f = _f("gemm_simt", "rf_gemm_simt", c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
+           c_int, c_int, c_int, c_int, c_int, c_void_p)
+    if splits >= 1:
+        need(not accumulate and out is None and bias is None, "gemm: partial sums take no bias and no output tensor")
+        out = torch.empty((splits, M, N), dtype=torch.float32, device=x.device)
+        check(f(dtype_code(x.dtype), ptr(x), ptr(w), ptr(None), 0, ptr(out), M, N, K, x.stride(0), N, 3, splits, stream()),
+              f"gemm_simt ({M}x{N}x{K}, {splits} partial sums)")
+        return out
     mode = 2 if accumulate else (1 if out_f32 else 0)
     odt = torch.float32 if mode else x.dtype
     if out is None:
         need(not accumulate, "gemm: accumulate needs an output tensor")
         out = torch.empty((M, N), dtype=odt, device=x.device)
     need(out.shape == (M, N) and out.dtype == odt and out.stride(1) == 1, "gemm: output has the wrong shape or dtype")
-    f = _f("gemm_simt", "rf_gemm_simt", c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
-           c_int, c_int, c_int, c_int, c_void_p)
     check(f(dtype_code(x.dtype), ptr(x), ptr(w), ptr(bias), int(bias is not None and bias.dtype == torch.float32),
-            ptr(out), M, N, K, x.stride(0), out.stride(0), mode, stream()), f"gemm_simt ({M}x{N}x{K})")
+            ptr(out), M, N, K, x.stride(0), out.stride(0), mode, 1, stream()), f"gemm_simt ({M}x{N}x{K})")
     return out
 
 

@@ -69,7 +69,8 @@ def test_add_rmsnorm(dt, H):
 
 
 @pytest.mark.parametrize("dt", DTS)
-@pytest.mark.parametrize("M,N,K", [(1, 7, 5), (5, 130, 33), (65, 64, 64), (130, 200, 257), (3, 1000, 3584)])
+@pytest.mark.parametrize("M,N,K", [(1, 7, 5), (5, 130, 33), (65, 64, 64), (130, 200, 257), (3, 1000, 3584), (17, 896, 4864),
+                                   (40, 300, 1000), (300, 1152, 896)])
 def test_gemm_simt(dt, M, N, K):
     from rocmforge_b200 import kernels
     x, w = rnd(M, K, dt=dt, seed=1), rnd(N, K, dt=dt, seed=2, scale=0.1)
@@ -86,10 +87,22 @@ def test_gemm_simt(dt, M, N, K):
     acc0 = acc.clone()
     kernels.gemm_simt(x, w, out=acc, accumulate=True)
     torch.testing.assert_close(acc.double(), acc0.double() + ref, atol=1e-4, rtol=1e-5)
-    # a row's result does not depend on the other rows of the batch
+    # a row's result does not depend on the other rows of the batch, whatever tile height their number selects
     if M > 1:
         alone = kernels.gemm_simt(x[M - 1:M].contiguous(), w, out_f32=True)
         assert torch.equal(alone, kernels.gemm_simt(x, w, out_f32=True)[M - 1:M])
+    # K ranges as partial sums: each split alone is the product over its range; their number follows N and K only
+    kb = (K + 15) // 16
+    for splits in {kernels.split_k_for_simt(N, K), (kb + (kb + 2) // 3 - 1) // ((kb + 2) // 3)}:       # the rule's, and about 3
+        parts = kernels.gemm_simt(x, w, splits=splits)
+        assert tuple(parts.shape) == (splits, M, N) and parts.dtype == torch.float32
+        torch.testing.assert_close(parts.double().sum(0), ref, atol=1e-4, rtol=1e-5)
+        per = ((K + 15) // 16 + splits - 1) // splits * 16
+        for s in range(splits):
+            lo, hi = s * per, min(K, (s + 1) * per)
+            torch.testing.assert_close(parts[s].double(), x[:, lo:hi].double() @ w[:, lo:hi].double().t(), atol=1e-4, rtol=1e-5)
+        if M > 1:
+            assert torch.equal(kernels.gemm_simt(x[M - 1:M].contiguous(), w, splits=splits)[:, 0], parts[:, M - 1])
 
 
 @pytest.mark.parametrize("dt", DTS)
