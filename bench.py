@@ -335,7 +335,7 @@ def e2e_rate(llm, prompts, steps, temperature=0.0, top_p=1.0):
     n = len(stamps) - 1
     dt = stamps[-1] - stamps[0]
     from rocmforge_b200.engine.batch import StepBatch
-    h2d = StepBatch.layout(batch, batch, batch)[1] * 4 + batch * 4 / 64.0     # descriptor + a block-table entry per 64 steps
+    h2d = StepBatch.layout(batch, batch, batch, decode_extras=True)[1] * 4 + batch * 4 / 64.0     # descriptor + a block-table entry per 64 steps
     return {"value": batch * n / dt, "unit": "tok/s", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": batch * 4,
             "steps": n, "generated": sum(len(r.tokens) for r in out)}
 

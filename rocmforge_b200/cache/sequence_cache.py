@@ -190,6 +190,7 @@ class SequenceCache:
         # grows whenever a slot is handed out or given back: whoever prepared a step ahead of time (pages taken,
         # descriptor built) compares it and drops what it prepared when the set of sequences has changed
         self.epoch = 0
+        self.generations = np.zeros((self.max_slots,), dtype=np.int64)      # how often each slot was handed out
 
         by_key: Dict[tuple, List[int]] = {}
         self._kv_request: Dict[tuple, KVRequest] = {}
@@ -217,6 +218,7 @@ class SequenceCache:
     def alloc_slot(self) -> int:
         slot = self.slots.take()
         self.epoch += 1
+        self.generations[slot] += 1
         self.lengths[slot] = 0
         for view in self.states.values():
             for t in view.tensors.values():
@@ -231,6 +233,11 @@ class SequenceCache:
         self.lengths[slot] = 0
         self.slots.give_back(slot)
         self.epoch += 1
+
+    def generation(self, slot: int) -> int:
+        """Which holder of the slot this is (it grows when the slot is handed out): a step prepared for a slot belongs
+        to one holder, and the number of a freed slot comes back with the next sequence."""
+        return int(self.generations[slot])
 
     def length(self, slot: int) -> int:
         return int(self.lengths[slot])

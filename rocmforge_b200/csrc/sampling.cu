@@ -491,6 +491,22 @@ __global__ void advance_decode_kernel(int* tokens, int* tok_pos, int* seq_start,
     }
 }
 
+// tokens[i] = ids[row_map[i]]: the tokens of a step that is launched before the host has seen the ids the step
+// before it sampled (the batch may have shrunk in between: row_map names each sequence's row in that step).
+__global__ void gather_tokens_kernel(int* tokens, const int* ids, const int* row_map, int B) {
+    pdl_trigger();
+    pdl_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < B) tokens[i] = ids[row_map[i]];
+}
+
+extern "C" int rf_gather_tokens(int* tokens, const int* ids, const int* row_map, int B, cudaStream_t st) {
+    if (B <= 0) return 0;
+    rf_launch(gather_tokens_kernel, dim3((B + 127) / 128), dim3(128), 0, st, tokens, ids, row_map, B);
+    RF_LAUNCH_CHECK();
+    return 0;
+}
+
 extern "C" int rf_advance_decode(int* tokens, int* tok_pos, int* seq_start, const int* sampled, int B,
                                  cudaStream_t st) {
     if (B <= 0) return 0;

@@ -78,10 +78,14 @@ class StepBatch:
 
     # layout of the packed descriptor, in int32 elements
     @staticmethod
-    def layout(T: int, B: int, R: int, n_tiles: int = 0, n_tiles128: int = 0):
+    def layout(T: int, B: int, R: int, n_tiles: int = 0, n_tiles128: int = 0, decode_extras: bool = False):
+        """``decode_extras``: two more arrays for decode steps that a runner launches ahead of the host: the rows'
+        64-bit sampling seeds (two words each) and each sequence's row in the step before."""
         names = [("tokens", T), ("tok_seq", T), ("tok_pos", T), ("seq_slot", B), ("seq_start", B),
                  ("seq_nnew", B), ("cu_q", B + 1), ("want_rows", R), ("q_tiles", 2 * n_tiles),
                  ("q_tiles128", 2 * n_tiles128)]
+        if decode_extras:
+            names += [("seeds", 2 * B), ("row_map", B)]
         off, out = 0, {}
         for name, n in names:
             out[name] = (off, n)
@@ -148,6 +152,6 @@ class DeviceDescriptor:
             self._done.record()
             self._busy = True
 
-    def views(self, T: int, B: int, R: int, n_tiles: int = 0, n_tiles128: int = 0):
-        lay, _ = StepBatch.layout(T, B, R, n_tiles, n_tiles128)
+    def views(self, T: int, B: int, R: int, n_tiles: int = 0, n_tiles128: int = 0, decode_extras: bool = False):
+        lay, _ = StepBatch.layout(T, B, R, n_tiles, n_tiles128, decode_extras)
         return {name: self.dev[o:o + n] for name, (o, n) in lay.items()}

@@ -46,9 +46,14 @@ class StepEngine:
     def free_slot(self, slot: int) -> None:
         raise NotImplementedError
 
+    wants_final_hint = False
+
     def run(self, slots: Sequence[int], tokens: Sequence[Sequence[int]], requests: Sequence[int],
             draws: Sequence[int], sampling: SamplingParams) -> List[int]:
-        """Step the given tokens of each slot and sample one next token per slot."""
+        """Step the given tokens of each slot and sample one next token per slot.
+
+        An engine that sets ``wants_final_hint`` also gets ``final=`` (the tokens sampled by this call are the last
+        ones of all its sequences whatever they are): it may then spare itself work it would do ahead of time."""
         raise NotImplementedError
 
 
@@ -116,7 +121,10 @@ def _run_batch(engine, batch, prompts, results, max_new_tokens, sampling, stop, 
             if not still:
                 return
             active = still
-            nxt = engine.run([slot[i] for i in active], feed, active, [draws[i] for i in active], sampling)
+            hint = {}
+            if engine.wants_final_hint:
+                hint["final"] = all(len(results[i].tokens) + 1 >= max_new_tokens for i in active)
+            nxt = engine.run([slot[i] for i in active], feed, active, [draws[i] for i in active], sampling, **hint)
             for i in active:
                 pos[i] += 1
     finally:

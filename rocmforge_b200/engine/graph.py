@@ -41,12 +41,18 @@ class DecodeRunner:
         self.sampler = DeviceSampler(model.device)
         self.replays = 0
         self._ready = None             # (slots, starts, packed descriptor without token ids, longest, cache epoch) of the next step
+        self._flight = None            # a step launched before the host saw the ids of the step before it (see step_ids)
+        self._templates: Dict[tuple, np.ndarray] = {}
+        self._host_ids = []            # pinned buffers for sampled ids, used in turn
+        self._turn = 0
+        self.launched_ahead = 0        # steps that were launched ahead and served a call
+        self.discarded = 0             # ... and that no call asked for
 
     @staticmethod
     def descriptor_words(max_batch: int) -> int:
         """int32 words of the largest packed decode descriptor (one token, one wanted row and one tile of each
         kind per sequence)."""
-        return StepBatch.layout(max_batch, max_batch, max_batch, max_batch, max_batch)[1]
+        return StepBatch.layout(max_batch, max_batch, max_batch, max_batch, max_batch, decode_extras=True)[1]
 
     @staticmethod
     def length_bucket(longest: int) -> int:
@@ -179,7 +185,161 @@ class DecodeRunner:
         self.cache.commit(slots, [steps] * B)
         return out, start, end, cap.launches
 
-    def run(self, slots, tokens, requests, draws, sampling) -> torch.Tensor:
-        if sampling.greedy:
-            return self.logits(slots, tokens, greedy=True)
-        return self.sampler.sample(self.logits(slots, tokens), sampling, requests, draws)
+    # ---------------------------------------------------------------- sampled ids, one step ahead of the host
+    def _capture_ids(self, B: int, bound: int, sampling) -> _Captured:
+        """The step's graph with the sampler inside: forward, then argmax or the seeded draw (seeds from the descriptor)."""
+        from .. import kernels
+        ctx = self._context(B, bound)
+        seeds = self.desc.views(B, B, B, decode_extras=True)["seeds"].view(torch.int64)
+        ids = torch.zeros((B,), dtype=torch.int32, device=self.model.device)
+
+        def body():
+            logits = self.model.forward(ctx, self.cache)
+            if sampling.greedy:
+                kernels.argmax(logits, out=ids)
+            else:
+                kernels.sample(logits, sampling.temperature, sampling.top_p, sampling.top_k, seeds, out=ids)
+            return logits
+        side = torch.cuda.Stream(device=self.model.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            body()                                         # warm-up: loads modules, sizes the allocator
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            logits = body()
+        cap = _Captured(graph, logits)
+        cap.ids = ids
+        return cap
+
+    def _pinned(self, B: int):
+        if not self._host_ids:
+            for _ in range(3):
+                t = torch.empty((self.max_batch,), dtype=torch.int32).pin_memory()
+                self._host_ids.append((t, t.numpy(), torch.cuda.Event()))
+        self._turn = (self._turn + 1) % len(self._host_ids)
+        return self._host_ids[self._turn]
+
+    def _launch(self, slots, starts, sampling, requests, draws, tokens=None, ids_from=None, row_map=None):
+        """Enqueue one decode step of ``slots`` at positions ``starts``: descriptor upload, the tokens (from the host, or
+        gathered on the device from the ids of the step before), graph replay, copy of the sampled ids to pinned memory."""
+        from .. import kernels
+        from ..sampling.params import as_int64, draw_seed
+        B = len(slots)
+        key = tuple(slots)
+        lay, total = StepBatch.layout(B, B, B, decode_extras=True)
+        packed = self._templates.get(key)
+        if packed is None:
+            if len(self._templates) > 256:
+                self._templates.clear()
+            packed = np.zeros((total,), dtype=np.int32)
+            for name, arr in (("tok_seq", np.arange(B)), ("seq_slot", np.asarray(slots)), ("seq_nnew", np.ones(B)),
+                              ("cu_q", np.arange(B + 1)), ("want_rows", np.arange(B))):
+                o, n = lay[name]
+                packed[o:o + n] = arr
+            self._templates[key] = packed
+        for name in ("tok_pos", "seq_start"):
+            o, n = lay[name]
+            packed[o:o + n] = starts
+        if tokens is not None:
+            packed[:B] = tokens
+        if not sampling.greedy:
+            o, n = lay["seeds"]
+            packed[o:o + n].view(np.int64)[:] = [as_int64(draw_seed(sampling.seed, r, d)) for r, d in zip(requests, draws)]
+        if row_map is not None:
+            o, n = lay["row_map"]
+            packed[o:o + n] = row_map
+        self.desc.upload(packed)
+        if tokens is None:
+            views = self.desc.views(B, B, B, decode_extras=True)
+            kernels.gather_tokens(views["tokens"], ids_from, views["row_map"])
+        gkey = ("ids", B, self.length_bucket(max(starts) + 1), sampling.greedy,
+                None if sampling.greedy else (sampling.temperature, sampling.top_p, sampling.top_k))
+        cap = self.graphs.get(gkey)
+        if cap is None:
+            cap = self.graphs[gkey] = self._capture_ids(B, gkey[2], sampling)
+            self.desc.upload(packed)                       # capture ran the step: put the descriptor back as it was
+            if tokens is None:
+                kernels.gather_tokens(views["tokens"], ids_from, views["row_map"])
+        cap.graph.replay()
+        self.replays += 1
+        pinned, host, event = self._pinned(B)
+        pinned[:B].copy_(cap.ids, non_blocking=True)
+        event.record()
+        return dict(slots=list(slots), gens=[self.cache.generation(s) for s in slots], starts=list(starts), cap=cap,
+                    host=host, event=event, sampling=sampling, requests=list(requests), draws=list(draws), B=B)
+
+    def step_ids(self, slots: Sequence[int], tokens: Sequence[int], sampling, requests: Sequence[int],
+                 draws: Sequence[int], more: bool = True):
+        """Step one token per slot and sample the next; returns the sampled ids as a list.
+
+        The device runs one step ahead of the host.  Before this call waits for its own ids it launches the next
+        step of the same sequences, whose tokens the device takes from this step's ids itself (``more`` = the
+        caller will come back unless sequences stop).  The next call then finds its step already running: it
+        checks that the caller passes the ids it was given, waits and returns.  Sequences that ended in between
+        are simply left out (their rows of the step that ran ahead are ignored, the rows of the others are as
+        valid as ever: a row does not depend on its neighbours).  If the call asks for anything else (other
+        tokens, other sequences, other sampling) the step that ran ahead is dropped and its pages given back.
+        """
+        slots = [int(s) for s in slots]
+        B = len(slots)
+        if B > self.max_batch:
+            raise ValueError(f"a decode batch of {B} exceeds the runner's limit of {self.max_batch}")
+        self._ready = None
+        cache = self.cache
+        fl, self._flight = self._flight, None
+        rows = None
+        if fl is not None:
+            where = {s: i for i, s in enumerate(fl["slots"])}
+            rows = [where.get(s, -1) for s in slots]
+            fits = (fl["sampling"] == sampling and all(r >= 0 for r in rows)
+                    and all(cache.slots.is_held(s) and cache.generation(s) == fl["gens"][r] and cache.length(s) == fl["starts"][r]
+                            and int(t) == fl["fed"][r] and rq == fl["requests"][r] and d == fl["draws"][r]
+                            for s, r, t, rq, d in zip(slots, rows, tokens, requests, draws)))
+            if not fits:
+                self.discarded += 1
+                cache.rollback([s for s, g in zip(fl["slots"], fl["gens"])
+                                if cache.slots.is_held(s) and cache.generation(s) == g])
+                fl = rows = None
+        if fl is None:
+            toks = np.asarray(tokens, dtype=np.int64)
+            if ((toks < 0) | (toks >= self.model.spec.vocab_size)).any():
+                raise BatchError("a token id is outside the vocabulary")
+            starts = [cache.length(s) for s in slots]
+            cache.prepare(slots, [1] * B)
+            try:
+                fl = self._launch(slots, starts, sampling, requests, draws, tokens=toks)
+            except BaseException:
+                cache.rollback(slots)
+                raise
+            rows = list(range(B))
+        else:
+            self.launched_ahead += 1
+        cache.commit(slots, [1] * B)                       # the step is under way for these sequences
+        if more:
+            # the next step of the same sequences, before the host knows this step's ids
+            try:
+                cache.prepare(slots, [1] * B)
+            except CacheError:
+                pass                                       # no room for a further token: the caller will learn it if it comes back
+            else:
+                try:
+                    self._flight = self._launch(slots, [cache.length(s) for s in slots], sampling, requests,
+                                                [d + 1 for d in draws], ids_from=fl["cap"].ids, row_map=rows)
+                except BaseException:
+                    cache.rollback(slots)
+                    raise
+        fl["event"].synchronize()
+        got = fl["host"][:fl["B"]].tolist()
+        ids = [got[r] for r in rows]
+        if self._flight is not None:
+            self._flight["fed"] = ids                      # what the step that runs ahead was fed, row by row
+        return ids
+
+    def drop_ahead(self) -> None:
+        """Forget a step that was launched ahead (its pages go back); the device finishes it unobserved."""
+        fl, self._flight = self._flight, None
+        if fl is not None:
+            self.discarded += 1
+            self.cache.rollback([s for s, g in zip(fl["slots"], fl["gens"])
+                                 if self.cache.slots.is_held(s) and self.cache.generation(s) == g])

@@ -13,6 +13,8 @@ from .generate import StepEngine
 
 
 class ModelEngine(StepEngine):
+    wants_final_hint = True          # ``run(..., final=True)``: no sequence of the call will be stepped again
+
     def __init__(self, model, cache, max_batch: int = 64):
         self.model = model
         self.cache = cache
@@ -58,15 +60,17 @@ class ModelEngine(StepEngine):
         if self.cache.live_slots == 0:     # a batch has ended: did any kernel give up waiting?
             kernels.tensor_core.check_status(self.model.device)
 
-    def run(self, slots, tokens, requests, draws, sampling: SamplingParams) -> List[int]:
+    def run(self, slots, tokens, requests, draws, sampling: SamplingParams, final: bool = False) -> List[int]:
         decode = all(len(t) == 1 for t in tokens)
         if decode and self.decode_runner is not None:
-            out = self.decode_runner.run(slots, [t[0] for t in tokens], requests, draws, sampling)
+            # replayed from a graph with the sampler inside, one step ahead of the host
+            ids = self.decode_runner.step_ids(slots, [t[0] for t in tokens], sampling, requests, draws, more=not final)
         else:
+            if self.decode_runner is not None:
+                self.decode_runner.drop_ahead()        # a step launched for sequences that all stopped
             reqs = [StepRequest(s, t, [len(t) - 1]) for s, t in zip(slots, tokens)]
             logits = self.model.step(self.cache, reqs)
-            out = self.sampler.sample(logits, sampling, requests, draws)
-        ids = self._to_host(out)
+            ids = self._to_host(self.sampler.sample(logits, sampling, requests, draws))
         self._calls += 1
         if self._calls % 64 == 0:          # a separate small read: not on every step
             kernels.tensor_core.check_status(self.model.device)

@@ -250,6 +250,16 @@ def advance_decode(tokens, tok_pos, seq_start, sampled) -> None:
     check(f(ptr(tokens), ptr(tok_pos), ptr(seq_start), ptr(sampled), B, stream()), "advance_decode")
 
 
+def gather_tokens(tokens, ids, row_map) -> None:
+    """tokens[i] = ids[row_map[i]] on the device (all int32)."""
+    need_cuda(tokens, ids, row_map)
+    B = tokens.shape[0]
+    need(all(t.dtype == torch.int32 and t.dim() == 1 for t in (tokens, ids, row_map)) and row_map.shape[0] == B,
+         "gather_tokens: int32 vectors, one map entry per token")
+    f = _f("sampling", "rf_gather_tokens", c_void_p, c_void_p, c_void_p, c_int, c_void_p)
+    check(f(ptr(tokens), ptr(ids), ptr(row_map), B, stream()), "gather_tokens")
+
+
 def attention_decode_supported(n_heads: int, n_kv_heads: int, head_dim: int) -> bool:
     f = _f("attention_decode", "rf_attention_decode_supported", c_int, c_int, c_int)
     return bool(f(n_heads, n_kv_heads, head_dim))

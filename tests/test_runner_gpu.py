@@ -96,3 +96,79 @@ def test_a_step_prepared_ahead_is_dropped_when_slots_change(folders, dtype):
     for i in range(100, 120):
         got = m.step(cache, [StepRequest(keep, [keep_toks[i]], [0])]).cpu()
         assert_logits_close(got, ref[i:i + 1], dtype, f"the third sequence at {i}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_launched_ahead_of_the_host_follow_the_plain_loop(folders, dtype):
+    """``step_ids`` keeps the device one step ahead: the next step's tokens are gathered on the device from the ids
+    the host has not seen yet.  Sequences stop at different times (their rows of the step that ran ahead are
+    ignored, the others go on without a relaunch), one call passes other tokens than it was given (the step that ran
+    ahead is dropped and its page given back), and a slot is freed and refilled between two calls."""
+    from rocmforge_b200 import SamplingParams, StepRequest, kernels
+    from rocmforge_b200.engine.graph import DecodeRunner
+    m, p = engine(folders, "D", dtype), plain(folders, "D", dtype)
+    V = CONFIGS["D"]["vocab_size"]
+    greedy = SamplingParams(temperature=0.0)
+    cache = m.new_cache(max_tokens=64 * 24, max_slots=4)
+    poison_free_pages(cache)
+    runner = DecodeRunner(m, cache)
+    prompts = [random_tokens(V, n, 950 + n) for n in (62, 127, 5)]
+    budget = [9, 30, 20]                                   # tokens each request may take: they stop at different times
+    want = [S.generate(lambda t: p.logits(t)[-1], pr, max_tokens=b)[0] for pr, b in zip(prompts, budget)]
+    slots = [cache.alloc_slot() for _ in prompts]
+    first = kernels.argmax(m.step(cache, [StepRequest(s, t, [len(t) - 1]) for s, t in zip(slots, prompts)])).cpu().tolist()
+    got = [[f] for f in first]
+    live = [0, 1, 2]
+    while True:
+        for i in [i for i in live if len(got[i]) >= budget[i]]:
+            cache.free_slot(slots[i])
+            live.remove(i)
+        if not live:
+            break
+        poison_free_pages(cache)
+        ids = runner.step_ids([slots[i] for i in live], [got[i][-1] for i in live], greedy, live,
+                              [len(got[i]) for i in live])             # request numbers and the count of each one's draws
+        for i, t in zip(live, ids):
+            got[i].append(t)
+    assert runner.launched_ahead >= 20, "the steps did not run ahead of the host"
+    for i in range(3):
+        if dtype == "float32":
+            assert got[i] == want[i], f"request {i}"
+        else:
+            check_tokens_up_to_near_ties(p, prompts[i], got[i], want[i])
+    assert cache.live_slots == 0 and all(f == cache.n_pages for f in cache.free_pages()), "a page taken ahead was lost"
+
+    # a caller that does not pass on what it was given: the step that ran ahead must not be used
+    toks = random_tokens(V, 90, 77)
+    ref = p.logits(toks)
+    s = cache.alloc_slot()
+    m.step(cache, [StepRequest(s, toks[:63], [])])
+    before = runner.discarded
+    for i in range(63, 90):                                # teacher forcing: the model's own pick is ignored
+        runner.step_ids([s], [toks[i]], greedy, [0], [i])
+        assert cache.length(s) == i + 1
+    assert runner.discarded > before
+    got_logits = m.step(cache, [StepRequest(s, [toks[0]], [0])])          # one more step reads the whole cache
+    again = p.logits(toks + [toks[0]])
+    assert_logits_close(got_logits.cpu(), again[-1:], dtype, "the cache after dropped steps")
+    cache.free_slot(s)
+    runner.drop_ahead()
+    assert all(f == cache.n_pages for f in cache.free_pages())
+
+
+def test_sampled_steps_inside_the_graph_follow_the_plain_sampler(folders):
+    """Temperature, top-p and top-k sampling replayed inside the step's graph, seeds travelling with the descriptor:
+    the same tokens as the plain sampler, request by request, while the batch shrinks."""
+    import rocmforge_b200 as rf
+    p = plain(folders, "B", "float32")
+    llm = rf.LLM(folders("B", "float32"), dtype="float32")
+    prompts = [random_tokens(384, n, 160 + n) for n in (3, 20, 41, 9)]
+    for kw in (dict(temperature=0.8, top_p=1.0), dict(temperature=1.1, top_p=0.9, top_k=30)):
+        out = llm.generate(prompts, max_tokens=25, seed=5, stop_token_ids=[7, 11, 13], **kw)
+        for i, (pr, r) in enumerate(zip(prompts, out)):
+            want, reason = S.generate(lambda t: p.logits(t)[-1].float(), pr, max_tokens=25, seed=5, request=i,
+                                      stop_ids=(7, 11, 13), top_k=kw.get("top_k", 0), temperature=kw["temperature"],
+                                      top_p=kw["top_p"])
+            assert r.tokens == want and r.reason == reason, f"request {i} with {kw}"
+    assert llm.engine.decode_runner.launched_ahead > 0
+    assert llm.cache.live_slots == 0 and all(f == llm.cache.n_pages for f in llm.cache.free_pages())
