@@ -154,7 +154,8 @@ __global__ void rope_kv_write_kernel(const void* __restrict__ src, int row_strid
                                      const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                                      const int* __restrict__ seq_slot,
                                      const int* __restrict__ block_table, int max_pages,
-                                     T* __restrict__ k_pages, T* __restrict__ v_pages, int write_kv) {
+                                     T* __restrict__ k_pages, T* __restrict__ v_pages, int write_kv,
+                                     int rot_dim, int interleaved) {
     // grid: (token, block of pairs).  Pair index space: nh + nkv rotated heads, then nkv value heads,
     // hd/2 pairs each (a value "pair" is two neighbouring elements, copied).
     // Position, slot, page, frequency, bias and the angle's sine and cosine do not depend on the kernel
@@ -169,9 +170,16 @@ __global__ void rope_kv_write_kernel(const void* __restrict__ src, int row_strid
     const int head = idx / half, i = idx - head * half;
     if (head >= nh && !write_kv) return;
     const int pos = tok_pos[t];
-    const bool rotated = head < nh + nkv;
-    const int col0 = rotated ? head * hd + i : head * hd + 2 * i;
-    const int col1 = rotated ? col0 + half : col0 + 1;
+    // which two elements of the head this pair is, and whether they turn: the first rot_dim elements of a query or
+    // key head are rotated, as pairs (i, i + rot_dim/2) or (2i, 2i+1); the rest, and values, pass through
+    const int rh = rot_dim >> 1;
+    bool rotated = head < nh + nkv;
+    int e0, e1;
+    if (rotated && interleaved) { e0 = 2 * i; e1 = e0 + 1; rotated = e0 < rot_dim; }
+    else if (rotated && i < rh) { e0 = i; e1 = i + rh; }
+    else if (rotated) { e0 = rot_dim + 2 * (i - rh); e1 = e0 + 1; rotated = false; }
+    else { e0 = 2 * i; e1 = e0 + 1; }
+    const int col0 = head * hd + e0, col1 = head * hd + e1;
     float b0 = 0.f, b1 = 0.f;
     if (PARTIALS && bias) { b0 = load_vec(bias, bias_is_f32, col0); b1 = load_vec(bias, bias_is_f32, col1); }
     size_t page_base = 0;
@@ -197,16 +205,13 @@ __global__ void rope_kv_write_kernel(const void* __restrict__ src, int row_strid
     }
     if (rotated) {
         const float r0 = x0 * c - x1 * s, r1 = x0 * s + x1 * c;
-        T* dst = head < nh ? q_out + (size_t)t * q_out_stride + (size_t)head * hd
-                           : k_pages + page_base + (size_t)(head - nh) * RF_PAGE * hd;
-        dst[i] = Cvt<T>::from_f32(r0);
-        dst[i + half] = Cvt<T>::from_f32(r1);
-    } else {
-        const int vh = head - nh - nkv;
-        T* dst = v_pages + page_base + (size_t)vh * RF_PAGE * hd;
-        dst[2 * i] = Cvt<T>::from_f32(x0);
-        dst[2 * i + 1] = Cvt<T>::from_f32(x1);
+        x0 = r0; x1 = r1;
     }
+    T* dst = head < nh ? q_out + (size_t)t * q_out_stride + (size_t)head * hd
+           : head < nh + nkv ? k_pages + page_base + (size_t)(head - nh) * RF_PAGE * hd
+                             : v_pages + page_base + (size_t)(head - nh - nkv) * RF_PAGE * hd;
+    dst[e0] = Cvt<T>::from_f32(x0);
+    dst[e1] = Cvt<T>::from_f32(x1);
 }
 
 // The same for many tokens (prompts) whose q | k | v rows are one tensor in the compute dtype: a block per
@@ -351,16 +356,16 @@ static int launch_rope_kv_write(const void* src, int row_stride, int n_partials,
                                 const void* bias, int bias_is_f32, void* q_out, int q_out_stride, int nh, int nkv,
                                 int hd, const float* inv_freq, const int* tok_seq, const int* tok_pos,
                                 const int* seq_slot, const int* block_table, int max_pages, void* k_pages,
-                                void* v_pages, int write_kv, int T_, cudaStream_t st) {
+                                void* v_pages, int write_kv, int T_, int rot_dim, int interleaved, cudaStream_t st) {
     if (T_ <= 0) return 0;
-    if (hd % 2) return RF_ERR_BAD_ARG;
+    if (hd % 2 || rot_dim % 2 || rot_dim < 0 || rot_dim > hd) return RF_ERR_BAD_ARG;
     const int n_pairs = (nh + 2 * nkv) * (hd / 2);
     const dim3 grid(T_, (n_pairs + 255) / 256);
     if (T_ > 2147483647 || grid.y > 65535) return RF_ERR_UNSUPPORTED;
     // prompts: rows of one tensor, everything aligned for accesses of four elements
     const size_t four = 4 * sizeof(T);
     auto aligned = [&](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) % four) == 0; };
-    if (n_partials == 0 && T_ >= 64 && hd % 8 == 0 && hd / 8 <= 256 && row_stride % 4 == 0 && q_out_stride % 4 == 0 &&
+    if (n_partials == 0 && rot_dim == hd && !interleaved && T_ >= 64 && hd % 8 == 0 && hd / 8 <= 256 && row_stride % 4 == 0 && q_out_stride % 4 == 0 &&
         aligned(src) && aligned(q_out) && (!write_kv || (aligned(k_pages) && aligned(v_pages)))) {
         const int groups = hd / 8;
         int threads = ((nh + 2 * nkv) * groups + 31) / 32 * 32;        // a row of groups per head, at most 256 threads
@@ -375,11 +380,13 @@ static int launch_rope_kv_write(const void* src, int row_stride, int n_partials,
     if (n_partials > 0)
         rf_launch(rope_kv_write_kernel<T, true>, grid, dim3(256), 0, st, src, row_stride, n_partials, partial_stride, bias,
             bias_is_f32, reinterpret_cast<T*>(q_out), q_out_stride, nh, nkv, hd, inv_freq, tok_seq, tok_pos, seq_slot,
-            block_table, max_pages, reinterpret_cast<T*>(k_pages), reinterpret_cast<T*>(v_pages), write_kv);
+            block_table, max_pages, reinterpret_cast<T*>(k_pages), reinterpret_cast<T*>(v_pages), write_kv, rot_dim,
+            interleaved);
     else
         rf_launch(rope_kv_write_kernel<T, false>, grid, dim3(256), 0, st, src, row_stride, 0, (size_t)0, (const void*)nullptr, 0,
             reinterpret_cast<T*>(q_out), q_out_stride, nh, nkv, hd, inv_freq, tok_seq, tok_pos, seq_slot,
-            block_table, max_pages, reinterpret_cast<T*>(k_pages), reinterpret_cast<T*>(v_pages), write_kv);
+            block_table, max_pages, reinterpret_cast<T*>(k_pages), reinterpret_cast<T*>(v_pages), write_kv, rot_dim,
+            interleaved);
     RF_LAUNCH_CHECK();
     return 0;
 }
@@ -411,14 +418,14 @@ int rf_rope_kv_write(int dtype, const void* src, int row_stride, int n_partials,
                      const void* bias, int bias_is_f32, void* q_out, int q_out_stride, int nh, int nkv, int hd,
                      const float* inv_freq, const int* tok_seq, const int* tok_pos, const int* seq_slot,
                      const int* block_table, int max_pages, void* k_pages, void* v_pages, int write_kv, int T_,
-                     cudaStream_t st) {
+                     int rot_dim, int interleaved, cudaStream_t st) {
     return dtype == 0
         ? launch_rope_kv_write<float>(src, row_stride, n_partials, (size_t)partial_stride, bias, bias_is_f32, q_out,
                                       q_out_stride, nh, nkv, hd, inv_freq, tok_seq, tok_pos, seq_slot, block_table,
-                                      max_pages, k_pages, v_pages, write_kv, T_, st)
+                                      max_pages, k_pages, v_pages, write_kv, T_, rot_dim, interleaved, st)
         : launch_rope_kv_write<__nv_bfloat16>(src, row_stride, n_partials, (size_t)partial_stride, bias, bias_is_f32,
                                               q_out, q_out_stride, nh, nkv, hd, inv_freq, tok_seq, tok_pos, seq_slot,
-                                              block_table, max_pages, k_pages, v_pages, write_kv, T_, st);
+                                              block_table, max_pages, k_pages, v_pages, write_kv, T_, rot_dim, interleaved, st);
 }
 int rf_swiglu(int dtype, const void* gu, void* a, int T_, int I, cudaStream_t st) {
     return dtype == 0 ? launch_swiglu<float>(gu, a, T_, I, st) : launch_swiglu<__nv_bfloat16>(gu, a, T_, I, st);

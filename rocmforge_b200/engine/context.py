@@ -145,14 +145,16 @@ class StepContext:
         tc = kernels.tensor_core
         w, bias = mixer.qkv.weight, mixer.qkv.bias
         y, row_ss = self._rows(y, w, tc.PARTIAL)
-        rope = dict(tok_seq=self.tok_seq, tok_pos=self.tok_pos, seq_slot=self.seq_slot,
+        rot = dict((mixer.position.rotation() if mixer.position is not None else None) or dict(inv_freq=None, rot_dim=0))
+        inv_freq = rot.pop("inv_freq")
+        rope = dict(rot_dim=rot["rot_dim"], interleaved=rot.get("interleaved", False), tok_seq=self.tok_seq, tok_pos=self.tok_pos, seq_slot=self.seq_slot,
                     block_table=view.block_table, k_pages=view.k_pages, v_pages=view.v_pages, write_kv=view.writes)
         if y.shape[0] <= tc.SKINNY_MAX_TOKENS and self._tensor_cores(y, w, tc.PARTIAL):
             splits = tc.split_k_for(w.shape[0], w.shape[1])
             if splits > 1:
                 parts = tc.gemm_tc_skinny(y, w, mode=tc.PARTIAL, splits=splits, row_ss=row_ss)
                 return kernels.rope_kv_write(parts, mixer.n_heads, mixer.n_kv_heads, mixer.head_dim,
-                                             mixer.position.inv_freq, bias=bias, compute_dtype=self.compute_dtype,
+                                             inv_freq, bias=bias, compute_dtype=self.compute_dtype,
                                              **rope)
         if row_ss is not None:
             y = ScaledRows(y, row_ss[0], row_ss[1], w.shape[1])
@@ -161,11 +163,11 @@ class StepContext:
             if splits > 1:                           # CUDA-core product of few tokens: the same scheme
                 parts = kernels.gemm_simt(y, w, splits=splits)
                 return kernels.rope_kv_write(parts, mixer.n_heads, mixer.n_kv_heads, mixer.head_dim,
-                                             mixer.position.inv_freq, bias=bias, compute_dtype=self.compute_dtype,
+                                             inv_freq, bias=bias, compute_dtype=self.compute_dtype,
                                              **rope)
         qkv = self.matmul(y, w, bias)
         return kernels.rope_kv_write(qkv, mixer.n_heads, mixer.n_kv_heads, mixer.head_dim,
-                                     mixer.position.inv_freq, **rope)
+                                     inv_freq, **rope)
 
     def attention(self, q, mixer, view):
         """Attention of the step's tokens over the cache; q is the first heads*head_dim columns of ``q``."""

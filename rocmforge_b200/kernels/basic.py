@@ -81,8 +81,13 @@ def rope_kv_write(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: in
                   tok_seq, tok_pos, seq_slot, block_table: torch.Tensor,
                   k_pages: torch.Tensor | None, v_pages: torch.Tensor | None, write_kv: bool = True, *,
                   bias: torch.Tensor | None = None, compute_dtype: torch.dtype | None = None,
-                  q_out: torch.Tensor | None = None) -> torch.Tensor:
+                  q_out: torch.Tensor | None = None, rot_dim: int | None = None,
+                  interleaved: bool = False) -> torch.Tensor:
     """Rotate q and k by position; write rotated k and v into their cache pages; return q.
+
+    The first ``rot_dim`` elements of every query and key head turn (default: the whole head; 0: none, and
+    ``inv_freq`` may then be None), as pairs (i, i + rot_dim/2) or, ``interleaved``, (2i, 2i+1), pair i by the angle
+    position * inv_freq[i]; the other elements pass through.
 
     ``qkv`` is [T, (heads + 2 kv_heads) * head_dim] in the compute dtype (q is then rotated in place and
     the returned q is a view of it), or a float32 stack [S, T, ...] of partial sums of a K-split product,
@@ -107,8 +112,10 @@ def rope_kv_write(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: in
         S, T, dt = 0, qkv.shape[0], qkv.dtype
         q_out = qkv
         row_stride, pstride = qkv.stride(0), 0
-    need(inv_freq.dtype == torch.float32 and inv_freq.numel() == head_dim // 2,
-         "rope_kv_write: inv_freq must hold head_dim/2 float32 frequencies")
+    rot_dim = head_dim if rot_dim is None else int(rot_dim)
+    need(0 <= rot_dim <= head_dim and rot_dim % 2 == 0, f"rope_kv_write: rot_dim {rot_dim} must be even and at most head_dim")
+    need(rot_dim == 0 or (inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dim // 2),
+         "rope_kv_write: inv_freq must hold rot_dim/2 float32 frequencies")
     if write_kv:
         for p in (k_pages, v_pages):
             need(p is not None and p.dtype == dt and p.is_contiguous()
@@ -116,11 +123,12 @@ def rope_kv_write(qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: in
                  "rope_kv_write: pages must be [n_pages, kv_heads, 64, head_dim] of the compute dtype")
     f = _f("elementwise", "rf_rope_kv_write", c_int, c_void_p, c_int, c_int, c_ll, c_void_p, c_int, c_void_p, c_int,
            c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
-           c_int, c_void_p)
+           c_int, c_int, c_int, c_void_p)
     check(f(dtype_code(dt), ptr(qkv), row_stride, S, pstride, ptr(bias),
             int(bias is not None and bias.dtype == torch.float32), ptr(q_out), q_out.stride(0), n_heads, n_kv_heads,
             head_dim, ptr(inv_freq), ptr(tok_seq), ptr(tok_pos), ptr(seq_slot), ptr(block_table),
-            block_table.shape[1], ptr(k_pages), ptr(v_pages), int(write_kv), T, stream()), "rope_kv_write")
+            block_table.shape[1], ptr(k_pages), ptr(v_pages), int(write_kv), T, rot_dim, int(interleaved), stream()),
+          "rope_kv_write")
     return q_out
 
 

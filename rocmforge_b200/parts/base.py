@@ -54,10 +54,20 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
-    """Knows how a position changes queries and keys; used by mixers that want one."""
+    """Knows how a position changes queries and keys; used by mixers that want one.
+
+    ``rotation()`` is what the encoding hands to the kernel that rotates queries and keys on their way into the
+    cache: a dict with ``inv_freq`` (float32 [rot_dim/2] on the device, pair i turns by position * inv_freq[i]),
+    ``rot_dim`` (how many leading elements of a head turn; the rest pass through) and ``interleaved`` (pairs
+    (2i, 2i+1) instead of (i, i + rot_dim/2)).  An encoding that does not rotate returns None (a mixer built with
+    ``position=None`` behaves the same): queries and keys then go into the cache as they are.
+    """
 
     def prepare(self, device) -> None:
         pass
+
+    def rotation(self):
+        return None
 
 
 class Mixer(Part):

@@ -205,6 +205,62 @@ def test_attention_finds_one_far_key_and_the_window_edge(dt):
     torch.testing.assert_close(out.double().view(1, hd), ref, **tol(dt))
 
 
+def plain_rotation(x, pos, inv_freq, rot_dim, interleaved):
+    """x [T, heads, hd] turned as maeddesg/ROCmForge src/cpu/ops.rs:69-98 does it: pair i of the first rot_dim
+    elements by the 32-bit angle pos * inv_freq[i]; pairs are (i, i + rot_dim/2) (neox) or (2i, 2i+1)."""
+    ang = (pos.to(torch.float32)[:, None] * inv_freq.float()[None, :]).double()
+    c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+    out = x.clone()
+    if interleaved:
+        a, b = x[..., 0:rot_dim:2], x[..., 1:rot_dim:2]
+        out[..., 0:rot_dim:2], out[..., 1:rot_dim:2] = a * c - b * s, a * s + b * c
+    else:
+        h = rot_dim // 2
+        a, b = x[..., :h], x[..., h:rot_dim]
+        out[..., :h], out[..., h:rot_dim] = a * c - b * s, a * s + b * c
+    return out
+
+
+@pytest.mark.parametrize("dt", DTS)
+@pytest.mark.parametrize("hd,rot_dim,interleaved", [(64, 64, True), (64, 32, False), (48, 16, True), (128, 0, False), (32, 2, False)])
+def test_rope_kv_write_partial_and_interleaved_rotations(dt, hd, rot_dim, interleaved):
+    """Only the first rot_dim elements of a head turn, as split or as neighbouring pairs; none at all with rot_dim 0.
+    Through both entries of the kernel: rows of one tensor (one token and 70) and partial sums plus bias."""
+    from rocmforge_b200 import kernels
+    nh, nkv = 6, 2
+    width = (nh + 2 * nkv) * hd
+    inv = (1.0 / (1e4 ** (torch.arange(rot_dim // 2, dtype=torch.float64) * 2 / max(rot_dim, 1)))).float().to(DEV) if rot_dim else None
+    for T in (1, 70):
+        pos = torch.randint(0, 3000, (T,), generator=torch.Generator().manual_seed(T)).to(torch.int32)
+        table = torch.arange(64, dtype=torch.int32).view(1, 64).to(DEV)
+        seq, slot = torch.zeros(T, dtype=torch.int32, device=DEV), torch.zeros(1, dtype=torch.int32, device=DEV)
+        parts = rnd(3, T, width, seed=9)
+        bias = rnd(width, seed=10)
+        total = parts.double().sum(0).cpu() + bias.double().cpu()
+        for source in ("rows", "partials"):
+            k_pages = torch.zeros(64, nkv, 64, hd, dtype=dt, device=DEV)
+            v_pages = torch.zeros_like(k_pages)
+            if source == "rows":
+                qkv = total.to(dt).to(DEV)
+                x = qkv.double().cpu()
+                q = kernels.rope_kv_write(qkv, nh, nkv, hd, inv, seq, pos.to(DEV), slot, table, k_pages, v_pages,
+                                          rot_dim=rot_dim, interleaved=interleaved)[:, :nh * hd]
+            else:
+                x = total
+                q = kernels.rope_kv_write(parts, nh, nkv, hd, inv, seq, pos.to(DEV), slot, table, k_pages, v_pages, bias=bias,
+                                          compute_dtype=dt, rot_dim=rot_dim, interleaved=interleaved)
+            turn = (lambda t: plain_rotation(t, pos, inv.cpu(), rot_dim, interleaved)) if rot_dim else (lambda t: t)
+            q_ref = turn(x[:, :nh * hd].reshape(T, nh, hd))
+            k_ref = turn(x[:, nh * hd:(nh + nkv) * hd].reshape(T, nkv, hd))
+            v_ref = x[:, (nh + nkv) * hd:].reshape(T, nkv, hd)
+            torch.testing.assert_close(q.double().cpu().view(T, nh, hd), q_ref, **tol(dt))
+            # a later token at the same position overwrites an earlier one: compare the last writer of each position
+            last = {int(p_): i for i, p_ in enumerate(pos.tolist())}
+            for p_, i in last.items():
+                torch.testing.assert_close(k_pages[p_ // 64, :, p_ % 64].double().cpu(), k_ref[i], **tol(dt))
+                torch.testing.assert_close(v_pages[p_ // 64, :, p_ % 64].double().cpu(), v_ref[i], **tol(dt))
+
+
 @pytest.mark.parametrize("dt", DTS)
 @pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (3, 1, 48), (28, 4, 128)])
 def test_rope_kv_write(dt, nh, nkv, hd):

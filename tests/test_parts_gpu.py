@@ -365,7 +365,8 @@ def _params_of(model):
 def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_plug_in():
     """Two more kinds defined here and reached through the registries alone: a feed-forward that routes every
     token to one of several small experts (router logits in 32-bit), and a position encoding that stretches
-    positions by a factor (it only has to hand the attention part its table of frequencies)."""
+    positions by a factor and turns only the first half of every head, neighbouring elements as pairs (it hands the
+    rotation kernel its table of frequencies, its rotary size and its pairing); and a mixer without any encoding."""
     import rocmforge_b200 as rf
     from rocmforge_b200.cache import SequenceCache
     from rocmforge_b200.engine import ResidualStream
@@ -402,14 +403,18 @@ def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_plug_in():
 
     @POSITIONS.register("toy_stretched_rope")
     class StretchedRope(PositionEncoding):
-        """Rotation by (position / factor): the same kernel, another table."""
-        def __init__(self, head_dim, theta, factor):
-            i = torch.arange(head_dim // 2, dtype=torch.float64)
-            self.inv_freq_host = (1.0 / (theta ** (2.0 * i / head_dim)) / factor).to(torch.float32)
+        """Rotation by (position / factor) of the first ``rot`` elements of a head, pairs (2i, 2i+1)."""
+        def __init__(self, head_dim, theta, factor, rot):
+            self.rot = rot
+            i = torch.arange(rot // 2, dtype=torch.float64)
+            self.inv_freq_host = (1.0 / (theta ** (2.0 * i / rot)) / factor).to(torch.float32)
             self.inv_freq = None
 
         def prepare(self, device):
             self.inv_freq = self.inv_freq_host.to(device)
+
+        def rotation(self):
+            return dict(inv_freq=self.inv_freq, rot_dim=self.rot, interleaved=True)
 
     # ---- the routed feed-forward against the same thing written out
     H, I, E, T = 40, 24, 3, 50
@@ -432,9 +437,9 @@ def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_plug_in():
     assert len(set(int(logits[t].argmax()) for t in range(T))) == E, "every expert should get tokens in this test"
 
     # ---- the stretched rotation inside the framework's attention part
-    nh, nkv, hd, factor = 4, 2, 16, 4.0
+    nh, nkv, hd, factor, rot_dim = 4, 2, 16, 4.0, 8
     mixer = MIXERS.build("gqa_attention", hidden=H, n_heads=nh, n_kv_heads=nkv, head_dim=hd, qkv_bias=False,
-                         position=POSITIONS.build("toy_stretched_rope", head_dim=hd, theta=100.0, factor=factor))
+                         position=POSITIONS.build("toy_stretched_rope", head_dim=hd, theta=100.0, factor=factor, rot=rot_dim))
     pm = {n: rnd(*sp.shape, seed=20 + i, scale=0.2) for i, (n, sp) in enumerate(mixer.param_specs().items())}
     mixer.bind(pm, dt)
     cache = SequenceCache({0: mixer.cache_request()}, max_tokens=128, dtype=dt, device=DEV)
@@ -449,10 +454,26 @@ def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_plug_in():
     v = (yd @ pm["v_proj.weight"].double().cpu().t()).view(T, nkv, hd)
 
     def rot(x):
-        half = hd // 2
+        # pairs (2i, 2i+1) of the first rot_dim elements (maeddesg/ROCmForge src/cpu/ops.rs:86-96, neox=false)
         ang = (torch.arange(T, dtype=torch.float32)[:, None] * mixer.position.inv_freq_host[None, :]).double()
         c, s_ = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
-        return torch.cat([x[..., :half] * c - x[..., half:] * s_, x[..., :half] * s_ + x[..., half:] * c], dim=-1)
+        out = x.clone()
+        x0, x1 = x[..., 0:rot_dim:2], x[..., 1:rot_dim:2]
+        out[..., 0:rot_dim:2] = x0 * c - x1 * s_
+        out[..., 1:rot_dim:2] = x0 * s_ + x1 * c
+        return out
     o = P.causal_attention(rot(q), rot(k), v)
     ref = o.reshape(T, nh * hd) @ pm["o_proj.weight"].double().cpu().t()
+    torch.testing.assert_close(stream.flush().double().cpu(), ref, atol=2e-5, rtol=1e-4)
+
+    # ---- no position encoding at all: queries and keys go into the cache as they are
+    bare = MIXERS.build("gqa_attention", hidden=H, n_heads=nh, n_kv_heads=nkv, head_dim=hd, qkv_bias=False, position=None)
+    bare.bind(pm, dt)
+    cache = SequenceCache({0: bare.cache_request()}, max_tokens=128, dtype=dt, device=DEV)
+    slot = cache.alloc_slot()
+    cache.prepare([slot], [T])
+    ctx = context(dt, [(slot, [0] * T, [])], [0])
+    stream = ResidualStream(torch.zeros(T, H, device=DEV))
+    bare.forward(ctx, y, cache.view(0), stream)
+    ref = P.causal_attention(q, k, v).reshape(T, nh * hd) @ pm["o_proj.weight"].double().cpu().t()
     torch.testing.assert_close(stream.flush().double().cpu(), ref, atol=2e-5, rtol=1e-4)
