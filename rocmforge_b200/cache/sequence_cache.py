@@ -324,6 +324,16 @@ class SequenceCache:
             return self.states[owner]
         return None
 
+    def snapshot_states(self):
+        """Copies of every fixed-size state tensor (for a step that is run once without being meant: unlike keys and
+        values, which a repeated step writes again with the same contents, state is read, changed and written)."""
+        return [(t, t.clone()) for v in self.states.values() for t in v.tensors.values()]
+
+    @staticmethod
+    def restore_states(snapshot) -> None:
+        for t, saved in snapshot:
+            t.copy_(saved)
+
     def memory_bytes(self) -> int:
         n = sum(g.storage.numel() * g.storage.element_size() for g in self.groups)
         n += sum(t.numel() * t.element_size() for v in self.states.values() for t in v.tensors.values())

@@ -27,13 +27,13 @@ class StepRequest:
     want: Sequence[int] = ()          # indices among ``tokens`` whose logits are wanted
 
 
-Q_TILE = 64           # rows of a prefill attention tile (PF_BM in csrc/attention_prefill.cu)
-
-
 class StepBatch:
-    """Host side of a step: flat int32 arrays, packed into one buffer for a single copy."""
+    """Host side of a step: flat int32 arrays, packed into one buffer for a single copy.
 
-    def __init__(self, requests: Sequence[StepRequest], starts: Sequence[int], vocab_size: int):
+    ``tables``: further int32 arrays that parts of the model build on the host for their kernels from this batch
+    ({name: function of the batch}); they travel in the same copy and appear as ``StepContext.tables[name]``."""
+
+    def __init__(self, requests: Sequence[StepRequest], starts: Sequence[int], vocab_size: int, tables=None):
         if not requests:
             raise BatchError("a step needs at least one sequence")
         self.slots = [int(r.slot) for r in requests]
@@ -62,28 +62,25 @@ class StepBatch:
                 rows.append(int(self.cu_q[i]) + int(w))
         self.want_rows = np.asarray(rows, dtype=np.int32)
         self.R = len(rows)
-        # 64-row tiles of the new tokens, (sequence, first row), for the tiled attention: decided here so
-        # that the device never searches
-        tiles = [(i, q0) for i in range(self.B) for q0 in range(0, int(self.n_new[i]), Q_TILE)]
-        tiles.sort(key=lambda t: int(self.starts[t[0]]) + t[1])    # by the keys a tile sees: the kernels start at the end
-        self.q_tiles = np.asarray(tiles, dtype=np.int32).reshape(-1)
-        self.n_tiles = len(tiles)
-        big = [(i, q0) for i in range(self.B) for q0 in range(0, int(self.n_new[i]), 2 * Q_TILE)]
-        big.sort(key=lambda t: int(self.starts[t[0]]) + t[1])
-        self.q_tiles128 = np.asarray(big, dtype=np.int32).reshape(-1)      # for the kernel with 128-row tiles
-        self.n_tiles128 = len(big)
         self.is_decode = bool((self.n_new == 1).all())
         self.max_new = int(self.n_new.max())
         self.max_end = int((self.starts + self.n_new).max())
+        self.tables = {name: np.ascontiguousarray(build(self), dtype=np.int32).reshape(-1)
+                       for name, build in (tables or {}).items()}
+
+    @property
+    def extras(self):
+        """(name, length) of the parts' tables, in packing order."""
+        return tuple((name, int(arr.size)) for name, arr in self.tables.items())
 
     # layout of the packed descriptor, in int32 elements
     @staticmethod
-    def layout(T: int, B: int, R: int, n_tiles: int = 0, n_tiles128: int = 0, decode_extras: bool = False):
-        """``decode_extras``: two more arrays for decode steps that a runner launches ahead of the host: the rows'
-        64-bit sampling seeds (two words each) and each sequence's row in the step before."""
+    def layout(T: int, B: int, R: int, extras=(), decode_extras: bool = False):
+        """``extras``: (name, length) of the parts' tables.  ``decode_extras``: two more arrays for decode steps that
+        a runner launches ahead of the host: the rows' 64-bit sampling seeds (two words each) and each sequence's row
+        in the step before."""
         names = [("tokens", T), ("tok_seq", T), ("tok_pos", T), ("seq_slot", B), ("seq_start", B),
-                 ("seq_nnew", B), ("cu_q", B + 1), ("want_rows", R), ("q_tiles", 2 * n_tiles),
-                 ("q_tiles128", 2 * n_tiles128)]
+                 ("seq_nnew", B), ("cu_q", B + 1), ("want_rows", R)] + [(n, k) for n, k in extras]
         if decode_extras:
             names += [("seeds", 2 * B), ("row_map", B)]
         off, out = 0, {}
@@ -93,12 +90,11 @@ class StepBatch:
         return out, off
 
     def pack(self) -> np.ndarray:
-        lay, total = self.layout(self.T, self.B, self.R, self.n_tiles, self.n_tiles128)
+        lay, total = self.layout(self.T, self.B, self.R, self.extras)
         buf = np.zeros((total,), dtype=np.int32)
-        for name, arr in (("tokens", self.tokens), ("tok_seq", self.tok_seq), ("tok_pos", self.tok_pos),
+        for name, arr in [("tokens", self.tokens), ("tok_seq", self.tok_seq), ("tok_pos", self.tok_pos),
                           ("seq_slot", np.asarray(self.slots, dtype=np.int32)), ("seq_start", self.starts),
-                          ("seq_nnew", self.n_new), ("cu_q", self.cu_q), ("want_rows", self.want_rows),
-                          ("q_tiles", self.q_tiles), ("q_tiles128", self.q_tiles128)):
+                          ("seq_nnew", self.n_new), ("cu_q", self.cu_q), ("want_rows", self.want_rows)] + list(self.tables.items()):
             o, n = lay[name]
             buf[o:o + n] = arr
         return buf
@@ -152,6 +148,6 @@ class DeviceDescriptor:
             self._done.record()
             self._busy = True
 
-    def views(self, T: int, B: int, R: int, n_tiles: int = 0, n_tiles128: int = 0, decode_extras: bool = False):
-        lay, _ = StepBatch.layout(T, B, R, n_tiles, n_tiles128, decode_extras)
+    def views(self, T: int, B: int, R: int, extras=(), decode_extras: bool = False):
+        lay, _ = StepBatch.layout(T, B, R, extras, decode_extras)
         return {name: self.dev[o:o + n] for name, (o, n) in lay.items()}

@@ -55,22 +55,22 @@ class StepContext:
         self.seq_nnew = views["seq_nnew"]
         self.cu_q = views["cu_q"]
         self.want_rows = views["want_rows"]
-        self.q_tiles = views["q_tiles"]
-        self.q_tiles128 = views["q_tiles128"]
+        known = {"tokens", "tok_seq", "tok_pos", "seq_slot", "seq_start", "seq_nnew", "cu_q", "want_rows", "seeds", "row_map"}
+        self.tables = {name: v for name, v in views.items() if name not in known}      # the parts' own tables
 
     # ---------------------------------------------------------------- matrix products
-    def _tensor_cores(self, x, w, mode) -> bool:
+    def uses_tensor_cores(self, x, w, mode) -> bool:
         return (self.compute_dtype == torch.bfloat16 and self.options.tensor_core_gemm
                 and kernels.tensor_core.supported(x.shape[0], w.shape[0], w.shape[1], mode)
                 and x.data_ptr() % 16 == 0 and (x.stride(0) * 2) % 16 == 0)
 
-    def _rows(self, x, w, mode):
+    def unpack_rows(self, x, w, mode):
         """(tensor, row_ss) of an activation: the sums of squares go along where the product scales rows itself,
         else the rows are normalised first."""
         if not isinstance(x, ScaledRows):
             return x, None
         tc = kernels.tensor_core
-        if x.x.shape[0] <= tc.SKINNY_MAX_TOKENS and self._tensor_cores(x.x, w, mode):
+        if x.x.shape[0] <= tc.SKINNY_MAX_TOKENS and self.uses_tensor_cores(x.x, w, mode):
             return x.x, x.row_ss
         return x.materialize(), None
 
@@ -78,8 +78,8 @@ class StepContext:
         """x [M,K] @ w[N,K]^T (+ bias) -> [M,N] in the compute dtype, or in float32."""
         tc = kernels.tensor_core
         mode = tc.F32 if out_f32 else tc.STORE
-        x, row_ss = self._rows(x, w, mode)
-        if self._tensor_cores(x, w, mode):
+        x, row_ss = self.unpack_rows(x, w, mode)
+        if self.uses_tensor_cores(x, w, mode):
             if x.shape[0] <= tc.SKINNY_MAX_TOKENS:
                 return tc.gemm_tc_skinny(x, w, bias, mode=mode, row_ss=row_ss)
             return tc.gemm_tc(x, w, bias, mode=mode)
@@ -90,8 +90,8 @@ class StepContext:
         32-bit partial sums of a K-split product (the next norm adds them in index order)."""
         tc = kernels.tensor_core
         follows = stream.take_hint()                 # the norm that reads the stream after this update, if we were told
-        x, row_ss = self._rows(x, w, tc.RESIDUAL)
-        if self._tensor_cores(x, w, tc.RESIDUAL):
+        x, row_ss = self.unpack_rows(x, w, tc.RESIDUAL)
+        if self.uses_tensor_cores(x, w, tc.RESIDUAL):
             if x.shape[0] <= tc.SKINNY_MAX_TOKENS:
                 deferred = (follows.deferred_params() if (follows is not None and self.options.fused_norm
                                                           and x.shape[0] <= self.options.fused_norm_max_tokens) else None)
@@ -124,8 +124,8 @@ class StepContext:
         """silu(gate) * up from the fused, row-interleaved gate/up matrix."""
         tc = kernels.tensor_core
         w = gate_up.weight
-        y, row_ss = self._rows(y, w, tc.SWIGLU)
-        if gate_up.bias is None and self._tensor_cores(y, w, tc.SWIGLU):
+        y, row_ss = self.unpack_rows(y, w, tc.SWIGLU)
+        if gate_up.bias is None and self.uses_tensor_cores(y, w, tc.SWIGLU):
             if y.shape[0] <= tc.SKINNY_MAX_TOKENS:
                 return tc.gemm_tc_skinny(y, w, mode=tc.SWIGLU, row_ss=row_ss)
             return tc.gemm_tc(y, w, mode=tc.SWIGLU)
@@ -133,83 +133,3 @@ class StepContext:
             y = ScaledRows(y, row_ss[0], row_ss[1], w.shape[1]).materialize()
         gu = self.matmul(y, w, gate_up.bias)
         return kernels.swiglu(gu)
-
-    # ---------------------------------------------------------------- attention
-    def project_qkv_into_cache(self, y, mixer, view):
-        """q/k/v projection (+ bias), rotation, cache write; returns rotated q [T, >= heads*head_dim].
-
-        With few tokens on the tensor-core path the product is K-split for parallelism and the
-        rotation kernel sums the 32-bit partial sums (and the bias) itself, so q/k/v never
-        exist as an intermediate bfloat16 tensor.
-        """
-        tc = kernels.tensor_core
-        w, bias = mixer.qkv.weight, mixer.qkv.bias
-        y, row_ss = self._rows(y, w, tc.PARTIAL)
-        rot = dict((mixer.position.rotation() if mixer.position is not None else None) or dict(inv_freq=None, rot_dim=0))
-        inv_freq = rot.pop("inv_freq")
-        rope = dict(rot_dim=rot["rot_dim"], interleaved=rot.get("interleaved", False), tok_seq=self.tok_seq, tok_pos=self.tok_pos, seq_slot=self.seq_slot,
-                    block_table=view.block_table, k_pages=view.k_pages, v_pages=view.v_pages, write_kv=view.writes)
-        if y.shape[0] <= tc.SKINNY_MAX_TOKENS and self._tensor_cores(y, w, tc.PARTIAL):
-            splits = tc.split_k_for(w.shape[0], w.shape[1])
-            if splits > 1:
-                parts = tc.gemm_tc_skinny(y, w, mode=tc.PARTIAL, splits=splits, row_ss=row_ss)
-                return kernels.rope_kv_write(parts, mixer.n_heads, mixer.n_kv_heads, mixer.head_dim,
-                                             inv_freq, bias=bias, compute_dtype=self.compute_dtype,
-                                             **rope)
-        if row_ss is not None:
-            y = ScaledRows(y, row_ss[0], row_ss[1], w.shape[1])
-        elif y.shape[0] <= tc.SKINNY_MAX_TOKENS and not self._tensor_cores(y, w, tc.STORE):
-            splits = kernels.split_k_for_simt(w.shape[0], w.shape[1])
-            if splits > 1:                           # CUDA-core product of few tokens: the same scheme
-                parts = kernels.gemm_simt(y, w, splits=splits)
-                return kernels.rope_kv_write(parts, mixer.n_heads, mixer.n_kv_heads, mixer.head_dim,
-                                             inv_freq, bias=bias, compute_dtype=self.compute_dtype,
-                                             **rope)
-        qkv = self.matmul(y, w, bias)
-        return kernels.rope_kv_write(qkv, mixer.n_heads, mixer.n_kv_heads, mixer.head_dim,
-                                     inv_freq, **rope)
-
-    def attention(self, q, mixer, view):
-        """Attention of the step's tokens over the cache; q is the first heads*head_dim columns of ``q``."""
-        nh, nkv, hd = mixer.n_heads, mixer.n_kv_heads, mixer.head_dim
-        longest = self.model_cache_limit if self.replayed else self.max_end
-        if (self.is_decode and self.compute_dtype == torch.bfloat16 and self.options.tuned_attention
-                and kernels.attention_decode_supported(nh, nkv, hd)):
-            if self.options.clustered_decode:
-                # a cluster of 1..8 CTAs per (sequence, kv head), every warp on its own tiles of keys, merged
-                # through distributed shared memory: no scratch memory, no second pass, any context length
-                return kernels.attention_decode_warps(
-                    q, nh, nkv, hd, view.k_pages, view.v_pages, self.tok_seq, self.tok_pos, self.seq_slot,
-                    view.block_table, mixer.scale, view.window,
-                    splits=kernels.decode_splits(self.B, nkv, longest, view.window))
-            if longest <= kernels.DECODE_CHUNK * kernels.DECODE_CHUNK:
-                # the earlier kernel: one CTA per 128-key chunk, partial results merged through scratch memory
-                need = max(1, (longest + kernels.DECODE_CHUNK - 1) // kernels.DECODE_CHUNK)
-                max_chunks = 1
-                while max_chunks < need:                   # powers of two: few distinct scratch sizes
-                    max_chunks *= 2
-                cap = 1
-                while cap < self.B:
-                    cap *= 2
-                n_o, n_ml, n_c = kernels.attention_decode_scratch(cap, nh, nkv, hd, max_chunks)
-                scratch = self.model.scratch
-                return kernels.attention_decode(
-                    q, nh, nkv, hd, view.k_pages, view.v_pages, self.tok_seq, self.tok_pos, self.seq_slot,
-                    view.block_table, mixer.scale, view.window, max_chunks,
-                    scratch("attn_decode_o", n_o, torch.float32), scratch("attn_decode_ml", n_ml, torch.float32),
-                    kernels.tensor_core.register_counters(scratch("attn_decode_counters", n_c, torch.int32)))
-        if (not self.is_decode and self.compute_dtype == torch.bfloat16 and self.options.tuned_attention
-                and self.options.tcgen05_attention and self.q_tiles128.numel() > 0
-                and kernels.attention_prefill_tc_supported(nh, nkv, hd)
-                and q.data_ptr() % 16 == 0 and (q.stride(0) * 2) % 16 == 0):
-            return kernels.attention_prefill_tc(q, nh, nkv, hd, view.k_pages, view.v_pages, self.q_tiles128,
-                                                self.seq_slot, self.seq_start, self.seq_nnew, self.cu_q,
-                                                view.block_table, mixer.scale, view.window)
-        if (not self.is_decode and self.compute_dtype == torch.bfloat16 and self.options.tuned_attention
-                and self.q_tiles.numel() > 0 and kernels.attention_prefill_supported(nh, nkv, hd)
-                and q.data_ptr() % 4 == 0 and q.stride(0) % 2 == 0):
-            return kernels.attention_prefill(q, nh, nkv, hd, view.k_pages, view.v_pages, self.q_tiles, self.seq_slot,
-                                             self.seq_start, self.seq_nnew, self.cu_q, view.block_table, mixer.scale,
-                                             view.window)
-        return kernels.attention_generic(q, nh, nkv, hd, view.k_pages, view.v_pages, self.tok_seq, self.tok_pos,
-                                         self.seq_slot, view.block_table, mixer.scale, view.window)

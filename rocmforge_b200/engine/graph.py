@@ -50,9 +50,9 @@ class DecodeRunner:
 
     @staticmethod
     def descriptor_words(max_batch: int) -> int:
-        """int32 words of the largest packed decode descriptor (one token, one wanted row and one tile of each
-        kind per sequence)."""
-        return StepBatch.layout(max_batch, max_batch, max_batch, max_batch, max_batch, decode_extras=True)[1]
+        """int32 words of the largest packed decode descriptor (one token and one wanted row per sequence, seeds and
+        row map of steps launched ahead)."""
+        return StepBatch.layout(max_batch, max_batch, max_batch, decode_extras=True)[1]
 
     @staticmethod
     def length_bucket(longest: int) -> int:
@@ -71,15 +71,22 @@ class DecodeRunner:
         ctx.replayed = True          # launch shapes must not depend on this step's lengths
         return ctx
 
+    def _warm_up(self, body) -> None:
+        """Run ``body`` once outside capture (loads modules, sizes the allocator) and undo what it did to per-sequence
+        state: the step it ran is not one of the sequence's steps."""
+        saved = self.cache.snapshot_states()
+        side = torch.cuda.Stream(device=self.model.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            body()
+        torch.cuda.current_stream().wait_stream(side)
+        self.cache.restore_states(saved)
+
     def _capture(self, B: int, bound: int, greedy: bool = False) -> _Captured:
         """The step's graph; with ``greedy`` the argmax is part of it and ``ids`` holds its result."""
         from .. import kernels
         ctx = self._context(B, bound)
-        side = torch.cuda.Stream(device=self.model.device)
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            self.model.forward(ctx, self.cache)            # warm-up: loads modules, sizes the allocator
-        torch.cuda.current_stream().wait_stream(side)
+        self._warm_up(lambda: self.model.forward(ctx, self.cache))
         graph = torch.cuda.CUDAGraph()
         ids = torch.zeros((B,), dtype=torch.int32, device=self.model.device) if greedy else None
         with torch.cuda.graph(graph):
@@ -162,11 +169,7 @@ class DecodeRunner:
         if cap is None:
             ctx = self._context(B, bound)
             sampled = torch.zeros((B,), dtype=torch.int32, device=self.model.device)
-            side = torch.cuda.Stream(device=self.model.device)
-            side.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(side):
-                kernels.argmax(self.model.forward(ctx, self.cache), out=sampled)
-            torch.cuda.current_stream().wait_stream(side)
+            self._warm_up(lambda: kernels.argmax(self.model.forward(ctx, self.cache), out=sampled))
             graph = torch.cuda.CUDAGraph()
             n0 = kernels.launch_count()
             with torch.cuda.graph(graph):
@@ -200,11 +203,7 @@ class DecodeRunner:
             else:
                 kernels.sample(logits, sampling.temperature, sampling.top_p, sampling.top_k, seeds, out=ids)
             return logits
-        side = torch.cuda.Stream(device=self.model.device)
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            body()                                         # warm-up: loads modules, sizes the allocator
-        torch.cuda.current_stream().wait_stream(side)
+        self._warm_up(body)
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             logits = body()
@@ -316,7 +315,9 @@ class DecodeRunner:
         else:
             self.launched_ahead += 1
         cache.commit(slots, [1] * B)                       # the step is under way for these sequences
-        if more:
+        if more and not cache.states:
+            # (a model with per-sequence state is not run ahead: a step that is dropped would have changed the state,
+            # whereas keys and values written by a dropped step are simply written again)
             # the next step of the same sequences, before the host knows this step's ids
             try:
                 cache.prepare(slots, [1] * B)

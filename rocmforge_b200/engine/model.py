@@ -109,6 +109,10 @@ class Model:
             local = {name[len(prefix):]: t for name, t in params.items()
                      if name.startswith(prefix) and name[len(prefix):] in part.param_specs()}
             part.bind(local, compute_dtype)
+        self._tables = {}                  # name -> builder of a host table that a part wants with every step
+        for part in spec.named_parts().values():
+            for name in part.step_table_names():
+                self._tables.setdefault(name, (lambda batch, part=part, name=name: part.step_table(name, batch)))
         self._desc = DeviceDescriptor(self.device)
         self._scratch: Dict[tuple, torch.Tensor] = {}
         self.weight_bytes = sum(t.numel() * t.element_size()
@@ -163,11 +167,11 @@ class Model:
                 raise BatchError(f"slot {r.slot}: a step must bring at least one token")
         # build (and validate) the batch before any page is taken
         starts_now = [cache.length(s) if cache.slots.is_held(s) else 0 for s in slots]
-        batch = StepBatch(requests, starts_now, self.spec.vocab_size)
+        batch = StepBatch(requests, starts_now, self.spec.vocab_size, tables=self._tables)
         cache.prepare(slots, n_new)
         try:
             self._desc.upload(batch.pack())
-            views = self._desc.views(batch.T, batch.B, batch.R, batch.n_tiles, batch.n_tiles128)
+            views = self._desc.views(batch.T, batch.B, batch.R, batch.extras)
             ctx = StepContext(self, views, T=batch.T, B=batch.B, R=batch.R, is_decode=batch.is_decode,
                               max_new=batch.max_new, max_end=batch.max_end, host=batch)
             logits = self.forward(ctx, cache)

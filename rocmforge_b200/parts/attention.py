@@ -4,10 +4,12 @@ from __future__ import annotations
 import math
 from typing import Dict, Optional
 
+import numpy as np
 import torch
 
 from .. import kernels
 from ..cache.requests import KVRequest
+from ..engine.stream import ScaledRows
 from ..weights.spec import ParamSpec
 from .base import MIXERS, Mixer, POSITIONS
 from .linear import Linear
@@ -78,7 +80,105 @@ class GQAAttention(Mixer):
     def cache_request(self):
         return KVRequest(self.n_kv_heads, self.head_dim, self.window)
 
+    # rows of the query tiles of the two tiled prefill kernels (csrc/attention_prefill.cu, attention_prefill_tc.cu)
+    TILE_ROWS = {"attention_tiles64": 64, "attention_tiles128": 128}
+
+    def step_table_names(self):
+        return tuple(self.TILE_ROWS)
+
+    def step_table(self, name, batch):
+        """(sequence, first row) of every query tile of the step's new tokens, sorted by the keys a tile sees (the
+        kernels start with the heaviest): decided on the host so that the device never searches.  Steps of one token
+        per sequence need none."""
+        if batch.is_decode:
+            return np.zeros((0,), dtype=np.int32)
+        rows = self.TILE_ROWS[name]
+        tiles = [(i, q0) for i in range(batch.B) for q0 in range(0, int(batch.n_new[i]), rows)]
+        tiles.sort(key=lambda t: int(batch.starts[t[0]]) + t[1])
+        return np.asarray(tiles, dtype=np.int32).reshape(-1)
+
     def forward(self, ctx, y, cache_view, stream):
-        q = ctx.project_qkv_into_cache(y, self, cache_view)                 # rotated q; k, v are in the cache
-        o = ctx.attention(q, self, cache_view)
+        q = self.project_into_cache(ctx, y, cache_view)                     # rotated q; k, v are in the cache
+        o = self.attend(ctx, q, cache_view)
         self.o.add_to_stream(ctx, o, stream)
+
+    def project_into_cache(self, ctx, y, view):
+        """q/k/v projection (+ bias), rotation, cache write; returns rotated q [T, >= heads*head_dim].
+
+        With few tokens on the tensor-core path the product is K-split for parallelism and the
+        rotation kernel sums the 32-bit partial sums (and the bias) itself, so q/k/v never
+        exist as an intermediate bfloat16 tensor.
+        """
+        tc = kernels.tensor_core
+        w, bias = self.qkv.weight, self.qkv.bias
+        y, row_ss = ctx.unpack_rows(y, w, tc.PARTIAL)
+        rot = dict((self.position.rotation() if self.position is not None else None) or dict(inv_freq=None, rot_dim=0))
+        inv_freq = rot.pop("inv_freq")
+        rope = dict(rot_dim=rot["rot_dim"], interleaved=rot.get("interleaved", False), tok_seq=ctx.tok_seq, tok_pos=ctx.tok_pos, seq_slot=ctx.seq_slot,
+                    block_table=view.block_table, k_pages=view.k_pages, v_pages=view.v_pages, write_kv=view.writes)
+        if y.shape[0] <= tc.SKINNY_MAX_TOKENS and ctx.uses_tensor_cores(y, w, tc.PARTIAL):
+            splits = tc.split_k_for(w.shape[0], w.shape[1])
+            if splits > 1:
+                parts = tc.gemm_tc_skinny(y, w, mode=tc.PARTIAL, splits=splits, row_ss=row_ss)
+                return kernels.rope_kv_write(parts, self.n_heads, self.n_kv_heads, self.head_dim,
+                                             inv_freq, bias=bias, compute_dtype=ctx.compute_dtype,
+                                             **rope)
+        if row_ss is not None:
+            y = ScaledRows(y, row_ss[0], row_ss[1], w.shape[1])
+        elif y.shape[0] <= tc.SKINNY_MAX_TOKENS and not ctx.uses_tensor_cores(y, w, tc.STORE):
+            splits = kernels.split_k_for_simt(w.shape[0], w.shape[1])
+            if splits > 1:                           # CUDA-core product of few tokens: the same scheme
+                parts = kernels.gemm_simt(y, w, splits=splits)
+                return kernels.rope_kv_write(parts, self.n_heads, self.n_kv_heads, self.head_dim,
+                                             inv_freq, bias=bias, compute_dtype=ctx.compute_dtype,
+                                             **rope)
+        qkv = ctx.matmul(y, w, bias)
+        return kernels.rope_kv_write(qkv, self.n_heads, self.n_kv_heads, self.head_dim,
+                                     inv_freq, **rope)
+
+    def attend(self, ctx, q, view):
+        """Attention of the step's tokens over the cache; q is the first heads*head_dim columns of ``q``."""
+        nh, nkv, hd = self.n_heads, self.n_kv_heads, self.head_dim
+        tiles64, tiles128 = ctx.tables.get("attention_tiles64"), ctx.tables.get("attention_tiles128")
+        longest = ctx.model_cache_limit if ctx.replayed else ctx.max_end
+        if (ctx.is_decode and ctx.compute_dtype == torch.bfloat16 and ctx.options.tuned_attention
+                and kernels.attention_decode_supported(nh, nkv, hd)):
+            if ctx.options.clustered_decode:
+                # a cluster of 1..8 CTAs per (sequence, kv head), every warp on its own tiles of keys, merged
+                # through distributed shared memory: no scratch memory, no second pass, any context length
+                return kernels.attention_decode_warps(
+                    q, nh, nkv, hd, view.k_pages, view.v_pages, ctx.tok_seq, ctx.tok_pos, ctx.seq_slot,
+                    view.block_table, self.scale, view.window,
+                    splits=kernels.decode_splits(ctx.B, nkv, longest, view.window))
+            if longest <= kernels.DECODE_CHUNK * kernels.DECODE_CHUNK:
+                # the earlier kernel: one CTA per 128-key chunk, partial results merged through scratch memory
+                need = max(1, (longest + kernels.DECODE_CHUNK - 1) // kernels.DECODE_CHUNK)
+                max_chunks = 1
+                while max_chunks < need:                   # powers of two: few distinct scratch sizes
+                    max_chunks *= 2
+                cap = 1
+                while cap < ctx.B:
+                    cap *= 2
+                n_o, n_ml, n_c = kernels.attention_decode_scratch(cap, nh, nkv, hd, max_chunks)
+                scratch = ctx.model.scratch
+                return kernels.attention_decode(
+                    q, nh, nkv, hd, view.k_pages, view.v_pages, ctx.tok_seq, ctx.tok_pos, ctx.seq_slot,
+                    view.block_table, self.scale, view.window, max_chunks,
+                    scratch("attn_decode_o", n_o, torch.float32), scratch("attn_decode_ml", n_ml, torch.float32),
+                    kernels.tensor_core.register_counters(scratch("attn_decode_counters", n_c, torch.int32)))
+        if (not ctx.is_decode and ctx.compute_dtype == torch.bfloat16 and ctx.options.tuned_attention
+                and ctx.options.tcgen05_attention and tiles128 is not None and tiles128.numel() > 0
+                and kernels.attention_prefill_tc_supported(nh, nkv, hd)
+                and q.data_ptr() % 16 == 0 and (q.stride(0) * 2) % 16 == 0):
+            return kernels.attention_prefill_tc(q, nh, nkv, hd, view.k_pages, view.v_pages, tiles128,
+                                                ctx.seq_slot, ctx.seq_start, ctx.seq_nnew, ctx.cu_q,
+                                                view.block_table, self.scale, view.window)
+        if (not ctx.is_decode and ctx.compute_dtype == torch.bfloat16 and ctx.options.tuned_attention
+                and tiles64 is not None and tiles64.numel() > 0 and kernels.attention_prefill_supported(nh, nkv, hd)
+                and q.data_ptr() % 4 == 0 and q.stride(0) % 2 == 0):
+            return kernels.attention_prefill(q, nh, nkv, hd, view.k_pages, view.v_pages, tiles64, ctx.seq_slot,
+                                             ctx.seq_start, ctx.seq_nnew, ctx.cu_q, view.block_table, self.scale,
+                                             view.window)
+        return kernels.attention_generic(q, nh, nkv, hd, view.k_pages, view.v_pages, ctx.tok_seq, ctx.tok_pos,
+                                         ctx.seq_slot, view.block_table, self.scale, view.window)
+

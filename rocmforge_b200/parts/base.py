@@ -36,6 +36,16 @@ class Part:
     def cuda_modules(self, compute_dtype: torch.dtype) -> List[str]:
         return []
 
+    def step_table_names(self):
+        """Names of int32 tables that this part builds on the host for every step (``step_table``).  They travel with
+        the step descriptor in its one copy and reach the part as ``ctx.tables[name]``.  A name identifies its
+        content: of several parts that name the same table, the first one builds it for all."""
+        return ()
+
+    def step_table(self, name: str, batch):
+        """The table ``name`` for ``batch`` (an engine.batch.StepBatch: B, n_new, starts, is_decode, ...)."""
+        raise NotImplementedError
+
 
 class Norm(Part):
     """y = norm(h + pending).  See engine.stream.ResidualStream for ``stream``.

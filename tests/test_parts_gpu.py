@@ -36,8 +36,8 @@ def rnd(*shape, dt=torch.float32, seed=0, scale=1.0):
     return (torch.randn(*shape, generator=g) * scale).to(dt).to(DEV)
 
 
-def context(dt, requests, starts, vocab=1 << 20):
-    """A StepContext for parts tested outside a model."""
+def context(dt, requests, starts, vocab=1 << 20, parts=()):
+    """A StepContext for parts tested outside a model (``parts``: those whose host tables the step must carry)."""
     from rocmforge_b200.engine import Options, StepBatch, StepContext, StepRequest
     from rocmforge_b200.engine.batch import DeviceDescriptor
     pool = {}
@@ -45,10 +45,12 @@ def context(dt, requests, starts, vocab=1 << 20):
     def scratch(name, n, dtype):
         return pool.setdefault((name, n, dtype), torch.zeros((max(n, 1),), dtype=dtype, device=DEV))
     fake_model = SimpleNamespace(options=Options(), compute_dtype=dt, device=torch.device(DEV), scratch=scratch)
-    batch = StepBatch([StepRequest(*r) for r in requests], starts, vocab)
+    tables = {name: (lambda b, part=part, name=name: part.step_table(name, b))
+              for part in parts for name in part.step_table_names()}
+    batch = StepBatch([StepRequest(*r) for r in requests], starts, vocab, tables=tables)
     desc = DeviceDescriptor(DEV)
     desc.upload(batch.pack())
-    ctx = StepContext(fake_model, desc.views(batch.T, batch.B, batch.R, batch.n_tiles, batch.n_tiles128), T=batch.T, B=batch.B, R=batch.R,
+    ctx = StepContext(fake_model, desc.views(batch.T, batch.B, batch.R, batch.extras), T=batch.T, B=batch.B, R=batch.R,
                       is_decode=batch.is_decode, max_new=batch.max_new, max_end=batch.max_end, host=batch)
     ctx._keep = desc
     return ctx
@@ -116,7 +118,7 @@ def test_attention_part_over_its_cache(dt, window):
     for chunk in ([100, 17], [30, 1], [1, 1], [19, 71]):
         reqs = [(s, [0] * n, []) for s, n in zip(slots, chunk)]
         cache.prepare(slots, chunk)
-        ctx = context(dt, reqs, done)
+        ctx = context(dt, reqs, done, parts=[mixer])
         y = torch.cat([ys[i][done[i]:done[i] + n] for i, n in enumerate(chunk)])
         stream = ResidualStream(torch.zeros(sum(chunk), H, device=DEV))
         mixer.forward(ctx, y, cache.view(0), stream)
@@ -270,13 +272,20 @@ def test_a_toy_mixer_with_state_registers_builds_and_steps():
 
         def forward(self, ctx, y, state, stream):
             u = ctx.matmul(y, self.w_in, out_f32=True)                      # the framework's product
-            out = torch.empty_like(u)
-            b = ctx.host
-            for i, slot in enumerate(b.slots):                              # the scan itself is plain torch
-                s = state["s"][slot]
-                for t in range(int(b.cu_q[i]), int(b.cu_q[i + 1])):
-                    s.mul_(self.decay).add_(u[t])
-                    out[t] = s
+            if ctx.is_decode:
+                # one token per sequence: the state rows of the step's slots, indexed on the device (the batch's host
+                # arrays do not exist inside a replayed graph)
+                rows = ctx.seq_slot.long()
+                out = state["s"][rows] * self.decay + u
+                state["s"].index_copy_(0, rows, out)
+            else:
+                out = torch.empty_like(u)
+                b = ctx.host
+                for i, slot in enumerate(b.slots):                          # the scan itself is plain torch
+                    s = state["s"][slot]
+                    for t in range(int(b.cu_q[i]), int(b.cu_q[i + 1])):
+                        s.mul_(self.decay).add_(u[t])
+                        out[t] = s
             ctx.matmul_residual(out.to(ctx.compute_dtype), self.w_out, None, stream)
 
     @dataclass
@@ -314,7 +323,7 @@ def test_a_toy_mixer_with_state_registers_builds_and_steps():
     m = rf.Model.random(cfg, seed=4, dtype=torch.float32)
     cache = m.new_cache(max_tokens=256, max_slots=4)
     assert cache.groups == [] and sorted(cache.states) == [0, 1]
-    toks = [random_tokens(50, n, n) for n in (30, 7)]
+    toks = [random_tokens(50, n, n) for n in (30, 14)]
     # whole, alone
     whole = []
     for t in toks:
@@ -331,6 +340,19 @@ def test_a_toy_mixer_with_state_registers_builds_and_steps():
         got = m.step(cache, [rf.StepRequest(s, [t[i]], [0]) for s, t in zip(slots, toks)])
         torch.testing.assert_close(got[0].cpu(), whole[0][i], atol=1e-5, rtol=1e-4)
         torch.testing.assert_close(got[1].cpu(), whole[1][i], atol=1e-5, rtol=1e-4)
+    # the same sequences go on through replayed graphs (logits, and sampled ids one step ahead of the host): the state
+    # lives in device tensors indexed by the step's slots, so a captured step reads and writes the right rows
+    from rocmforge_b200.engine.graph import DecodeRunner
+    runner = DecodeRunner(m, cache)
+    for i in range(7, 11):
+        got = runner.logits(slots, [t[i] for t in toks]).cpu()
+        torch.testing.assert_close(got[0], whole[0][i], atol=1e-5, rtol=1e-4)
+        torch.testing.assert_close(got[1], whole[1][i], atol=1e-5, rtol=1e-4)
+    greedy = rf.SamplingParams(temperature=0.0)
+    for i in range(11, 14):
+        ids = runner.step_ids(slots, [t[i] for t in toks], greedy, [0, 1], [i, i], more=False)
+        assert ids == [int(whole[0][i].argmax()), int(whole[1][i].argmax())]
+    assert runner.replays >= 7
     # and against the recurrence written out
     p = {n: t.double().cpu() for n, t in _params_of(m).items()}
     x = p["emb.weight"][torch.tensor(toks[1])]
