@@ -73,8 +73,11 @@ class LLM:
 
     def generate(self, prompts: Sequence[Union[str, Sequence[int]]], max_tokens: int = 256,
                  temperature: float = 1.0, top_p: float = 0.9, top_k: int = 0, seed: int = DEFAULT_SEED,
-                 stop_token_ids: Optional[Iterable[int]] = None, on_token=None) -> List[GenerationResult]:
+                 stop_token_ids: Optional[Iterable[int]] = None, on_token=None, on_logits=None) -> List[GenerationResult]:
         """Token ids in, token ids out (strings go through the byte-level stand-in tokenizer).
+
+        ``on_logits(logits, requests, draws)`` sees the float32 logits (on the device) from which each step's tokens
+        are drawn, row i belonging to request ``requests[i]`` at its ``draws[i]``-th token; steps then run one by one.
 
         ``temperature == 0`` decodes greedily.  Stop tokens default to the configuration's
         ``eos_token_id``; a stop token is not part of the output.
@@ -91,9 +94,13 @@ class LLM:
         self._ensure_cache(sum((n + 63) // 64 * 64 for n in batch))
         stops = self.model.spec.stop_token_ids if stop_token_ids is None else stop_token_ids
         t0 = time.perf_counter()
-        out = generate(self.engine, ids, max_new_tokens=max_tokens,
-                       sampling=SamplingParams(temperature, top_p, top_k, seed), stop_token_ids=stops,
-                       on_token=on_token)
+        self.engine.logits_hook = on_logits
+        try:
+            out = generate(self.engine, ids, max_new_tokens=max_tokens,
+                           sampling=SamplingParams(temperature, top_p, top_k, seed), stop_token_ids=stops,
+                           on_token=on_token)
+        finally:
+            self.engine.logits_hook = None
         torch.cuda.synchronize(self.model.device)
         dt = time.perf_counter() - t0
         n_out = sum(len(r.tokens) for r in out)

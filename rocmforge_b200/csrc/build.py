@@ -32,6 +32,7 @@ MODULES: Dict[str, List[str]] = {
     "gemm_simt": ["gemm_simt.cu", "common.cuh"],
     "attention_generic": ["attention_generic.cu", "common.cuh"],
     "sampling": ["sampling.cu", "common.cuh"],
+    "random_fill": ["random_fill.cu", "common.cuh"],
     "gemm_tcgen05": ["gemm_tcgen05.cu", "tcgen05_common.cuh", "common.cuh"],
     # has one CTA load a tile for its whole cluster (this GPU's memory only): a file of its own, left out of
     # multi-GPU runs; the package works without it

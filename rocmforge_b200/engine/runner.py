@@ -23,6 +23,8 @@ class ModelEngine(StepEngine):
         self.sampler = DeviceSampler(model.device)
         self._calls = 0
         self._host_ids = None            # pinned buffer for the sampled ids
+        self.logits_hook = None          # callable(logits [rows, vocab] on the device, requests, draws): the caller looks
+                                         # at every step's logits; steps then run one by one, outside graphs
         self.decode_runner = None
         if model.options.decode_graphs:
             from .graph import DecodeRunner
@@ -62,7 +64,7 @@ class ModelEngine(StepEngine):
 
     def run(self, slots, tokens, requests, draws, sampling: SamplingParams, final: bool = False) -> List[int]:
         decode = all(len(t) == 1 for t in tokens)
-        if decode and self.decode_runner is not None:
+        if decode and self.decode_runner is not None and self.logits_hook is None:
             # replayed from a graph with the sampler inside, one step ahead of the host
             ids = self.decode_runner.step_ids(slots, [t[0] for t in tokens], sampling, requests, draws, more=not final)
         else:
@@ -70,6 +72,8 @@ class ModelEngine(StepEngine):
                 self.decode_runner.drop_ahead()        # a step launched for sequences that all stopped
             reqs = [StepRequest(s, t, [len(t) - 1]) for s, t in zip(slots, tokens)]
             logits = self.model.step(self.cache, reqs)
+            if self.logits_hook is not None:
+                self.logits_hook(logits, list(requests), list(draws))
             ids = self._to_host(self.sampler.sample(logits, sampling, requests, draws))
         self._calls += 1
         if self._calls % 64 == 0:          # a separate small read: not on every step

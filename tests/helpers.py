@@ -48,13 +48,13 @@ def config_dict(cfg: dict) -> dict:
     return {k: v for k, v in cfg.items() if k != "seed"}
 
 
-def write_tiny(cfg: dict, folder: str, dtype: str = "float32") -> None:
+def write_tiny(cfg: dict, folder: str, dtype: str = "float32", device: str = "cpu") -> None:
     import rocmforge_b200 as rf
     from rocmforge_b200.config import Qwen2Config, architecture_for
     c = Qwen2Config.from_dict(config_dict(cfg))
     spec = architecture_for(c.architecture).build(c)
     dt = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
-    rf.write_model_folder(folder, c.to_dict(), spec.param_specs(), cfg["seed"], dt)
+    rf.write_model_folder(folder, c.to_dict(), spec.param_specs(), cfg["seed"], dt, device=device)
 
 
 def random_tokens(vocab: int, n: int, seed: int):

@@ -53,6 +53,20 @@ def test_cli_generates_and_reports(folders):
     want, _ = S.generate(lambda t: p.logits(t)[-1], prompt, max_tokens=5)
     assert got == want
     assert "Prefill:" in out.stderr and "tokens in" in out.stderr and "ended by max_tokens" in out.stderr
+    # --debug as the reference means it: ten candidates after the prompt, five for each of the first steps, the
+    # first candidate being the token that greedy decoding took
+    assert "[Prompt logits]" in out.stderr and "Top-10 tokens" in out.stderr and "[Token 3 logits]" in out.stderr
+    assert "[Token 4 logits]" not in out.stderr
+    firsts = [int(l.split("id=")[1]) for l in out.stderr.splitlines() if l.strip().startswith("1.")]
+    assert firsts == want[:4]
+    # random prompts by length, graphs off, statistics as JSON
+    js = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "rocmforge"), "--model", folders("A"), "--dtype",
+                         "float32", "--prompt-len", "9", "--prompt-len", "20", "--max-tokens", "4", "--temperature", "0",
+                         "--stop-ids", "", "--no-graph", "--stats-json", "-"], capture_output=True, text=True)
+    assert js.returncode == 0, js.stderr
+    stats = json.loads(js.stdout.strip().splitlines()[-1])
+    assert stats["prompt_tokens"] == 29 and stats["generated_tokens"] == 8 and stats["graphs"] is False
+    assert [r["reason"] for r in stats["results"]] == ["max_tokens", "max_tokens"]
     bad = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "rocmforge"), "--model", folders("A"),
                           "--prompt-ids", "999"], capture_output=True, text=True)
     assert bad.returncode == 1 and "Error:" in bad.stderr

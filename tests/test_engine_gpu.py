@@ -320,6 +320,21 @@ def check_tokens_up_to_near_ties(p, prompt, got, want):
         toks.append(g)
 
 
+def check_sampled_up_to_swapped_neighbours(p, prompt, got, want, temperature):
+    """Sampled tokens must be the plain sampler's.  The sampler walks the tokens in the order of their probabilities;
+    two tokens whose probabilities agree to seven digits may stand in either order, and a draw that lands on them then
+    picks the one or the other: up to the first such place the tokens must agree, and there the two candidates must
+    be such a pair."""
+    toks = list(prompt)
+    for k, (g, w) in enumerate(zip(got, want)):
+        if g != w:
+            pr = torch.softmax(p.logits(toks)[-1].double() / temperature, dim=0)
+            assert abs(float(pr[g] - pr[w])) < 1e-6 * float(pr[w]), f"token {k}: {g} instead of {w} without a tie in the order"
+            return
+        toks.append(g)
+    assert len(got) == len(want)
+
+
 def test_sampled_generation_follows_the_plain_sampler(folders):
     """Tiny B, temperature 0.8, seeded: a batch of 4 with prompt lengths 1/7/16/31, 6 steps."""
     import rocmforge_b200 as rf
@@ -332,7 +347,7 @@ def test_sampled_generation_follows_the_plain_sampler(folders):
         for i, (pr, r) in enumerate(zip(prompts, out)):
             want, _ = S.generate(lambda t: p.logits(t)[-1].float(), pr, max_tokens=6, seed=1, request=i,
                                  top_k=kw.get("top_k", 0), temperature=kw["temperature"], top_p=kw["top_p"])
-            assert r.tokens == want, f"request {i} with {kw}"
+            check_sampled_up_to_swapped_neighbours(p, pr, r.tokens, want, kw["temperature"])
     # a request's draws do not depend on its neighbours
     alone = llm.generate(prompts[:1], max_tokens=6, seed=1, temperature=0.8, top_p=1.0, stop_token_ids=[])
     both = llm.generate(prompts[:2], max_tokens=6, seed=1, temperature=0.8, top_p=1.0, stop_token_ids=[])

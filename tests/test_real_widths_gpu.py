@@ -42,7 +42,7 @@ def pair(name, tmp_path_factory):
     if name not in _made:
         import rocmforge_b200 as rf
         folder = str(tmp_path_factory.mktemp(f"widths_{name.replace('.', '_')}"))
-        write_tiny(WIDTHS[name], folder, "bfloat16")
+        write_tiny(WIDTHS[name], folder, "bfloat16", device="cuda:0")      # the same values as on the host, in seconds
         plain = PlainModel(folder, as_stored=True, device="cuda:0")
         _made.clear()                                   # one pair at a time on the device
         torch.cuda.empty_cache()

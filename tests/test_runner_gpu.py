@@ -5,7 +5,8 @@ import torch
 
 from helpers import CONFIGS, assert_logits_close, random_tokens
 from plain import sampling_plain as S
-from test_engine_gpu import check_tokens_up_to_near_ties, engine, plain, poison_free_pages
+from test_engine_gpu import (check_sampled_up_to_swapped_neighbours, check_tokens_up_to_near_ties, engine, plain,
+                             poison_free_pages)
 
 pytestmark = pytest.mark.gpu
 
@@ -169,6 +170,9 @@ def test_sampled_steps_inside_the_graph_follow_the_plain_sampler(folders):
             want, reason = S.generate(lambda t: p.logits(t)[-1].float(), pr, max_tokens=25, seed=5, request=i,
                                       stop_ids=(7, 11, 13), top_k=kw.get("top_k", 0), temperature=kw["temperature"],
                                       top_p=kw["top_p"])
-            assert r.tokens == want and r.reason == reason, f"request {i} with {kw}"
+            if r.tokens == want:
+                assert r.reason == reason, f"request {i} with {kw}"
+            else:
+                check_sampled_up_to_swapped_neighbours(p, pr, r.tokens, want, kw["temperature"])
     assert llm.engine.decode_runner.launched_ahead > 0
     assert llm.cache.live_slots == 0 and all(f == llm.cache.n_pages for f in llm.cache.free_pages())

@@ -45,6 +45,48 @@ def test_random_weights_follow_seed_and_scheme(tmp_path):
     assert "lm_head.weight" in set(a.names())                  # untied: stored
 
 
+def test_random_values_depend_on_seed_name_and_index_alone():
+    """The generator behind the random-weights mode: an element is a function of (seed, tensor name, index), so it
+    does not depend on the tensor's length, on how the work is cut into chunks, or on other tensors; the values are
+    close to normal with the asked deviation."""
+    from rocmforge_b200.weights.random_init import fill_normal_host, normal_table, tensor_key
+    key = tensor_key(7, "model.layers.3.mlp.up_proj.weight")
+    a = fill_normal_host(5000, key, 0.02, torch.float32)
+    assert torch.equal(a[:1234], fill_normal_host(1234, key, 0.02, torch.float32))
+    assert torch.equal(a, fill_normal_host(5000, key, 0.02, torch.float32, chunk=777))
+    assert not torch.equal(a, fill_normal_host(5000, tensor_key(8, "model.layers.3.mlp.up_proj.weight"), 0.02, torch.float32))
+    assert not torch.equal(a, fill_normal_host(5000, tensor_key(7, "model.layers.4.mlp.up_proj.weight"), 0.02, torch.float32))
+    assert torch.equal(a.bfloat16(), fill_normal_host(5000, key, 0.02, torch.bfloat16))
+    big = fill_normal_host(1 << 20, key, 0.5, torch.float32).double()
+    assert abs(float(big.mean())) < 3e-3 and abs(float(big.std()) - 0.5) < 3e-3
+    assert abs(float((big ** 4).mean()) / 0.5 ** 4 - 3.0) < 0.05          # the fourth moment of a normal variable
+    t = normal_table()
+    assert t.shape == (65537,) and torch.all(t[1:] > t[:-1]) and float(t[32768]) == 0.0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_model_made_on_the_device_equals_the_folder_written_on_the_host(tmp_path, dtype):
+    """``Model.random(config, seed)`` fills its tensors with a kernel, ``write_model_folder`` with host arithmetic:
+    the same bits, tensor by tensor (what the parts fuse at load time is compared after the same fusion)."""
+    import rocmforge_b200 as rf
+    c, spec = spec_of("D")
+    write_model_folder(str(tmp_path), c.to_dict(), spec.param_specs(), 5, dtype)
+    a = rf.Model.from_folder(str(tmp_path), dtype=dtype)
+    b = rf.Model.random(c, seed=5, dtype=dtype)
+    for (pa, xa), (pb, xb) in zip(a.spec.named_parts().items(), b.spec.named_parts().items()):
+        for attr in ("weight", "qkv", "o", "gate_up", "down", "linear"):
+            ta, tb = getattr(xa, attr, None), getattr(xb, attr, None)
+            ta, tb = getattr(ta, "weight", ta), getattr(tb, "weight", tb)
+            if isinstance(ta, torch.Tensor):
+                assert torch.equal(ta, tb), f"{pa}{attr} differs between the folder and the device-made model"
+    toks = list(range(40))
+    ca, cb = a.new_cache(max_tokens=64), b.new_cache(max_tokens=64)
+    la = a.step(ca, [rf.StepRequest(ca.alloc_slot(), toks, [39])])
+    lb = b.step(cb, [rf.StepRequest(cb.alloc_slot(), toks, [39])])
+    assert torch.equal(la, lb)
+
+
 def test_load_keeps_dtypes(folders):
     c, spec = spec_of("A")
     got = load_folder(folders("A", "bfloat16"), spec.param_specs(), torch.bfloat16, "cpu")
