@@ -22,16 +22,20 @@
 // Every wait on an mbarrier is bounded: when it runs out the CTA records a code in the
 // global status word, all roles leave their loops, tensor memory is freed and the kernel
 // returns; the host reads the word and raises.
+#include <type_traits>
 #include "tcgen05_common.cuh"
 
 // ---------------------------------------------------------------- the kernel
 // SWAP = false: map A = X (rows are tokens), map B = W;  SWAP = true: map A = W, map B = X.
-// NORM = true (weights-as-rows only): the variant that applies a deferred norm to its input rows (p.norm.ss_in)
+// NORM = true (weights-as-rows only): the variant that applies a deferred norm to its input rows (pn.ss_in)
 // and/or finishes the residual update and prepares the next norm (EPI_RESNORM); it needs more registers, so the
 // ordinary products do not carry it.
 template <int BN, bool SWAP, int STAGES, bool NORM = false>
 __global__ void __launch_bounds__(TC_THREADS, SWAP ? 2 : 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p,
+               typename std::conditional<NORM, TcNorm, TcNoNorm>::type norm_arg) {
+    // the variant without the norm never looks at this (every use below sits behind ``NORM &&``)
+    const TcNorm& pn = *reinterpret_cast<const TcNorm*>(&norm_arg);
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2;
     constexpr uint32_t B_BYTES = BN * TC_BK * 2;
     constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
@@ -131,7 +135,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // ---------------- epilogue: four warps, one quarter of the 128 lanes each
         const int quarter = warp & 3;
         pdl_wait();                                      // the output may still be read by the kernel before us
-        if (NORM && p.norm.ss_in) {
+        if (NORM && pn.ss_in) {
             // the input's norm was left unfinished by the product before us: 1 / RMS of each token of this tile, from
             // the tiles' sums of squares in index order
             const int t = threadIdx.x - 64;
@@ -139,8 +143,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const int m = tile_b * BN + t;
                 float ss = 0.f;
                 if (m < p.M)
-                    for (int i = 0; i < p.norm.ss_in_tiles; ++i) ss += p.norm.ss_in[(size_t)i * p.norm.ss_in_stride + m];
-                rstd_s[t] = rsqrtf(ss * p.norm.ss_inv_width + p.norm.ss_eps);
+                    for (int i = 0; i < pn.ss_in_tiles; ++i) ss += pn.ss_in[(size_t)i * pn.ss_in_stride + m];
+                rstd_s[t] = rsqrtf(ss * pn.ss_inv_width + pn.ss_eps);
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
         }
@@ -163,7 +167,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const int n = row_a, m0 = tile_b * BN + c0;
                     const float b = (p.bias && n < p.N && p.mode != EPI_RESNORM) ? load_vec(p.bias, p.bias_is_f32, n) : 0.f;
                     if (m0 >= p.M) break;                // the tile's other columns are padding, not tokens
-                    if (NORM && p.norm.ss_in) {
+                    if (NORM && pn.ss_in) {
 #pragma unroll
                         for (int j = 0; j < CH; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * rstd_s[c0 + j]);
                     }
@@ -204,7 +208,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             __threadfence();                                             // this split's partial sums are visible device-wide
             asm volatile("bar.sync 1, 128;" ::: "memory");
             if (threadIdx.x == 64) {
-                int* ctr = p.norm.counters + tile_a * gridDim.x + tile_b;
+                int* ctr = pn.counters + tile_a * gridDim.x + tile_b;
                 const int seen = atomicAdd(ctr, 1);
                 last_split = (seen == (int)gridDim.z - 1) && !abort_flag;
                 if (seen == (int)gridDim.z - 1) *ctr = 0;                // zero again for the next launch
@@ -222,7 +226,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 for (int q = 0; q < 4; ++q) {
                     const bool okq = n4 + q < p.N;
                     bv[q] = (p.bias && okq) ? load_vec(p.bias, p.bias_is_f32, n4 + q) : 0.f;
-                    wv[q] = okq ? load_vec(p.norm.norm_w, p.norm.norm_w_is_f32, n4 + q) : 0.f;
+                    wv[q] = okq ? load_vec(pn.norm_w, pn.norm_w_is_f32, n4 + q) : 0.f;
                 }
                 constexpr int TOK = 2;                                   // tokens of a warp in flight at once
                 for (int j0 = quarter * TOK; j0 < BN && m0 + j0 < p.M; j0 += 4 * TOK) {
@@ -231,7 +235,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                         for (int t = 0; t < TOK; ++t) {
                             const int m = m0 + j0 + t;
-                            acc[t] = m < p.M ? *reinterpret_cast<const float4*>(p.norm.resid + (size_t)m * p.ldo + n4)
+                            acc[t] = m < p.M ? *reinterpret_cast<const float4*>(pn.resid + (size_t)m * p.ldo + n4)
                                              : make_float4(0.f, 0.f, 0.f, 0.f);
                         }
                         for (int s0 = 0; s0 < S; s0 += 8) {              // eight splits of each token in flight at once
@@ -266,7 +270,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                 for (int q = 0; q < 4; ++q)
                                     if (n4 + q < p.N) {
                                         const size_t o = (size_t)m * p.ldo + n4 + q;
-                                        a[q] = p.norm.resid[o];
+                                        a[q] = pn.resid[o];
                                         for (int s2 = 0; s2 < S; ++s2) a[q] += __ldcg(part + (size_t)s2 * p.partial_stride + o);
                                     }
                             acc[t] = make_float4(a[0], a[1], a[2], a[3]);
@@ -280,20 +284,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         const size_t o = (size_t)m * p.ldo + n4;
                         float sq = 0.f;
                         if (vec) {
-                            *reinterpret_cast<float4*>(p.norm.resid + o) = make_float4(v[0], v[1], v[2], v[3]);
-                            *reinterpret_cast<uint2*>(p.norm.normed + o) =
+                            *reinterpret_cast<float4*>(pn.resid + o) = make_float4(v[0], v[1], v[2], v[3]);
+                            *reinterpret_cast<uint2*>(pn.normed + o) =
                                 make_uint2(pack_bf16x2(v[0] * wv[0], v[1] * wv[1]), pack_bf16x2(v[2] * wv[2], v[3] * wv[3]));
                             sq = (v[0] * v[0] + v[1] * v[1]) + (v[2] * v[2] + v[3] * v[3]);
                         } else {
                             for (int q = 0; q < 4; ++q)
                                 if (n4 + q < p.N) {
-                                    p.norm.resid[o + q] = v[q];
-                                    p.norm.normed[o + q] = __float2bfloat16_rn(v[q] * wv[q]);
+                                    pn.resid[o + q] = v[q];
+                                    pn.normed[o + q] = __float2bfloat16_rn(v[q] * wv[q]);
                                     sq += v[q] * v[q];
                                 }
                         }
                         sq = warp_sum(sq);
-                        if (lane == 0) p.norm.ss_out[(size_t)tile_a * p.norm.ss_out_stride + m] = sq;
+                        if (lane == 0) pn.ss_out[(size_t)tile_a * pn.ss_out_stride + m] = sq;
                     }
                 }
             }
@@ -310,7 +314,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
 // ---------------------------------------------------------------- host side
 template <int BN, bool SWAP, int STAGES, bool NORM = false>
-static int launch_cfg(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, dim3 grid, cudaStream_t st) {
+static int launch_cfg(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, dim3 grid, cudaStream_t st,
+                      const TcNorm* norm = nullptr) {
     constexpr size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + (2 * STAGES + 1) * 8 + 16 + 1024;
     static bool configured = false;
     if (!configured) {
@@ -319,7 +324,9 @@ static int launch_cfg(const CUtensorMap& ma, const CUtensorMap& mb, const TcPara
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    rf_launch(gemm_tc_kernel<BN, SWAP, STAGES, NORM>, grid, dim3(TC_THREADS), smem, st, ma, mb, p);
+    typename std::conditional<NORM, TcNorm, TcNoNorm>::type extra{};
+    if constexpr (NORM) extra = *norm;
+    rf_launch(gemm_tc_kernel<BN, SWAP, STAGES, NORM>, grid, dim3(TC_THREADS), smem, st, ma, mb, p, extra);
     RF_LAUNCH_CHECK();
     return 0;
 }
@@ -340,7 +347,7 @@ int rf_gemm_tc(const void* X, int ldx, const void* W, const void* bias, int bias
     if (!rf_gemm_tc_supported(M, N, K, mode) || mode == EPI_PARTIAL || mode == EPI_RESNORM) return RF_ERR_UNSUPPORTED;
     CUtensorMap ma, mb;
     int e;
-    TcParams p{out, bias, bias_is_f32, M, N, K, ldo, mode, (K + TC_BK - 1) / TC_BK, 0, status, 1, {}};
+    TcParams p{out, bias, bias_is_f32, M, N, K, ldo, mode, (K + TC_BK - 1) / TC_BK, 0, status, 1};
     if (N > 128) {
         if ((e = make_map(&ma, X, M, K, ldx, TC_BM)) || (e = make_map(&mb, W, N, K, K, 256))) return e;
         dim3 grid((N + 255) / 256, (M + TC_BM - 1) / TC_BM, 1);
@@ -373,8 +380,8 @@ int rf_gemm_tc_skinny_ex(const void* X, int ldx, const void* W, const void* bias
     const int kb = (K + TC_BK - 1) / TC_BK;
     const int per = (kb + splits - 1) / splits;
     if ((splits - 1) * per >= kb) return RF_ERR_BAD_ARG;          // an empty split would leave its partial unwritten
-    TcParams p{out, bias, bias_is_f32, M, N, K, ldo, mode, per, (long long)M * ldo, status, 1, {}};
-    p.norm = TcNorm{resid, norm_w, norm_w_is_f32, reinterpret_cast<__nv_bfloat16*>(normed), ss_out, ss_out_stride,
+    TcParams p{out, bias, bias_is_f32, M, N, K, ldo, mode, per, (long long)M * ldo, status, 1};
+    const TcNorm nrm = TcNorm{resid, norm_w, norm_w_is_f32, reinterpret_cast<__nv_bfloat16*>(normed), ss_out, ss_out_stride,
                     counters, ss_in, ss_in_tiles, ss_in_stride, ss_eps, 1.0f / (float)K};
     CUtensorMap ma, mb;
     int e;
@@ -386,10 +393,10 @@ int rf_gemm_tc_skinny_ex(const void* X, int ldx, const void* W, const void* bias
     // two CTAs with three 32 KB stages each, 5.09 ms a decode step of the 7B shape; one CTA with six
     // stages 6.46 ms; two tiles of 64 tokens sharing the weight tile through L2 5.65 ms.)
     if (ss_in || mode == EPI_RESNORM) {
-        if (bn == 16) return launch_cfg<16, true, 6, true>(ma, mb, p, grid, st);
-        if (bn == 32) return launch_cfg<32, true, 5, true>(ma, mb, p, grid, st);
-        if (bn == 64) return launch_cfg<64, true, 4, true>(ma, mb, p, grid, st);
-        return launch_cfg<128, true, 3, true>(ma, mb, p, grid, st);
+        if (bn == 16) return launch_cfg<16, true, 6, true>(ma, mb, p, grid, st, &nrm);
+        if (bn == 32) return launch_cfg<32, true, 5, true>(ma, mb, p, grid, st, &nrm);
+        if (bn == 64) return launch_cfg<64, true, 4, true>(ma, mb, p, grid, st, &nrm);
+        return launch_cfg<128, true, 3, true>(ma, mb, p, grid, st, &nrm);
     }
     if (bn == 16) return launch_cfg<16, true, 6>(ma, mb, p, grid, st);
     if (bn == 32) return launch_cfg<32, true, 5>(ma, mb, p, grid, st);

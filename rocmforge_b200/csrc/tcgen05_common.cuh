@@ -43,8 +43,12 @@ struct TcParams {
     long long partial_stride;   // elements between the partial sums of two splits
     int* status;            // device word: 0 = fine
     int splits;             // clustered kernel: K parts of the residual epilogue, added in order (1 = none)
-    TcNorm norm;            // weights-as-rows kernel only; zero elsewhere
 };
+// (TcNorm travels as a kernel parameter of its own, and only to the kernel variant that uses it.  Inside TcParams it
+// took the kernel's parameters from 328 to 416 bytes, and every product of few tokens then needed about 4 us longer:
+// measured on the 0.5B shape, a decode step of 1.14 ms became 1.45 ms; up to 384 bytes nothing changes, from 400 on
+// the time is lost.)
+struct TcNoNorm {};
 
 // ---------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
