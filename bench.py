@@ -438,6 +438,7 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prompt length of --only decode / ablate")
     ap.add_argument("--fused-norm-max", type=int, default=None,
                     help="--only runs: most tokens of a step for which products prepare the norm that follows them")
+    ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="--only prefill: tokens of the prompt")
     ap.add_argument("--seed", type=int, default=0)
     args = ap.parse_args()
     if args.impl == "reference":
@@ -475,8 +476,10 @@ def main():
             print(json.dumps(row))
         return 0
     if args.only == "prefill":
-        ms = prefill_rate(model, PREFILL_TOKENS, 2, args.seed + 2)
-        print(json.dumps({"only": "prefill", "layers": cfg.num_hidden_layers, "tokens": PREFILL_TOKENS, "ms": round(ms, 3)}))
+        ms = prefill_rate(model, args.prefill_tokens, 4, args.seed + 2)
+        print(json.dumps({"only": "prefill", "shape": args.shape, "layers": cfg.num_hidden_layers, "tokens": args.prefill_tokens,
+                          "ms": round(ms, 3),
+                          "frac": round(prefill_flops(cfg, args.prefill_tokens) / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}))
         return 0
     # the prompt step first, and few of them: a few steps of 25 ms are a burst, like the product the peak was measured
     # with (nine in a row run into the power cap and come out 5 % slower: that is the sustained figure's case)
