@@ -436,6 +436,7 @@ def main():
     ap.add_argument("--shape", choices=["7b", "0.5b", "14b"], default="7b",
                     help="layer sizes for --only decode / prefill / ablate (the full run always measures all three)")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prompt length of --only decode / ablate")
+    ap.add_argument("--fused-norm", action="store_true", help="--only runs: products of few tokens prepare the norm that follows")
     ap.add_argument("--fused-norm-max", type=int, default=None,
                     help="--only runs: most tokens of a step for which products prepare the norm that follows them")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="--only prefill: tokens of the prompt")
@@ -462,6 +463,8 @@ def main():
     cfg = Qwen2Config.from_dict(raw)
     V = cfg.vocab_size
     model = rf.Model.random(cfg, seed=args.seed, dtype=torch.bfloat16)
+    if args.only and args.fused_norm:
+        model.options.fused_norm = True
     if args.only and args.fused_norm_max is not None:
         model.options.fused_norm_max_tokens = args.fused_norm_max
 

@@ -47,7 +47,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
     __shared__ int abort_flag;
     __shared__ float rstd_s[NORM ? BN : 1];                    // 1 / RMS of this tile's tokens (deferred norm of the input)
-    __shared__ int last_split;
+    __shared__ float ss_w[NORM ? 4 * BN : 1];                  // EPI_RESNORM: the four epilogue warps' sums of squares
 
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -150,7 +150,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         const bool ok = mbar_wait(smem_u32(&bars[2 * STAGES]), 0, &abort_flag);
         tcgen05_fence_after();
-        if (ok && n_kb > 0) {
+        if (ok && n_kb > 0 && !(NORM && p.mode == EPI_RESNORM)) {
             const int row_a = tile_a * TC_BM + quarter * 32 + lane;        // index along map A's rows
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
             constexpr int CH = BN < 32 ? 16 : 32;
@@ -203,104 +203,80 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
             }
         }
-        if (NORM && p.mode == EPI_RESNORM) {
-            // ---- the split that arrives last at this output tile finishes the residual update and prepares the norm
-            __threadfence();                                             // this split's partial sums are visible device-wide
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (threadIdx.x == 64) {
-                int* ctr = pn.counters + tile_a * gridDim.x + tile_b;
-                const int seen = atomicAdd(ctr, 1);
-                last_split = (seen == (int)gridDim.z - 1) && !abort_flag;
-                if (seen == (int)gridDim.z - 1) *ctr = 0;                // zero again for the next launch
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (last_split) {
-                __threadfence();
-                // a warp takes whole tokens: lane l owns columns 4l .. 4l+3 of the tile, so a token's 128 columns are
-                // one 16-byte load per lane and per addend, all of them in flight before the first is used
-                const int m0 = tile_b * BN, n4 = tile_a * TC_BM + 4 * lane, S = (int)gridDim.z;
-                const float* part = reinterpret_cast<const float*>(p.out);
-                const bool vec = n4 + 3 < p.N && (p.ldo & 3) == 0;
-                float bv[4], wv[4];
+    }
+    if (NORM && p.mode == EPI_RESNORM) {
+        // ---- the K splits of an output tile are one thread-block cluster (along grid.z).  Every CTA owns BN / S of the
+        // tile's tokens: the others push their partial sums of those tokens into its shared memory, it adds them in
+        // rank order to the 32-bit stream and prepares the norm.  Nothing goes through global memory, and the order of
+        // the sum is the ranks', whatever the timing.
+        const int S = (int)gridDim.z, TS = BN / S;
+        uint32_t rank;
+        asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+        float* recv = reinterpret_cast<float*>(smem);                // [S senders][TS tokens][128 rows], where the ring lay
+        // 1. every CTA of the cluster has finished its products: its ring is free to receive
+        tcgen05_fence_before();
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        tcgen05_fence_after();
+        const int quarter = warp & 3, row = quarter * 32 + lane;
+        if (warp >= 2 && !abort_flag && n_kb > 0) {
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+            constexpr int CH = BN < 32 ? 16 : 32;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += CH) {
+                uint32_t r[32];
+                if (CH == 32) tcgen05_ld32(taddr + c0, r); else tcgen05_ld16(taddr + c0, r);
+                tcgen05_wait_ld();
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const bool okq = n4 + q < p.N;
-                    bv[q] = (p.bias && okq) ? load_vec(p.bias, p.bias_is_f32, n4 + q) : 0.f;
-                    wv[q] = okq ? load_vec(pn.norm_w, pn.norm_w_is_f32, n4 + q) : 0.f;
-                }
-                constexpr int TOK = 2;                                   // tokens of a warp in flight at once
-                for (int j0 = quarter * TOK; j0 < BN && m0 + j0 < p.M; j0 += 4 * TOK) {
-                    float4 acc[TOK];
-                    if (vec) {
-#pragma unroll
-                        for (int t = 0; t < TOK; ++t) {
-                            const int m = m0 + j0 + t;
-                            acc[t] = m < p.M ? *reinterpret_cast<const float4*>(pn.resid + (size_t)m * p.ldo + n4)
-                                             : make_float4(0.f, 0.f, 0.f, 0.f);
-                        }
-                        for (int s0 = 0; s0 < S; s0 += 8) {              // eight splits of each token in flight at once
-                            float4 add[TOK][8];
-#pragma unroll
-                            for (int t = 0; t < TOK; ++t) {
-                                const size_t o = (size_t)(m0 + j0 + t) * p.ldo + n4;
-                                if (m0 + j0 + t < p.M) {
-#pragma unroll
-                                    for (int s2 = 0; s2 < 8; ++s2)
-                                        if (s0 + s2 < S)
-                                            add[t][s2] = __ldcg(reinterpret_cast<const float4*>(part + (size_t)(s0 + s2) * p.partial_stride + o));
-                                }
-                            }
-#pragma unroll
-                            for (int t = 0; t < TOK; ++t)
-                                if (m0 + j0 + t < p.M) {
-#pragma unroll
-                                    for (int s2 = 0; s2 < 8; ++s2)       // splits in index order, whoever comes last
-                                        if (s0 + s2 < S) {
-                                            acc[t].x += add[t][s2].x; acc[t].y += add[t][s2].y;
-                                            acc[t].z += add[t][s2].z; acc[t].w += add[t][s2].w;
-                                        }
-                                }
-                        }
-                    } else {
-#pragma unroll
-                        for (int t = 0; t < TOK; ++t) {
-                            const int m = m0 + j0 + t;
-                            float a[4] = {0.f, 0.f, 0.f, 0.f};
-                            if (m < p.M)
-                                for (int q = 0; q < 4; ++q)
-                                    if (n4 + q < p.N) {
-                                        const size_t o = (size_t)m * p.ldo + n4 + q;
-                                        a[q] = pn.resid[o];
-                                        for (int s2 = 0; s2 < S; ++s2) a[q] += __ldcg(part + (size_t)s2 * p.partial_stride + o);
-                                    }
-                            acc[t] = make_float4(a[0], a[1], a[2], a[3]);
-                        }
-                    }
-#pragma unroll
-                    for (int t = 0; t < TOK; ++t) {
-                        const int m = m0 + j0 + t;
-                        if (m >= p.M) break;                             // uniform over the warp
-                        const float v[4] = {acc[t].x + bv[0], acc[t].y + bv[1], acc[t].z + bv[2], acc[t].w + bv[3]};
-                        const size_t o = (size_t)m * p.ldo + n4;
-                        float sq = 0.f;
-                        if (vec) {
-                            *reinterpret_cast<float4*>(pn.resid + o) = make_float4(v[0], v[1], v[2], v[3]);
-                            *reinterpret_cast<uint2*>(pn.normed + o) =
-                                make_uint2(pack_bf16x2(v[0] * wv[0], v[1] * wv[1]), pack_bf16x2(v[2] * wv[2], v[3] * wv[3]));
-                            sq = (v[0] * v[0] + v[1] * v[1]) + (v[2] * v[2] + v[3] * v[3]);
-                        } else {
-                            for (int q = 0; q < 4; ++q)
-                                if (n4 + q < p.N) {
-                                    pn.resid[o + q] = v[q];
-                                    pn.normed[o + q] = __float2bfloat16_rn(v[q] * wv[q]);
-                                    sq += v[q] * v[q];
-                                }
-                        }
-                        sq = warp_sum(sq);
-                        if (lane == 0) pn.ss_out[(size_t)tile_a * pn.ss_out_stride + m] = sq;
-                    }
+                for (int j = 0; j < CH; ++j) {
+                    const int tok = c0 + j, owner = tok / TS;
+                    float v = __uint_as_float(r[j]);
+                    if (pn.ss_in) v *= rstd_s[tok];
+                    uint32_t raddr;
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr)
+                                 : "r"(smem_u32(recv + ((size_t)(rank * TS + (tok - owner * TS)) * TC_BM + row))), "r"(owner));
+                    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(raddr), "f"(v) : "memory");
                 }
             }
+        }
+        // 2. every push has landed
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        if (warp >= 2) {
+            const int n = tile_a * TC_BM + row, m0 = tile_b * BN + (int)rank * TS;
+            const bool n_ok = n < p.N;
+            const float b = (p.bias && n_ok) ? load_vec(p.bias, p.bias_is_f32, n) : 0.f;
+            const float wn = n_ok ? load_vec(pn.norm_w, pn.norm_w_is_f32, n) : 0.f;
+            float* stream = reinterpret_cast<float*>(p.out);
+            for (int t0 = 0; t0 < TS; t0 += 8) {                         // eight tokens' stream values in flight at once
+                float hv[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int m = m0 + t0 + u;
+                    hv[u] = (t0 + u < TS && m < p.M && n_ok) ? stream[(size_t)m * p.ldo + n] : 0.f;
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int tk = t0 + u, m = m0 + tk;
+                    if (tk >= TS) break;                                 // uniform over the CTA
+                    float sq = 0.f;
+                    if (m < p.M && n_ok && !abort_flag) {
+                        const size_t o = (size_t)m * p.ldo + n;
+                        float v = hv[u];
+                        for (int s2 = 0; s2 < S; ++s2) v += recv[((size_t)s2 * TS + tk) * TC_BM + row];      // ranks in order
+                        v += b;
+                        stream[o] = v;
+                        pn.normed[o] = __float2bfloat16_rn(v * wn);
+                        sq = v * v;
+                    }
+                    sq = warp_sum(sq);
+                    if (lane == 0) ss_w[quarter * BN + tk] = sq;
+                }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            const int t = threadIdx.x - 64;
+            if (t < TS && m0 + t < p.M)
+                pn.ss_out[(size_t)tile_a * pn.ss_out_stride + m0 + t] = (ss_w[t] + ss_w[BN + t]) + (ss_w[2 * BN + t] + ss_w[3 * BN + t]);
         }
     }
     tcgen05_fence_before();
@@ -315,7 +291,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // ---------------------------------------------------------------- host side
 template <int BN, bool SWAP, int STAGES, bool NORM = false>
 static int launch_cfg(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, dim3 grid, cudaStream_t st,
-                      const TcNorm* norm = nullptr) {
+                      const TcNorm* norm = nullptr, int cluster_z = 1) {
     constexpr size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + (2 * STAGES + 1) * 8 + 16 + 1024;
     static bool configured = false;
     if (!configured) {
@@ -326,6 +302,24 @@ static int launch_cfg(const CUtensorMap& ma, const CUtensorMap& mb, const TcPara
     }
     typename std::conditional<NORM, TcNorm, TcNoNorm>::type extra{};
     if constexpr (NORM) extra = *norm;
+    if (cluster_z > 1) {                             // the K splits of a tile as one cluster
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(TC_THREADS);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = cluster_z;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = g_rf_pdl ? 2 : 1;
+        cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, SWAP, STAGES, NORM>, ma, mb, p, extra);
+        if (e != cudaSuccess) return (int)e;
+        RF_LAUNCH_CHECK();
+        return 0;
+    }
     rf_launch(gemm_tc_kernel<BN, SWAP, STAGES, NORM>, grid, dim3(TC_THREADS), smem, st, ma, mb, p, extra);
     RF_LAUNCH_CHECK();
     return 0;
@@ -365,24 +359,28 @@ int rf_gemm_tc(const void* X, int ldx, const void* W, const void* bias, int bias
 // ss_in (optional): the activations X are (residual stream * norm weight) of a norm that the product before left
 // unfinished; ss_in [ss_in_tiles][ss_in_stride] holds the tiles' sums of squares of the stream, and every output row m
 // is scaled by rsqrt(sum_t ss_in[t][m] / K + ss_eps).
-// Mode RESNORM: out is the [splits, M, N] scratch for the partial sums; resid [M, N] += their sum (+ bias), normed
-// [M, N] = resid * norm_w in bfloat16, ss_out [ceil(N/128)][ss_out_stride] = each weight tile's sum of resid^2 per
-// token; counters: ceil(N/128) * ceil(M/tile) ints, zero before the first launch and left zero.
+// Mode RESNORM (splits = 1, 2, 4 or 8: the splits of an output tile are one thread-block cluster and add their
+// partial sums through each other's shared memory): resid [M, N] += the product (+ bias), normed [M, N] = resid *
+// norm_w in bfloat16, ss_out [ceil(N/128)][ss_out_stride] = each weight tile's sum of resid^2 per token; out and
+// counters are not used.
 int rf_gemm_tc_skinny_ex(const void* X, int ldx, const void* W, const void* bias, int bias_is_f32, void* out, int ldo,
                          int M, int N, int K, int mode, int splits, const float* ss_in, int ss_in_tiles,
                          int ss_in_stride, float ss_eps, float* resid, const void* norm_w, int norm_w_is_f32,
                          void* normed, float* ss_out, int ss_out_stride, int* counters, int* status, cudaStream_t st) {
     if (!rf_gemm_tc_supported(M, N, K, mode) || M > 256 || splits < 1) return RF_ERR_UNSUPPORTED;
     if (splits > 1 && mode != EPI_PARTIAL && mode != EPI_RESNORM) return RF_ERR_BAD_ARG;
-    if (mode == EPI_RESNORM && (!resid || !norm_w || !normed || !ss_out || !counters || ldo != N || ss_out_stride < M))
+    if (mode == EPI_RESNORM && (!resid || !norm_w || !normed || !ss_out || ldo != N || ss_out_stride < M))
         return RF_ERR_BAD_ARG;
+    // the splits of a tile form a cluster whose CTAs share the tile's tokens: 1, 2, 4 or 8 of them
+    if (mode == EPI_RESNORM && splits != 1 && splits != 2 && splits != 4 && splits != 8) return RF_ERR_BAD_ARG;
     if (ss_in && (ss_in_tiles <= 0 || ss_in_stride < M)) return RF_ERR_BAD_ARG;
     const int kb = (K + TC_BK - 1) / TC_BK;
     const int per = (kb + splits - 1) / splits;
     if ((splits - 1) * per >= kb) return RF_ERR_BAD_ARG;          // an empty split would leave its partial unwritten
-    TcParams p{out, bias, bias_is_f32, M, N, K, ldo, mode, per, (long long)M * ldo, status, 1};
-    const TcNorm nrm = TcNorm{resid, norm_w, norm_w_is_f32, reinterpret_cast<__nv_bfloat16*>(normed), ss_out, ss_out_stride,
-                    counters, ss_in, ss_in_tiles, ss_in_stride, ss_eps, 1.0f / (float)K};
+    TcParams p{mode == EPI_RESNORM ? (void*)resid : out, bias, bias_is_f32, M, N, K, ldo, mode, per, (long long)M * ldo, status, 1};
+    const TcNorm nrm = TcNorm{norm_w, reinterpret_cast<__nv_bfloat16*>(normed), ss_out, ss_in, norm_w_is_f32, ss_out_stride,
+                              ss_in_tiles, ss_in_stride, ss_eps, 1.0f / (float)K};
+    static_assert(sizeof(TcParams) + sizeof(TcNorm) <= 128, "two tensor maps and these must stay within 384 bytes");
     CUtensorMap ma, mb;
     int e;
     const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
@@ -393,10 +391,11 @@ int rf_gemm_tc_skinny_ex(const void* X, int ldx, const void* W, const void* bias
     // two CTAs with three 32 KB stages each, 5.09 ms a decode step of the 7B shape; one CTA with six
     // stages 6.46 ms; two tiles of 64 tokens sharing the weight tile through L2 5.65 ms.)
     if (ss_in || mode == EPI_RESNORM) {
-        if (bn == 16) return launch_cfg<16, true, 6, true>(ma, mb, p, grid, st, &nrm);
-        if (bn == 32) return launch_cfg<32, true, 5, true>(ma, mb, p, grid, st, &nrm);
-        if (bn == 64) return launch_cfg<64, true, 4, true>(ma, mb, p, grid, st, &nrm);
-        return launch_cfg<128, true, 3, true>(ma, mb, p, grid, st, &nrm);
+        const int cz = mode == EPI_RESNORM ? splits : 1;
+        if (bn == 16) return launch_cfg<16, true, 6, true>(ma, mb, p, grid, st, &nrm, cz);
+        if (bn == 32) return launch_cfg<32, true, 5, true>(ma, mb, p, grid, st, &nrm, cz);
+        if (bn == 64) return launch_cfg<64, true, 4, true>(ma, mb, p, grid, st, &nrm, cz);
+        return launch_cfg<128, true, 3, true>(ma, mb, p, grid, st, &nrm, cz);
     }
     if (bn == 16) return launch_cfg<16, true, 6>(ma, mb, p, grid, st);
     if (bn == 32) return launch_cfg<32, true, 5>(ma, mb, p, grid, st);

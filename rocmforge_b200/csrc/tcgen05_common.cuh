@@ -14,20 +14,18 @@ enum { EPI_STORE = 0, EPI_F32 = 1, EPI_RESIDUAL = 2, EPI_SWIGLU = 3, EPI_PARTIAL
 
 // What the weights-as-rows kernel needs to finish a residual update and prepare the norm that follows it
 // (mode EPI_RESNORM), and to apply a norm that was prepared that way to its own input (ss_in).
-struct TcNorm {
-    // EPI_RESNORM: of the K splits of an output tile the one that arrives last adds their partial sums (in index
-    // order) and the bias into the residual stream, writes stream * norm weight in bfloat16 for the next product
-    // and the tile's share of every token's sum of squares
-    float* resid;               // [M, N] 32-bit residual stream, updated in place
+struct TcNorm {             // 56 bytes: with TcParams and two tensor maps the kernel's parameters are 384 bytes, no more
+    // EPI_RESNORM: the K splits of an output tile add their partial sums (in rank order) and the bias into the residual
+    // stream (TcParams.out: [M, N] float32, updated in place), and write stream * norm weight in bfloat16 for the next
+    // product and the tile's share of every token's sum of squares
     const void* norm_w;         // [N] weight of the norm that follows
-    int norm_w_is_f32;
     __nv_bfloat16* normed;      // [M, N] out: (stream after the update) * norm weight, not yet divided by the RMS
     float* ss_out;              // [ceil(N/128)][ss_out_stride] out: sum over the tile's columns of stream^2
-    int ss_out_stride;
-    int* counters;              // one per (weight tile, token tile): zero between launches
     // input side: this product's activations are stream * norm weight of a norm prepared as above; row m is
     // scaled by rsqrt(sum_t ss_in[t][m] * ss_inv_width + ss_eps) in the epilogue (the product is linear in it)
     const float* ss_in;         // null: the activations are already normalised
+    int norm_w_is_f32;
+    int ss_out_stride;
     int ss_in_tiles, ss_in_stride;
     float ss_eps, ss_inv_width;
 };

@@ -25,10 +25,11 @@ class Options:
     tcgen05_attention: bool = True       # prefill attention with tcgen05.mma (else the mma.sync kernel)
     clustered_decode: bool = True        # decode attention by clusters of CTAs (else one CTA per 128-key chunk)
     decode_graphs: bool = True           # replay decode steps from CUDA graphs in the generation loop
-    # few tokens: the product that updates the stream also prepares the norm that follows (no norm kernel).  Off: at
-    # the 7B shape the split that finishes an output tile last needs as long for the fence, the counter and the partial
-    # sums of its tile (o product 6.3 -> 11.0 us, down 22.9 -> 25.9 us at batch 8) as the two norm kernels took
-    # (7.6 us a layer): 2.92 ms a step against 2.91 ms; with 64 tokens, or the 19 splits of the 0.5B shape, it loses
+    # few tokens: the product that updates the stream also prepares the norm that follows (no norm kernel): its K splits
+    # form a thread-block cluster and add their partial sums through shared memory.  Off: two kernels fewer a layer, but
+    # the clusters start later than single CTAs do and end with two cluster barriers; measured per decode step, 7B shape:
+    # batch 1 2.73 against 2.76 ms, batch 8 2.86 against 2.80 ms, batch 64 3.70 against 3.52 ms; 0.5B shape, batch 64:
+    # 1.58 against 1.15 ms
     fused_norm: bool = False
     fused_norm_max_tokens: int = 32
 
@@ -99,7 +100,7 @@ class StepContext:
                     # the split that finishes last adds all partial sums into the stream and prepares the norm
                     stream.flush()
                     normed, ss = tc.gemm_tc_skinny_resnorm(x, w, bias, stream.h, deferred[0],
-                                                           splits=tc.split_k_for(w.shape[0], w.shape[1]), row_ss=row_ss)
+                                                           splits=tc.resnorm_splits(w.shape[0], w.shape[1]), row_ss=row_ss)
                     stream.prepared = (follows, ScaledRows(normed, ss, deferred[1], w.shape[0]))
                     return
                 splits = tc.split_k_for(w.shape[0], w.shape[1]) if bias is None else 1

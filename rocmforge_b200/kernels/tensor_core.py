@@ -216,27 +216,26 @@ def gemm_tc_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor
     return out
 
 
-_tile_counters = {}
-
-
-def tile_counters(device, n: int) -> torch.Tensor:
-    """Arrival counters of the fused residual + norm epilogue (one per output tile): zeroed once, left zeroed by every launch."""
-    need(n <= 1 << 16, f"resnorm: {n} output tiles exceed the counters of this library")
-    key = torch.device(device).index or 0
-    t = _tile_counters.get(key)
-    if t is None:              # one buffer of fixed size per device, never replaced: captured graphs keep its address
-        t = _tile_counters[key] = register_counters(torch.zeros((1 << 16,), dtype=torch.int32, device=device))
-    return t
+def resnorm_splits(N: int, K: int) -> int:
+    """K splits of the product that finishes the residual update itself: the splits of a tile are one thread-block
+    cluster, so a power of two up to 8, as near the ordinary rule as that allows; from N and K alone."""
+    want = split_k_for(N, K)
+    kb = (K + 63) // 64
+    s = 1
+    while s * 2 <= min(want, 8) and (s * 2 - 1) * ((kb + s * 2 - 1) // (s * 2)) < kb:
+        s *= 2
+    return s
 
 
 def gemm_tc_skinny_resnorm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], h: torch.Tensor,
                            norm_weight: torch.Tensor, splits: int = 1, row_ss=None):
     """h += x w^T (+ bias) for few tokens, and the next RMS norm prepared in the same launch.
 
-    The product is split over K as in mode PARTIAL; of the splits of an output tile the one that finishes last adds all
-    partial sums (in index order, so the result does not depend on which one that is) and the bias into the 32-bit
-    stream ``h`` [M, N], and writes ``normed`` [M, N] = h * norm_weight in bfloat16 and ``ss`` [ceil(N/128), M], each
-    weight tile's sum of h^2 per token.  Whoever multiplies ``normed`` by a matrix next scales its output rows by
+    The product is split over K; the ``splits`` (1, 2, 4 or 8) CTAs of an output tile form a thread-block cluster, each
+    owns a share of the tile's tokens, receives the others' partial sums of those tokens in its shared memory, adds
+    them in rank order (so the result does not depend on timing) and the bias into the 32-bit stream ``h`` [M, N], and
+    writes ``normed`` [M, N] = h * norm_weight in bfloat16 and ``ss`` [ceil(N/128), M], each weight tile's sum of h^2
+    per token.  Whoever multiplies ``normed`` by a matrix next scales its output rows by
     rsqrt(sum_t ss[t, m] / N + eps) (``row_ss`` of ``gemm_tc_skinny``), which completes the norm.  Returns (normed, ss)."""
     _common(x, w, bias, None)
     need_cuda(h, norm_weight)
@@ -246,16 +245,14 @@ def gemm_tc_skinny_resnorm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torc
     need(supported(M, N, K, RESNORM), f"tensor-core gemm: shape {M}x{N}x{K} is not supported")
     need(h.dtype == torch.float32 and tuple(h.shape) == (M, N) and h.is_contiguous(), "resnorm: h must be float32 [M, N]")
     need(norm_weight.shape == (N,) and norm_weight.dtype in (torch.float32, torch.bfloat16), "resnorm: norm weight must be [N]")
+    need(splits in (1, 2, 4, 8), "resnorm: 1, 2, 4 or 8 K splits (they form a thread-block cluster)")
     tiles = (N + 127) // 128
-    bn = 16 if M <= 16 else (32 if M <= 32 else (64 if M <= 64 else 128))
-    parts = torch.empty((splits, M, N), dtype=torch.float32, device=x.device)
     normed = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
     ss = torch.empty((tiles, M), dtype=torch.float32, device=x.device)
-    counters = tile_counters(x.device, tiles * ((M + bn - 1) // bn))
     f = _f("rf_gemm_tc_skinny_ex", *_EX_ARGS)
     ss_ptr, ss_tiles, ss_stride, eps = _row_ss_args(row_ss, M)
-    check(f(ptr(x), x.stride(0), ptr(w), ptr(bias), int(bias is not None and bias.dtype == torch.float32), ptr(parts),
+    check(f(ptr(x), x.stride(0), ptr(w), ptr(bias), int(bias is not None and bias.dtype == torch.float32), ptr(None),
             N, M, N, K, RESNORM, splits, ss_ptr, ss_tiles, ss_stride, eps, ptr(h), ptr(norm_weight),
-            int(norm_weight.dtype == torch.float32), ptr(normed), ptr(ss), ss.stride(0), ptr(counters),
+            int(norm_weight.dtype == torch.float32), ptr(normed), ptr(ss), ss.stride(0), ptr(None),
             ptr(status_word(x.device)), stream()), f"gemm_tc_skinny_resnorm ({M}x{N}x{K})")
     return normed, ss
