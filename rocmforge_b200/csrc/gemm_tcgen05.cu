@@ -31,7 +31,7 @@
 // and/or finishes the residual update and prepares the next norm (EPI_RESNORM); it needs more registers, so the
 // ordinary products do not carry it.
 template <int BN, bool SWAP, int STAGES, bool NORM = false>
-__global__ void __launch_bounds__(TC_THREADS, SWAP ? 2 : 1)
+__global__ void __launch_bounds__(TC_THREADS, SWAP ? (STAGES <= 4 && BN == 16 ? 3 : 2) : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p,
                typename std::conditional<NORM, TcNorm, TcNoNorm>::type norm_arg) {
     // the variant without the norm never looks at this (every use below sits behind ``NORM &&``)
@@ -386,8 +386,10 @@ int rf_gemm_tc_skinny_ex(const void* X, int ldx, const void* W, const void* bias
     const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
     if ((e = make_map(&ma, W, N, K, K, TC_BM)) || (e = make_map(&mb, X, M, K, ldx, bn))) return e;
     dim3 grid((M + bn - 1) / bn, (N + TC_BM - 1) / TC_BM, splits);      // token tiles fastest: they share a weight tile in L2
-    // stage counts chosen so that two CTAs share an SM: their pipelines overlap each other's
-    // start-up and epilogue, and 2 x stages x 16 KB of weight bytes are in flight per SM.  (128 tokens:
+    // stage counts chosen so that two CTAs share an SM (three with up to 16 tokens: 3 x 4 stages hold as many weight
+    // bytes as 2 x 6, and the third place takes a CTA of the next product while this one still runs: 2.791 against
+    // 2.802 ms a decode step of the 7B shape at batch 8, 2.737 against 2.756 ms at batch 1): their pipelines overlap each
+    // other's start-up and epilogue, and 2 x stages x 16 KB of weight bytes are in flight per SM.  (128 tokens:
     // two CTAs with three 32 KB stages each, 5.09 ms a decode step of the 7B shape; one CTA with six
     // stages 6.46 ms; two tiles of 64 tokens sharing the weight tile through L2 5.65 ms.)
     if (ss_in || mode == EPI_RESNORM) {
@@ -397,7 +399,7 @@ int rf_gemm_tc_skinny_ex(const void* X, int ldx, const void* W, const void* bias
         if (bn == 64) return launch_cfg<64, true, 4, true>(ma, mb, p, grid, st, &nrm, cz);
         return launch_cfg<128, true, 3, true>(ma, mb, p, grid, st, &nrm, cz);
     }
-    if (bn == 16) return launch_cfg<16, true, 6>(ma, mb, p, grid, st);
+    if (bn == 16) return launch_cfg<16, true, 4>(ma, mb, p, grid, st);
     if (bn == 32) return launch_cfg<32, true, 5>(ma, mb, p, grid, st);
     if (bn == 64) return launch_cfg<64, true, 4>(ma, mb, p, grid, st);
     return launch_cfg<128, true, 3>(ma, mb, p, grid, st);
