@@ -439,6 +439,7 @@ def main():
     ap.add_argument("--fused-norm", action="store_true", help="--only runs: products of few tokens prepare the norm that follows")
     ap.add_argument("--fused-norm-max", type=int, default=None,
                     help="--only runs: most tokens of a step for which products prepare the norm that follows them")
+    ap.add_argument("--dtype", choices=["bf16", "fp32"], default="bf16", help="--only decode / prefill: the bfloat16 or the true 32-bit path")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="--only prefill: tokens of the prompt")
     ap.add_argument("--seed", type=int, default=0)
     args = ap.parse_args()
@@ -462,7 +463,7 @@ def main():
         raw["num_hidden_layers"] = args.layers
     cfg = Qwen2Config.from_dict(raw)
     V = cfg.vocab_size
-    model = rf.Model.random(cfg, seed=args.seed, dtype=torch.bfloat16)
+    model = rf.Model.random(cfg, seed=args.seed, dtype=torch.float32 if (args.only and args.dtype == "fp32") else torch.bfloat16)
     if args.only and args.fused_norm:
         model.options.fused_norm = True
     if args.only and args.fused_norm_max is not None:
