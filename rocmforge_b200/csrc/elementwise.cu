@@ -23,6 +23,31 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
     for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = Cvt<T>::to_f32(row[i]);
 }
 
+// Four neighbouring elements as one access.
+template <typename T> struct Four;
+template <> struct Four<float> {
+    static __device__ __forceinline__ void load(const float* p, float* v) {
+        const float4 x = *reinterpret_cast<const float4*>(p);
+        v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float* v) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+};
+template <> struct Four<__nv_bfloat16> {
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* v) {
+        const uint2 x = *reinterpret_cast<const uint2*>(p);
+        v[0] = __uint_as_float(x.x << 16); v[1] = __uint_as_float(x.x & 0xffff0000u);
+        v[2] = __uint_as_float(x.y << 16); v[3] = __uint_as_float(x.y & 0xffff0000u);
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float* v) {
+        const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+        uint2 x;
+        x.x = *reinterpret_cast<const uint32_t*>(&a); x.y = *reinterpret_cast<const uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(p) = x;
+    }
+};
+
 // ---------------------------------------------------------------- add + RMSNorm
 // v = h[row] + sum_s pending[s][row];  y = v * rsqrt(mean(v^2) + eps) * w.
 // pending_kind: 0 none, 1 = n_pending 32-bit partial sums [S, T, H] (split-K outputs,
@@ -133,9 +158,8 @@ add_rmsnorm_vec_kernel(float* __restrict__ h, const void* __restrict__ pending, 
             }
             const float o0 = v[i].x * inv * w0, o1 = v[i].y * inv * w1;
             const float o2 = v[i].z * inv * w2, o3 = v[i].w * inv * w3;
-            T* o = yrow + 4 * c;
-            o[0] = Cvt<T>::from_f32(o0); o[1] = Cvt<T>::from_f32(o1);
-            o[2] = Cvt<T>::from_f32(o2); o[3] = Cvt<T>::from_f32(o3);
+            const float ov[4] = {o0, o1, o2, o3};
+            Four<T>::store(yrow + 4 * c, ov);              // one 16-byte (8-byte) store: the row is aligned for it
         }
     }
 }
@@ -218,30 +242,6 @@ __global__ void rope_kv_write_kernel(const void* __restrict__ src, int row_strid
 // token; a thread takes four neighbouring pair indices, computes their sines and cosines once and walks
 // over the heads in steps of blockDim.x / (hd/8) with loads and stores of four elements, so the
 // trigonometry is shared by the heads and every access is 8 or 16 bytes wide.
-template <typename T> struct Four;
-template <> struct Four<float> {
-    static __device__ __forceinline__ void load(const float* p, float* v) {
-        const float4 x = *reinterpret_cast<const float4*>(p);
-        v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
-    }
-    static __device__ __forceinline__ void store(float* p, const float* v) {
-        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
-    }
-};
-template <> struct Four<__nv_bfloat16> {
-    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* v) {
-        const uint2 x = *reinterpret_cast<const uint2*>(p);
-        v[0] = __uint_as_float(x.x << 16); v[1] = __uint_as_float(x.x & 0xffff0000u);
-        v[2] = __uint_as_float(x.y << 16); v[3] = __uint_as_float(x.y & 0xffff0000u);
-    }
-    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float* v) {
-        const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
-        uint2 x;
-        x.x = *reinterpret_cast<const uint32_t*>(&a); x.y = *reinterpret_cast<const uint32_t*>(&b);
-        *reinterpret_cast<uint2*>(p) = x;
-    }
-};
-
 template <typename T>
 __global__ void __launch_bounds__(256)
 rope_kv_write_rows_kernel(const T* __restrict__ src, int row_stride, T* __restrict__ q_out, int q_out_stride,
@@ -321,7 +321,7 @@ static int launch_add_rmsnorm(float* h, const void* pending, int kind, int n_pen
                               int n_rows, int H, cudaStream_t st) {
     if (n_rows <= 0) return 0;
     if (H % 4 == 0 && H <= 4 * 4 * 1024 && (pstride % 4) == 0 &&
-        !(reinterpret_cast<uintptr_t>(h) & 15) && !(reinterpret_cast<uintptr_t>(w) & 15) &&
+        !(reinterpret_cast<uintptr_t>(h) & 15) && !(reinterpret_cast<uintptr_t>(w) & 15) && !(reinterpret_cast<uintptr_t>(y) & 15) &&
         !(kind == 1 && (reinterpret_cast<uintptr_t>(pending) & 15))) {
         const int nvec = H / 4;
         // few rows (decode): one 16-byte vector per thread, the shortest chain per row;

@@ -78,3 +78,17 @@ def fn(module: str, name: str, argtypes):
     f.argtypes = argtypes
     f.restype = c_int
     return f
+
+
+_sm_count = {}
+
+
+def sm_count(device=None) -> int:
+    """Streaming multiprocessors of the device (148 on a B200): launch shapes are sized by it, not by a constant.
+    Without a CUDA device (host-side tests of the launch rules) the B200's number stands in."""
+    if not torch.cuda.is_available():
+        return 148
+    idx = torch.cuda.current_device() if device is None else (torch.device(device).index or 0)
+    if idx not in _sm_count:
+        _sm_count[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return _sm_count[idx]

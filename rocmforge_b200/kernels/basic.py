@@ -9,7 +9,7 @@ import functools
 
 import torch
 
-from ._ffi import (KernelError, c_float, c_int, c_ll, c_void_p, check, dtype_code, fn, need, need_cuda,
+from ._ffi import (KernelError, sm_count as device_sm_count, c_float, c_int, c_ll, c_void_p, check, dtype_code, fn, need, need_cuda,
                    ptr, stream)
 
 PAGE = 64      # tokens per cache page (RF_PAGE in csrc/common.cuh)
@@ -144,9 +144,10 @@ def swiglu(gu: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     return out
 
 
-def split_k_for_simt(N: int, K: int, sm_count: int = 148) -> int:
+def split_k_for_simt(N: int, K: int, sm_count: int | None = None) -> int:
     """K splits of a CUDA-core product of few tokens, from N and K alone (never from the batch): about two CTAs
     per SM, every split at least 4 blocks of 16."""
+    sm_count = sm_count or device_sm_count()
     tiles = (N + 127) // 128
     kb = (K + 15) // 16
     if tiles >= 2 * sm_count or kb < 8:
@@ -366,7 +367,7 @@ def decode_splits(B: int, n_kv_heads: int, longest: int | None = None, window: i
     3.54, 3.54, 3.72; batch 64 / 512: 3.76, 4.04."""
     pairs = max(1, B * n_kv_heads)
     s = 1
-    while s < 8 and pairs * s * 2 <= 128:
+    while s < 8 and pairs * s * 2 <= device_sm_count() * 7 // 8:          # 128 on the 148 SMs these numbers were taken on
         s *= 2
     if s == 8 and pairs > 8:
         s = 4
@@ -408,7 +409,7 @@ def attention_decode_warps(q: torch.Tensor, n_heads: int, n_kv_heads: int, head_
     if splits is None:
         splits = decode_splits(B, n_kv_heads)
     if warps is None:
-        warps = 8 if B * n_kv_heads * splits <= 148 else 4
+        warps = 8 if B * n_kv_heads * splits <= device_sm_count(q.device) else 4
     if out is None:
         out = torch.empty((B, n_heads * head_dim), dtype=torch.bfloat16, device=q.device)
     from .tensor_core import status_word

@@ -6,7 +6,7 @@ from typing import Optional
 
 import torch
 
-from ._ffi import KernelError, c_float, c_int, c_ll, c_void_p, check, fn, need, need_cuda, ptr, stream
+from ._ffi import KernelError, sm_count as device_sm_count, c_float, c_int, c_ll, c_void_p, check, fn, need, need_cuda, ptr, stream
 
 STORE, F32, RESIDUAL, SWIGLU, PARTIAL, RESNORM = 0, 1, 2, 3, 4, 5
 SKINNY_MAX_TOKENS = 128     # above it the large-M kernels stream the weights better (7B shape, decode step: 128 tokens
@@ -154,9 +154,10 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = Non
     return out
 
 
-def split_k_for(N: int, K: int, sm_count: int = 148) -> int:
+def split_k_for(N: int, K: int, sm_count: Optional[int] = None) -> int:
     """K splits of a skinny product, from N and K alone (never from the batch), so that about two
     CTAs per SM stream the weight and every split keeps at least 4 blocks of 64."""
+    sm_count = sm_count or device_sm_count()
     tiles = (N + 127) // 128
     kb = (K + 63) // 64
     if tiles >= 2 * sm_count or kb < 8:

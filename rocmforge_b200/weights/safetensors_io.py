@@ -123,6 +123,13 @@ class ModelFiles:
                 if name in self.entries:
                     raise SafetensorsError(f"tensor {name} is stored in both {self.entries[name].file} and {e.file}")
                 self.entries[name] = e
+        if os.path.exists(index):
+            # an index that names a tensor its shard does not hold is a stale index: say which shard
+            stale = sorted(f"{name} (index says {shard})" for name, shard in weight_map.items()
+                           if name not in self.files[shard].entries)
+            if stale:
+                raise SafetensorsError(f"{index} names tensors that their shards do not hold: " + ", ".join(stale[:8])
+                                       + (f" and {len(stale) - 8} more" if len(stale) > 8 else ""))
         self._by_name = {name: sf for sf in self.files.values() for name in sf.entries}
 
     def names(self) -> Iterable[str]:

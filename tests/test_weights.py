@@ -168,3 +168,14 @@ def test_shards_and_duplicates(tmp_path):
     write_safetensors(str(tmp_path / "b.safetensors"), [("x", torch.ones(2))])
     with pytest.raises(SafetensorsError):
         ModelFiles(str(tmp_path))
+
+
+def test_a_stale_index_names_the_shard(tmp_path):
+    """An index that sends a tensor to a shard which does not hold it: the error names tensor and shard."""
+    write_safetensors(str(tmp_path / "a.safetensors"), [("x", torch.ones(2))])
+    write_safetensors(str(tmp_path / "b.safetensors"), [("z", torch.zeros(1))])
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps(
+        {"weight_map": {"x": "a.safetensors", "y": "b.safetensors", "z": "b.safetensors"}}))
+    with pytest.raises(SafetensorsError) as e:
+        ModelFiles(str(tmp_path))
+    assert "y (index says b.safetensors)" in str(e.value)
