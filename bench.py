@@ -6,7 +6,7 @@
 Prints ONE JSON line.  ``value`` is decoded tokens per second at the given batch, timed on
 the device with CUDA events around K replayed decode steps whose sampled ids feed the next
 step; ``e2e`` is the same rate through ``rocmforge_b200.LLM.generate`` with token ids going
-in from the host and coming back to it every step; ``prefill`` is one step of 2,048 prompt
+in from the host and coming back to it every step (W warm-up steps, then K timed steps of one call); ``prefill`` is one step of 2,048 prompt
 tokens; ``roofline`` relates the decode step to the HBM bandwidth; ``points`` holds batch 1
 and batch 64.  maeddesg/ROCmForge publishes no number for this metric (its figures are for
 4-bit weights on an RX 9070 XT), so ``vs_baseline`` is null.
@@ -319,8 +319,10 @@ def ablation(model, batch, steps=32, prompt_len=PROMPT_LEN):
     return rows
 
 
-def e2e_rate(llm, prompts, steps, temperature=0.0, top_p=1.0):
-    """The same through LLM.generate: token ids from the host in, sampled ids back to the host, every step."""
+def e2e_rate(llm, prompts, steps, temperature=0.0, top_p=1.0, warmup=0):
+    """The same through LLM.generate: token ids from the host in, sampled ids back to the host, every step.  One call
+    generates warmup + steps + 1 tokens per request; the time of the last ``steps`` decode steps counts (the steps right
+    after a batch of prompts run at lower clocks for some tens of milliseconds: the power cap after the prompts' burst)."""
     import torch
     batch = len(prompts)
     stamps = []
@@ -330,8 +332,10 @@ def e2e_rate(llm, prompts, steps, temperature=0.0, top_p=1.0):
             stamps.append(time.perf_counter())
     llm.generate(prompts, max_tokens=min(steps, 8) + 1, temperature=temperature, top_p=top_p, stop_token_ids=[])     # warm-up, graphs
     stamps.clear()
-    out = llm.generate(prompts, max_tokens=steps + 1, temperature=temperature, top_p=top_p, stop_token_ids=[], on_token=on_token)
+    out = llm.generate(prompts, max_tokens=warmup + steps + 1, temperature=temperature, top_p=top_p, stop_token_ids=[],
+                       on_token=on_token)
     torch.cuda.synchronize()
+    stamps = stamps[warmup:]
     n = len(stamps) - 1
     dt = stamps[-1] - stamps[0]
     from rocmforge_b200.engine.batch import StepBatch
@@ -385,7 +389,7 @@ def other_shapes(pk, seed, only=None):
             out[key + "_ms_per_step"] = round(r["ms_per_step"], 4)
             out[key + "_hbm_frac"] = round(step_bytes(cfg, 64, r["mean_ctx"], elem) / (r["ms_per_step"] / 1e3) / 1e9 / hbm, 4)
             llm = rf.LLM(model, cache_tokens=sum((len(p) + 256 + 80) // 64 * 64 for p in prompts), max_batch=64)
-            out[key + "_e2e_tok_s"] = round(e2e_rate(llm, prompts, 128 if elem == 2 else 32)["value"], 1)
+            out[key + "_e2e_tok_s"] = round(e2e_rate(llm, prompts, 128 if elem == 2 else 32, warmup=8)["value"], 1)
             del llm
             if elem == 4:
                 # the 32-bit products run on the CUDA cores: 148 SMs x 128 lanes x 2 flops at the highest SM clock
@@ -492,11 +496,11 @@ def main():
     sampler.start()
     main_run = decode_rate(model, random_prompts(args.batch, PROMPT_LEN, V, args.seed), args.steps, warmup)
     clocks = sampler.summary(main_run["t0"], main_run["t1"])
-    llm = rf.LLM(model, cache_tokens=args.batch * (PROMPT_LEN + args.steps + 80), max_batch=args.batch)
-    e2e = e2e_rate(llm, random_prompts(args.batch, PROMPT_LEN, V, args.seed + 1), args.steps)
+    llm = rf.LLM(model, cache_tokens=args.batch * (PROMPT_LEN + warmup + args.steps + 80), max_batch=args.batch)
+    e2e = e2e_rate(llm, random_prompts(args.batch, PROMPT_LEN, V, args.seed + 1), args.steps, warmup=warmup)
     # the reference's own default is sampled decoding (temperature 1.0, top-p 0.9): the same loop with the device sampler
     sampled = e2e_rate(llm, random_prompts(args.batch, PROMPT_LEN, V, args.seed + 5), max(args.steps // 2, 16),
-                       temperature=1.0, top_p=0.9)
+                       temperature=1.0, top_p=0.9, warmup=warmup)
     llm.cache = llm.engine = None
     del llm
     torch.cuda.empty_cache()
