@@ -361,12 +361,11 @@ int rf_gemm_tc(const void* X, int ldx, const void* W, const void* bias, int bias
 // is scaled by rsqrt(sum_t ss_in[t][m] / K + ss_eps).
 // Mode RESNORM (splits = 1, 2, 4 or 8: the splits of an output tile are one thread-block cluster and add their
 // partial sums through each other's shared memory): resid [M, N] += the product (+ bias), normed [M, N] = resid *
-// norm_w in bfloat16, ss_out [ceil(N/128)][ss_out_stride] = each weight tile's sum of resid^2 per token; out and
-// counters are not used.
+// norm_w in bfloat16, ss_out [ceil(N/128)][ss_out_stride] = each weight tile's sum of resid^2 per token; out is not used.
 int rf_gemm_tc_skinny_ex(const void* X, int ldx, const void* W, const void* bias, int bias_is_f32, void* out, int ldo,
                          int M, int N, int K, int mode, int splits, const float* ss_in, int ss_in_tiles,
                          int ss_in_stride, float ss_eps, float* resid, const void* norm_w, int norm_w_is_f32,
-                         void* normed, float* ss_out, int ss_out_stride, int* counters, int* status, cudaStream_t st) {
+                         void* normed, float* ss_out, int ss_out_stride, int* status, cudaStream_t st) {
     if (!rf_gemm_tc_supported(M, N, K, mode) || M > 256 || splits < 1) return RF_ERR_UNSUPPORTED;
     if (splits > 1 && mode != EPI_PARTIAL && mode != EPI_RESNORM) return RF_ERR_BAD_ARG;
     if (mode == EPI_RESNORM && (!resid || !norm_w || !normed || !ss_out || ldo != N || ss_out_stride < M))
@@ -409,7 +408,7 @@ int rf_gemm_tc_skinny(const void* X, int ldx, const void* W, const void* bias, i
                       int M, int N, int K, int mode, int splits, int* status, cudaStream_t st) {
     if (mode == EPI_RESNORM) return RF_ERR_BAD_ARG;
     return rf_gemm_tc_skinny_ex(X, ldx, W, bias, bias_is_f32, out, ldo, M, N, K, mode, splits, nullptr, 0, 0, 0.f,
-                                nullptr, nullptr, 0, nullptr, nullptr, 0, nullptr, status, st);
+                                nullptr, nullptr, 0, nullptr, nullptr, 0, status, st);
 }
 
 }

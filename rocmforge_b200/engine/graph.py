@@ -28,7 +28,9 @@ class _Captured:
 
 
 class DecodeRunner:
-    """Runs one-token-per-sequence steps of a model over one cache, a graph per batch size."""
+    """Runs one-token-per-sequence steps of a model over one cache from CUDA graphs: ``logits`` (a graph per batch size
+    and context bucket, logits back), ``greedy_loop`` (ids fed back on the device, no host work between steps) and
+    ``step_ids`` (sampler inside the graph, one step ahead of the host: what the generation loop uses)."""
 
     def __init__(self, model, cache, max_batch: int = 1024):
         self.model = model
@@ -37,8 +39,6 @@ class DecodeRunner:
         self.desc = DeviceDescriptor(model.device, fixed=True, capacity=self.descriptor_words(max_batch))
         self.max_batch = max_batch
         self.graphs: Dict[tuple, _Captured] = {}
-        from ..sampling import DeviceSampler
-        self.sampler = DeviceSampler(model.device)
         self.replays = 0
         self._ready = None             # (slots, starts, packed descriptor without token ids, longest, cache epoch) of the next step
         self._flight = None            # a step launched before the host saw the ids of the step before it (see step_ids)

@@ -169,7 +169,7 @@ def split_k_for(N: int, K: int, sm_count: Optional[int] = None) -> int:
 
 
 _EX_ARGS = (c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-            c_void_p, c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p)
+            c_void_p, c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p)
 
 
 def _row_ss_args(row_ss, M):
@@ -213,7 +213,7 @@ def gemm_tc_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor
     ss_ptr, ss_tiles, ss_stride, eps = _row_ss_args(row_ss, M)
     check(f(ptr(x), x.stride(0), ptr(w), ptr(bias), int(bias is not None and bias.dtype == torch.float32), ptr(out),
             cols, M, N, K, mode, splits, ss_ptr, ss_tiles, ss_stride, eps, ptr(None), ptr(None), 0, ptr(None), ptr(None), 0,
-            ptr(None), ptr(status_word(x.device)), stream()), f"gemm_tc_skinny ({M}x{N}x{K}, rows scaled)")
+            ptr(status_word(x.device)), stream()), f"gemm_tc_skinny ({M}x{N}x{K}, rows scaled)")
     return out
 
 
@@ -254,6 +254,6 @@ def gemm_tc_skinny_resnorm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torc
     ss_ptr, ss_tiles, ss_stride, eps = _row_ss_args(row_ss, M)
     check(f(ptr(x), x.stride(0), ptr(w), ptr(bias), int(bias is not None and bias.dtype == torch.float32), ptr(None),
             N, M, N, K, RESNORM, splits, ss_ptr, ss_tiles, ss_stride, eps, ptr(h), ptr(norm_weight),
-            int(norm_weight.dtype == torch.float32), ptr(normed), ptr(ss), ss.stride(0), ptr(None),
+            int(norm_weight.dtype == torch.float32), ptr(normed), ptr(ss), ss.stride(0),
             ptr(status_word(x.device)), stream()), f"gemm_tc_skinny_resnorm ({M}x{N}x{K})")
     return normed, ss
