@@ -499,3 +499,141 @@ def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_plug_in():
     bare.forward(ctx, y, cache.view(0), stream)
     ref = P.causal_attention(q, k, v).reshape(T, nh * hd) @ pm["o_proj.weight"].double().cpu().t()
     torch.testing.assert_close(stream.flush().double().cpu(), ref, atol=2e-5, rtol=1e-4)
+
+
+def test_a_model_whose_layers_differ_in_mixer_window_rotation_and_width():
+    """One model, three kinds of layer: attention over a window of 24 keys with the whole head rotated; a mixer
+    with per-sequence state and no cache of keys (defined here); attention over all keys with half of every head
+    rotated; feed-forwards of three widths.  The cache gets a page group per need and a state tensor beside them;
+    whole prompts, chunks, single tokens, an unequal batch and replayed graphs all give the logits of the same
+    arithmetic written out."""
+    import rocmforge_b200 as rf
+    from rocmforge_b200.cache import StateRequest
+    from rocmforge_b200.config import register_architecture
+    from rocmforge_b200.engine import ModelSpec, ScheduleEntry
+    from rocmforge_b200.engine.graph import DecodeRunner
+    from rocmforge_b200.parts import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, Mixer, OutputHead, TokenEmbedding
+    from rocmforge_b200.weights import ParamSpec
+    from test_kernels_gpu import plain_rotation
+    H, nh, nkv, hd, V, eps, decay = 48, 4, 2, 16, 90, 1e-5, 0.7
+    inters, windows, rots = (40, 24, 72), (24, None, None), (16, None, 8)
+
+    @MIXERS.register("toy_leaky_state")
+    class LeakyState(Mixer):
+        """s_t = decay * s_{t-1} + y_t (the state is as wide as the model); update = W s_t."""
+        def __init__(self, hidden):
+            self.hidden = hidden
+
+        def param_specs(self):
+            return {"mix.weight": ParamSpec((self.hidden, self.hidden), std=0.2)}
+
+        def bind(self, params, compute_dtype):
+            self.w = params["mix.weight"]
+
+        def cache_request(self):
+            return StateRequest.of(s=((self.hidden,), torch.float32))
+
+        def forward(self, ctx, y, state, stream):
+            y32 = y.to(torch.float32)
+            rows = ctx.seq_slot.long()
+            if ctx.is_decode:
+                out = state["s"][rows] * decay + y32
+                state["s"].index_copy_(0, rows, out)
+            else:
+                out = torch.empty_like(y32)
+                b = ctx.host
+                for i, slot in enumerate(b.slots):
+                    s = state["s"][slot]
+                    for t in range(int(b.cu_q[i]), int(b.cu_q[i + 1])):
+                        s.mul_(decay).add_(y32[t])
+                        out[t] = s
+            ctx.matmul_residual(out.to(ctx.compute_dtype), self.w, None, stream)
+
+    @dataclass
+    class MixedConfig:
+        architecture: str
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(raw["architectures"][0])
+
+    def build(cfg):
+        blocks = []
+        for layer in range(3):
+            if layer == 1:
+                mixer = MIXERS.build("toy_leaky_state", hidden=H)
+            else:
+                mixer = MIXERS.build("gqa_attention", hidden=H, n_heads=nh, n_kv_heads=nkv, head_dim=hd, qkv_bias=layer == 0,
+                                     window=windows[layer],
+                                     position=POSITIONS.build("rope_neox", head_dim=hd, theta=500.0, rotary_dim=rots[layer]))
+            blocks.append(BLOCKS.build("prenorm", norm1=NORMS.build("rmsnorm", size=H, eps=eps), mixer=mixer,
+                                       norm2=NORMS.build("rmsnorm", size=H, eps=eps),
+                                       ffn=FEED_FORWARDS.build("gated_mlp", hidden=H, intermediate=inters[layer]),
+                                       names={"norm1": "n1.", "mixer": "mix.", "norm2": "n2.", "ffn": "ff."}))
+        return ModelSpec(config=cfg, embedding=TokenEmbedding(V, H), embedding_prefix="emb.", blocks=blocks,
+                         block_prefixes=[f"l{i}." for i in range(3)], final_norm=NORMS.build("rmsnorm", size=H, eps=eps),
+                         final_norm_prefix="fn.", head=OutputHead(V, H, tied_to="emb.weight"), head_prefix="head.",
+                         schedule=[ScheduleEntry(i) for i in range(3)], vocab_size=V, hidden_size=H, max_position=512)
+
+    register_architecture("ToyMixedLM", MixedConfig, build)
+    m = rf.Model.random(MixedConfig("ToyMixedLM"), seed=9, dtype=torch.float32)
+    cache = m.new_cache(max_tokens=64 * 8, max_slots=4)
+    assert sorted(g.window or 0 for g in cache.groups) == [0, 24] and sorted(cache.states) == [1]
+
+    # ---- the same arithmetic written out
+    dd = lambda t: t.double().cpu()
+    def plain_logits(tokens):
+        T = len(tokens)
+        pos = torch.arange(T)
+        x = dd(m.spec.embedding.weight)[torch.tensor(tokens)]
+        for layer, blk in enumerate(m.spec.blocks):
+            y = P.rms_norm(x, dd(blk.norm1.weight), eps)
+            mx = blk.mixer
+            if layer == 1:
+                s, outs = torch.zeros(H, dtype=torch.float64), []
+                for t in range(T):
+                    s = decay * s + y[t]
+                    outs.append(s)
+                x = x + torch.stack(outs) @ dd(mx.w).t()
+            else:
+                qkv = y @ dd(mx.qkv.weight).t() + (dd(mx.qkv.bias) if mx.qkv.bias is not None else 0.0)
+                q, k, v = qkv[:, :nh * hd].reshape(T, nh, hd), qkv[:, nh * hd:(nh + nkv) * hd].reshape(T, nkv, hd), qkv[:, (nh + nkv) * hd:].reshape(T, nkv, hd)
+                inv = mx.position.inv_freq_host
+                q, k = plain_rotation(q, pos, inv, rots[layer], False), plain_rotation(k, pos, inv, rots[layer], False)
+                o = P.causal_attention(q, k, v, window=windows[layer])
+                x = x + o.reshape(T, nh * hd) @ dd(mx.o.weight).t()
+            y = P.rms_norm(x, dd(blk.norm2.weight), eps)
+            gu = dd(blk.ffn.gate_up.weight)
+            x = x + P.swiglu_mlp(y, gu[0::2], gu[1::2], dd(blk.ffn.down.weight))
+        return P.rms_norm(x, dd(m.spec.final_norm.weight), eps) @ dd(m.spec.embedding.weight).t()
+
+    seqs = [random_tokens(V, n, 40 + n) for n in (100, 37, 70)]
+    refs = [plain_logits(t) for t in seqs]
+    # whole, alone
+    for t, r in zip(seqs, refs):
+        s = cache.alloc_slot()
+        assert_logits_close(m.step(cache, [rf.StepRequest(s, t, range(len(t)))]).cpu(), r, "float32", "mixed model, whole")
+        cache.free_slot(s)
+    # an unequal batch: prompts in one step, a chunk each, single tokens, then replayed graphs; the shortest ends first
+    slots = [cache.alloc_slot() for _ in seqs]
+    at = [20, 5, 33]
+    m.step(cache, [rf.StepRequest(s, t[:a], []) for s, t, a in zip(slots, seqs, at)])
+    got = m.step(cache, [rf.StepRequest(s, t[a:a + 6], range(6)) for s, t, a in zip(slots, seqs, at)]).cpu()
+    assert_logits_close(got, torch.cat([r[a:a + 6] for r, a in zip(refs, at)]), "float32", "mixed model, chunks")
+    at = [a + 6 for a in at]
+    runner = DecodeRunner(m, cache)
+    live = [0, 1, 2]
+    for step in range(60):
+        for i in [i for i in live if at[i] >= len(seqs[i])]:
+            cache.free_slot(slots[i]); live.remove(i)
+        if not live:
+            break
+        toks = [seqs[i][at[i]] for i in live]
+        if step < 8:
+            got = m.step(cache, [rf.StepRequest(slots[i], [tk], [0]) for i, tk in zip(live, toks)]).cpu()
+        else:
+            got = runner.logits([slots[i] for i in live], toks).cpu()
+        assert_logits_close(got, torch.stack([refs[i][at[i]] for i in live]), "float32", f"mixed model, step {step}")
+        for i in live:
+            at[i] += 1
+    assert runner.replays > 20 and cache.live_slots == 1        # the longest sequence is still there
