@@ -53,6 +53,47 @@ __device__ __forceinline__ void tcgen05_commit_multicast(uint32_t bar, uint16_t 
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
                  ::"r"(bar), "h"(mask) : "memory");
 }
+// ---- two CTAs as one MMA unit (cta_group::2).  The even CTA of a pair issues 256-row products that read both
+// CTAs' shared memory (each holds its own 128 activation rows and its half of the weight rows) and write both
+// CTAs' tensor memory; loads of either CTA report their bytes to the even CTA's barrier.
+__device__ __forceinline__ uint32_t cluster_addr_of(uint32_t local, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t cluster_bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ void tcgen05_alloc_pair(uint32_t smem_dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tcgen05_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                      uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tcgen05_commit_pair(uint32_t bar, uint16_t mask) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(mask) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+// M = 256 over the pair, N = n
+__host__ __device__ constexpr uint32_t make_idesc_pair(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+}
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int c1, uint32_t src) {
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];"
                  ::"l"(map), "r"(c0), "r"(c1), "r"(src) : "memory");
@@ -80,19 +121,31 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 // parts that are in; the last part sets it back to zero for the next launch.  Parts are scheduled
 // part-major (all first parts, then all second parts, ...), and all clusters of the grid are resident, so a
 // wait is always for work that was handed out earlier: it cannot deadlock, and in practice it never spins.
-template <int CL>
+// PAIR (CL = 2 only): the two CTAs of a cluster form one MMA unit.  A stage then holds this CTA's activation tile and
+// only its own half of the weight tile (32 KB instead of 48 KB, so the ring has six stages), nothing is multicast,
+// and per 64-deep step an SM reads 32 KB of operands from its shared memory instead of 48 KB for the same flops.
+template <bool PAIR> struct ClusterLayout {
+    static constexpr int stages = PAIR ? 6 : CG_STAGES;
+    static constexpr uint32_t a_bytes = TC_BM * TC_BK * 2;
+    static constexpr uint32_t b_bytes = (PAIR ? CG_BN / 2 : CG_BN) * TC_BK * 2;
+    static constexpr size_t smem = (size_t)stages * (a_bytes + b_bytes) + 2 * 16384 + (2 * stages + 4) * 8 + 16 + 1024;
+};
+
+template <int CL, bool PAIR>
 __global__ void __launch_bounds__(CG_THREADS, 1)
 gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                        const __grid_constant__ CUtensorMap map_out, TcParams p, int groups_m, int tiles_n, int bn,
                        int* __restrict__ flags) {
     // bn: columns of a tile (a multiple of 32, at most CG_BN; the host picks the width that wastes least of the last
     // round of clusters); the ring and the accumulators are laid out for CG_BN
-    constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2;
-    constexpr uint32_t B_BYTES = CG_BN * TC_BK * 2;
+    static_assert(!PAIR || CL == 2, "a pair is two CTAs");
+    constexpr uint32_t A_BYTES = ClusterLayout<PAIR>::a_bytes;
+    constexpr uint32_t B_BYTES = ClusterLayout<PAIR>::b_bytes;
     constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
     const uint32_t b_part = (uint32_t)(bn / CL) * TC_BK * 2;            // bytes of the weight rows this CTA loads
-    const uint32_t stage_tx = A_BYTES + (uint32_t)bn * TC_BK * 2;
-    constexpr int S = CG_STAGES;
+    // bytes that a stage's "full" barrier expects: as a pair, both CTAs' loads report to the even CTA's barrier
+    const uint32_t stage_tx = (PAIR ? 2 * A_BYTES : A_BYTES) + (uint32_t)bn * TC_BK * 2;
+    constexpr int S = ClusterLayout<PAIR>::stages;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -116,19 +169,24 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         abort_flag = 0;
         for (int s = 0; s < S; ++s) {
             mbar_init(smem_u32(&bars[s]), 1);
-            mbar_init(smem_u32(&bars[S + s]), CL);
+            mbar_init(smem_u32(&bars[S + s]), PAIR ? 1 : CL);         // as a pair: one commit of the even CTA frees both
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&bars[2 * S + b]), 1);
-            mbar_init(smem_u32(&bars[2 * S + 2 + b]), 128);
+            mbar_init(smem_u32(&bars[2 * S + 2 + b]), PAIR ? 2 : 128);  // as a pair: one arrival per CTA, at the even CTA
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
     }
     if (warp == 1) {
-        tcgen05_alloc(smem_u32(tmem_slot), 512);
-        tcgen05_relinquish();
+        if constexpr (PAIR) {                            // the same warp of both CTAs allocates for the pair
+            tcgen05_alloc_pair(smem_u32(tmem_slot), 512);
+            tcgen05_relinquish_pair();
+        } else {
+            tcgen05_alloc(smem_u32(tmem_slot), 512);
+            tcgen05_relinquish();
+        }
     }
     tcgen05_fence_before();
     __syncthreads();
@@ -141,15 +199,31 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             // The weights do not depend on the kernel before this one: the ring's first lap gets its weight
             // tiles at once; the activations follow into the same stages after the dependency wait.
             int pre = 0;
+            // where a stage's loads report their bytes: this CTA's barrier, as a pair the even CTA's
+            auto full_of = [&](int s) -> uint32_t {
+                const uint32_t local = smem_u32(&bars[s]);
+                if constexpr (PAIR) return cluster_addr_of(local, 0);
+                return local;
+            };
+            auto load_weights = [&](uint32_t sa, int kb, int tile_n, uint32_t full) {
+                if constexpr (PAIR)
+                    tma_load_2d_pair(sa + A_BYTES, &map_b, kb * TC_BK, tile_n * bn + (int)rank * (bn / CL), full);
+                else
+                    tma_load_2d_multicast(sa + A_BYTES + rank * b_part, &map_b, kb * TC_BK,
+                                          tile_n * bn + (int)rank * (bn / CL), full, all);
+            };
+            auto load_rows = [&](uint32_t sa, int kb, int tile_m, uint32_t full) {
+                if constexpr (PAIR) tma_load_2d_pair(sa, &map_a, kb * TC_BK, tile_m * TC_BM, full);
+                else tma_load_2d(sa, &map_a, kb * TC_BK, tile_m * TC_BM, full);
+            };
+            const bool arms = !PAIR || rank == 0;        // who tells the barrier how many bytes to expect
             if (cluster_id < n_work) {
                 const int tile_n = (cluster_id / groups_m) % tiles_n;
                 const int kb0 = (cluster_id / n_tiles) * kb_part, kb1 = min(kb_all, kb0 + kb_part);
                 pre = min(S, kb1 - kb0);
                 for (int i = 0; i < pre; ++i) {
-                    const uint32_t full = smem_u32(&bars[i]);
-                    mbar_expect_tx(full, stage_tx);
-                    tma_load_2d_multicast(smem_u32(smem + i * STAGE_BYTES) + A_BYTES + rank * b_part, &map_b,
-                                          (kb0 + i) * TC_BK, tile_n * bn + (int)rank * (bn / CL), full, all);
+                    if (arms) mbar_expect_tx(smem_u32(&bars[i]), stage_tx);
+                    load_weights(smem_u32(smem + i * STAGE_BYTES), kb0 + i, tile_n, full_of(i));
                 }
             }
             pdl_wait();
@@ -159,23 +233,22 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 const int kb0 = (w / n_tiles) * kb_part, kb1 = min(kb_all, kb0 + kb_part);
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % S;
-                    const uint32_t full = smem_u32(&bars[s]);
+                    const uint32_t full = full_of(s);
                     const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
                     if (it < pre) {                      // armed above, the weights are on their way
-                        tma_load_2d(sa, &map_a, kb * TC_BK, tile_m * TC_BM, full);
+                        load_rows(sa, kb, tile_m, full);
                         continue;
                     }
                     if (!mbar_wait(smem_u32(&bars[S + s]), ((it / S) & 1) ^ 1, &abort_flag)) break;
-                    mbar_expect_tx(full, stage_tx);
-                    tma_load_2d(sa, &map_a, kb * TC_BK, tile_m * TC_BM, full);
-                    tma_load_2d_multicast(sa + A_BYTES + rank * b_part, &map_b, kb * TC_BK,
-                                          tile_n * bn + (int)rank * (bn / CL), full, all);
+                    if (arms) mbar_expect_tx(smem_u32(&bars[s]), stage_tx);
+                    load_rows(sa, kb, tile_m, full);
+                    load_weights(sa, kb, tile_n, full);
                 }
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
-            const uint32_t idesc = make_idesc(bn);
+        if (lane == 0 && (!PAIR || rank == 0)) {          // as a pair, the even CTA issues the products of both
+            const uint32_t idesc = PAIR ? make_idesc_pair(bn) : make_idesc(bn);
             int it = 0, local = 0;
             for (int w = cluster_id; w < n_work && !abort_flag; w += n_clusters, ++local) {
                 const int buf = local & 1;
@@ -192,12 +265,18 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                     const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
                     const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + A_BYTES);
 #pragma unroll
-                    for (int k = 0; k < TC_BK / 16; ++k)
-                        tcgen05_mma_bf16(acc, da + 2 * k, db + 2 * k, idesc, (kb | k) ? 1u : 0u);
-                    tcgen05_commit_multicast(smem_u32(&bars[S + s]), all);   // the stage is free in every CTA that fed it
+                    for (int k = 0; k < TC_BK / 16; ++k) {
+                        if constexpr (PAIR) tcgen05_mma_bf16_pair(acc, da + 2 * k, db + 2 * k, idesc, (kb | k) ? 1u : 0u);
+                        else tcgen05_mma_bf16(acc, da + 2 * k, db + 2 * k, idesc, (kb | k) ? 1u : 0u);
+                    }
+                    // the stage is free in every CTA that fed it
+                    if constexpr (PAIR) tcgen05_commit_pair(smem_u32(&bars[S + s]), all);
+                    else tcgen05_commit_multicast(smem_u32(&bars[S + s]), all);
                 }
                 if (!ok) break;
-                tcgen05_commit(smem_u32(&bars[2 * S + buf]));                // this accumulator is complete
+                // this accumulator is complete (as a pair: both halves, and both CTAs' epilogues are told)
+                if constexpr (PAIR) tcgen05_commit_pair(smem_u32(&bars[2 * S + buf]), all);
+                else tcgen05_commit(smem_u32(&bars[2 * S + buf]));
             }
         }
     } else {
@@ -298,7 +377,12 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 }
             }
             tcgen05_fence_before();
-            mbar_arrive(smem_u32(&bars[2 * S + 2 + buf]));                   // 128 arrivals hand the buffer back
+            if constexpr (PAIR) {                        // one arrival per CTA at the even CTA, where the products are issued
+                epi_barrier();
+                if (leader) mbar_arrive_cluster(cluster_addr_of(smem_u32(&bars[2 * S + 2 + buf]), 0));
+            } else {
+                mbar_arrive(smem_u32(&bars[2 * S + 2 + buf]));               // 128 arrivals hand the buffer back
+            }
             if (leader && p.splits > 1) {
                 // this part's additions are complete in memory before the next part of the tile may start
                 asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
@@ -317,7 +401,8 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     cluster_sync_all();                                  // no peer may still write here or signal our barriers
     if (warp == 1) {
         tcgen05_fence_after();
-        tcgen05_dealloc(tmem_base, 512);
+        if constexpr (PAIR) tcgen05_dealloc_pair(tmem_base, 512);
+        else tcgen05_dealloc(tmem_base, 512);
     }
     if (threadIdx.x == 0 && abort_flag && p.status) atomicExch(p.status, 4);
 }
@@ -338,9 +423,9 @@ static int make_out_map(CUtensorMap* map, const void* base, long long rows, long
     return r == CUDA_SUCCESS ? 0 : RF_ERR_BAD_ARG;
 }
 
-template <int CL>
+template <int CL, bool PAIR>
 static int cluster_width() {
-    constexpr size_t smem = (size_t)CG_STAGES * (TC_BM * TC_BK * 2 + CG_BN * TC_BK * 2) + 2 * 16384 + (2 * CG_STAGES + 4) * 8 + 16 + 1024;
+    constexpr size_t smem = ClusterLayout<PAIR>::smem;
     static int max_clusters = -1;
     if (max_clusters < 0) {
         cudaLaunchConfig_t cfg = {};
@@ -352,11 +437,11 @@ static int cluster_width() {
         cfg.attrs = attr;
         cfg.numAttrs = 1;
         cfg.gridDim = dim3(CL);
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_cluster_kernel<CL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_cluster_kernel<CL, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)smem);
         if (e != cudaSuccess) return -(int)e - 100;
         int n = 0;
-        e = cudaOccupancyMaxActiveClusters(&n, gemm_tc_cluster_kernel<CL>, &cfg);
+        e = cudaOccupancyMaxActiveClusters(&n, gemm_tc_cluster_kernel<CL, PAIR>, &cfg);
         if (e != cudaSuccess) return -(int)e - 100;
         if (n <= 0) return RF_ERR_UNSUPPORTED;
         max_clusters = n;
@@ -364,11 +449,11 @@ static int cluster_width() {
     return max_clusters;
 }
 
-template <int CL>
+template <int CL, bool PAIR>
 static int launch_cluster(const void* X, int ldx, const void* W, TcParams p, int parts, int* flags, int n_flags,
                           cudaStream_t st) {
-    constexpr size_t smem = (size_t)CG_STAGES * (TC_BM * TC_BK * 2 + CG_BN * TC_BK * 2) + 2 * 16384 + (2 * CG_STAGES + 4) * 8 + 16 + 1024;
-    const int max_clusters = cluster_width<CL>();
+    constexpr size_t smem = ClusterLayout<PAIR>::smem;
+    const int max_clusters = cluster_width<CL, PAIR>();
     if (max_clusters <= 0) return max_clusters < -100 ? -(max_clusters + 100) : RF_ERR_UNSUPPORTED;
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[2];
@@ -433,13 +518,19 @@ static int launch_cluster(const void* X, int ldx, const void* W, TcParams p, int
     if (n_clusters > max_clusters) n_clusters = max_clusters;
     cfg.gridDim = dim3(n_clusters * CL);
     cfg.numAttrs = g_rf_pdl ? 2 : 1;
-    cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_tc_cluster_kernel<CL>, ma, mb, mo, p, groups_m, tiles_n, bn, flags);
+    cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_tc_cluster_kernel<CL, PAIR>, ma, mb, mo, p, groups_m, tiles_n, bn, flags);
     if (le != cudaSuccess) return (int)le;
     RF_LAUNCH_CHECK();
     return 0;
 }
 
+// Whether clusters of two run as one MMA unit (cta_group::2) or as two CTAs that multicast their weight halves.
+static int g_pair = 1;
+
 extern "C" {
+
+int rf_gemm_tc_cluster_set_pair(int on) { g_pair = on ? 1 : 0; return 0; }
+int rf_gemm_tc_cluster_pair() { return g_pair; }
 
 int rf_gemm_tc_cluster_supported(int M, int N, int K, int mode) {
     // more tokens than the skinny kernel takes: below 256 rows a cluster's second CTA works on an empty tile, which
@@ -464,14 +555,16 @@ int rf_gemm_tc_cluster(const void* X, int ldx, const void* W, const void* bias, 
     if (!rf_gemm_tc_cluster_supported(M, N, K, mode)) return RF_ERR_UNSUPPORTED;
     if (parts < 0 || parts > 5) return RF_ERR_BAD_ARG;
     TcParams p{out, bias, bias_is_f32, M, N, K, ldo, mode, (K + TC_BK - 1) / TC_BK, 0, status, 1};
-    if (cluster == 2) return launch_cluster<2>(X, ldx, W, p, parts, flags, n_flags, st);
-    if (cluster == 4) return launch_cluster<4>(X, ldx, W, p, parts, flags, n_flags, st);
+    if (cluster == 2 && g_pair) return launch_cluster<2, true>(X, ldx, W, p, parts, flags, n_flags, st);
+    if (cluster == 2) return launch_cluster<2, false>(X, ldx, W, p, parts, flags, n_flags, st);
+    if (cluster == 4) return launch_cluster<4, false>(X, ldx, W, p, parts, flags, n_flags, st);
     return RF_ERR_BAD_ARG;
 }
 
 int rf_gemm_tc_cluster_width(int cluster) {
-    if (cluster == 2) return cluster_width<2>();
-    if (cluster == 4) return cluster_width<4>();
+    if (cluster == 2 && g_pair) return cluster_width<2, true>();
+    if (cluster == 2) return cluster_width<2, false>();
+    if (cluster == 4) return cluster_width<4, false>();
     return RF_ERR_BAD_ARG;
 }
 

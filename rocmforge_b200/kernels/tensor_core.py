@@ -97,12 +97,23 @@ _cluster_width = {}
 
 def cluster_width(cluster: int = 2) -> int:
     """Clusters of the persistent kernel that run at once on this device."""
-    if cluster not in _cluster_width:
+    key = (cluster, cluster_pair())
+    if key not in _cluster_width:
         f = fn("gemm_tcgen05_cluster", "rf_gemm_tc_cluster_width", [c_int])
         n = f(cluster)
         need(n > 0, f"the clustered kernel cannot be launched with clusters of {cluster} (code {n})")
-        _cluster_width[cluster] = n
-    return _cluster_width[cluster]
+        _cluster_width[key] = n
+    return _cluster_width[key]
+
+
+def set_cluster_pair(on: bool) -> None:
+    """Clusters of two as one MMA unit (the even CTA issues 256-row products over both CTAs' shared and tensor
+    memory) instead of two CTAs that multicast their halves of a weight tile to each other."""
+    fn("gemm_tcgen05_cluster", "rf_gemm_tc_cluster_set_pair", [c_int])(1 if on else 0)
+
+
+def cluster_pair() -> bool:
+    return bool(fn("gemm_tcgen05_cluster", "rf_gemm_tc_cluster_pair", [])())
 
 
 _part_flags = {}

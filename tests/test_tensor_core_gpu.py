@@ -43,7 +43,7 @@ def test_tokens_as_rows(M, N, K):
     tc.check_status(DEV)
 
 
-@pytest.mark.parametrize("cluster", [2, 4])
+@pytest.mark.parametrize("cluster", [2, 4, "pair"])
 @pytest.mark.parametrize("M,N,K", [(256, 256, 64), (300, 520, 1000), (2048, 4608, 3584), (1100, 3584, 18944),
                                    (257, 1000, 3584), (640, 37888, 3584), (65, 3584, 3584), (128, 4608, 3584),
                                    (200, 3584, 18944)])
@@ -51,6 +51,16 @@ def test_clustered_persistent_kernel(M, N, K, cluster):
     from rocmforge_b200.kernels import tensor_core as tc
     if not tc.cluster_available():
         pytest.skip("the clustered module is not part of this checkout")
+    # "pair": the two CTAs of a cluster as one MMA unit; 2 and 4: CTAs that multicast weight tiles to each other
+    was = tc.cluster_pair()
+    tc.set_cluster_pair(cluster == "pair")
+    try:
+        clustered_cases(tc, M, N, K, 2 if cluster == "pair" else cluster)
+    finally:
+        tc.set_cluster_pair(was)
+
+
+def clustered_cases(tc, M, N, K, cluster):
     x, w, b = rnd(M, K, seed=1), rnd(N, K, seed=2, scale=0.05), rnd(N, seed=3, dt=torch.float32)
     ref = x.double() @ w.double().t()
     close(tc.gemm_tc(x, w, cluster=cluster), ref, "store")
