@@ -12,25 +12,53 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------- argmax
+// The largest logit of a row; among equal logits the largest index; NaN never wins (a row of NaNs yields 0).
+// A row is scanned by a thread-block cluster of 1 to 16 CTAs, each on its slice of the vocabulary with 16-byte
+// loads where the row allows them: a decode step has a handful of rows of 150,000 logits, and one CTA per row
+// (64 rows: 65 us of a step) leaves most of the GPU idle.  Every CTA hands its winner to the cluster's first CTA
+// through distributed shared memory; that one merges them in rank order.
+__device__ __forceinline__ void argmax_take(float& best, int& bi, float v, int i) {
+    if (i >= 0 && (bi < 0 || v > best || (v == best && i > bi))) { best = v; bi = i; }
+}
+
 __global__ void __launch_bounds__(1024)
-argmax_kernel(const float* __restrict__ logits, int V, long long row_stride, int* __restrict__ out) {
+argmax_kernel(const float* __restrict__ logits, int V, long long row_stride, int* __restrict__ out, int slices) {
     pdl_trigger();
-    pdl_wait();
     __shared__ float sval[32];
     __shared__ int sidx[32];
-    const float* x = logits + (size_t)blockIdx.x * row_stride;
+    __shared__ float cval[16];          // the cluster's winners, filled in the first CTA only
+    __shared__ int cidx[16];
+    const int row = blockIdx.x / slices, rank = blockIdx.x % slices;      // cluster dimension = slices along x
+    const float* x = logits + (size_t)row * row_stride;
+    int per = (V + slices - 1) / slices;
+    per = (per + 3) & ~3;                                                 // slices start on 16-byte borders of the row
+    const int i0 = min(V, rank * per), i1 = min(V, i0 + per);
+    pdl_wait();
     float best = -INFINITY;
     int bi = -1;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-        const float v = x[i];
-        if (v > best || (v == best && i > bi) || bi < 0) { best = v; bi = i; }
+    if ((reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+        const int n4 = (i1 - i0) >> 2;
+        const float4* x4 = reinterpret_cast<const float4*>(x + i0);
+        for (int j = threadIdx.x; j < n4; j += blockDim.x) {
+            const float4 v = x4[j];
+            const int i = i0 + 4 * j;
+            // a NaN fails every comparison: it is taken only as a thread's first candidate, and loses to any number later
+            if (v.x == v.x) argmax_take(best, bi, v.x, i);
+            if (v.y == v.y) argmax_take(best, bi, v.y, i + 1);
+            if (v.z == v.z) argmax_take(best, bi, v.z, i + 2);
+            if (v.w == v.w) argmax_take(best, bi, v.w, i + 3);
+        }
+        for (int i = i0 + 4 * n4 + threadIdx.x; i < i1; i += blockDim.x)
+            if (x[i] == x[i]) argmax_take(best, bi, x[i], i);
+    } else {
+        for (int i = i0 + threadIdx.x; i < i1; i += blockDim.x)
+            if (x[i] == x[i]) argmax_take(best, bi, x[i], i);
     }
-    // NaN never wins a comparison: a row of NaNs yields its first scanned index per thread
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, best, o);
         const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (oi >= 0 && (bi < 0 || ov > best || (ov == best && oi > bi))) { best = ov; bi = oi; }
+        argmax_take(best, bi, ov, oi);
     }
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (lane == 0) { sval[warp] = best; sidx[warp] = bi; }
@@ -43,16 +71,57 @@ argmax_kernel(const float* __restrict__ logits, int V, long long row_stride, int
         for (int o = 16; o > 0; o >>= 1) {
             const float ov = __shfl_xor_sync(0xffffffffu, best, o);
             const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (oi >= 0 && (bi < 0 || ov > best || (ov == best && oi > bi))) { best = ov; bi = oi; }
+            argmax_take(best, bi, ov, oi);
         }
-        if (lane == 0) out[blockIdx.x] = bi < 0 ? 0 : bi;
+        if (lane == 0) {
+            if (slices == 1) {
+                out[row] = bi < 0 ? 0 : bi;
+            } else {                                 // into the first CTA's shared memory
+                uint32_t va, ia;
+                asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(va) : "r"((uint32_t)__cvta_generic_to_shared(&cval[rank])));
+                asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(ia) : "r"((uint32_t)__cvta_generic_to_shared(&cidx[rank])));
+                asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(va), "f"(best) : "memory");
+                asm volatile("st.shared::cluster.s32 [%0], %1;" ::"r"(ia), "r"(bi) : "memory");
+            }
+        }
+    }
+    if (slices > 1) {
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        if (rank == 0 && threadIdx.x == 0) {
+            best = cval[0]; bi = cidx[0];
+            for (int r = 1; r < slices; ++r) argmax_take(best, bi, cval[r], cidx[r]);
+            out[row] = bi < 0 ? 0 : bi;
+        }
     }
 }
 
 extern "C" int rf_argmax(const float* logits, int rows, int V, long long row_stride, int* out, cudaStream_t st) {
     if (rows <= 0) return 0;
     if (V <= 0) return RF_ERR_BAD_ARG;
-    rf_launch(argmax_kernel, dim3(rows), dim3(1024), 0, st, logits, V, row_stride, out);
+    // as many CTAs per row as fill the GPU about twice over, each with at least 4,096 logits
+    int slices = 16;
+    while (slices > 1 && ((long long)rows * slices > 320 || V / slices < 4096)) slices >>= 1;
+    if (row_stride % 4) slices = 1;                  // rows that do not start on 16-byte borders: one CTA, scalar loads
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(argmax_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(rows * slices);
+    cfg.blockDim = dim3(1024);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = slices; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_rf_pdl ? 2 : 1;
+    cudaError_t err = cudaLaunchKernelEx(&cfg, argmax_kernel, logits, V, row_stride, out, slices);
+    if (err != cudaSuccess) return (int)err;
     RF_LAUNCH_CHECK();
     return 0;
 }

@@ -487,6 +487,25 @@ def test_argmax_ties_and_sizes():
     assert got[4] == S.greedy(x[4].cpu())
     y = rnd(3, 300, seed=1)
     assert kernels.argmax(y).cpu().tolist() == [S.greedy(r) for r in y.cpu()]
+    # every split of a row over CTAs (16 down to 1 with the number of rows), winners planted in every part of the row
+    for rows, V in ((1, 152064), (20, 152064), (64, 151936), (300, 40000), (3, 9000), (7, 8191)):
+        z = rnd(rows, V, seed=rows)
+        want = []
+        for r in range(rows):
+            at = (r * 7919 + 13) * 104729 % V
+            z[r, at] = 40.0
+            if r % 3 == 0:
+                z[r, min(V - 1, at + 4097)] = 40.0               # an equal maximum further on, often in another CTA's part
+                at = max(at, min(V - 1, at + 4097))
+            want.append(at)
+        z[0, 5] = float("nan")                                   # a NaN never wins
+        assert kernels.argmax(z).cpu().tolist() == want, (rows, V)
+    wide = rnd(6, 1003, seed=3)                                   # rows that start off 16-byte borders
+    view = wide[:, 1:1002]
+    assert kernels.argmax(view).cpu().tolist() == [S.greedy(r) for r in view.cpu()]
+    nans = torch.full((2, 5000), float("nan"), device=DEV)
+    nans[1, 4321] = -3.0
+    assert kernels.argmax(nans).cpu().tolist() == [0, 4321]
 
 
 @pytest.mark.parametrize("V", [300, 5000, 152064])
