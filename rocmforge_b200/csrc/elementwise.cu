@@ -92,20 +92,53 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const void* __restrict
 // thread), every load is 16 bytes wide and independent of the others, so a short row costs a few
 // memory round trips instead of a chain of them.  Sums are formed in the same order as above
 // (h first, then the partial sums in index order), element by element.
+//
+// A row may be shared by a thread-block cluster of `cl` CTAs (few rows: a decode step's norm reads the K-split
+// partial sums of the product before it, 150 KB a row at width 3,584 with ten splits, and one CTA per row leaves a
+// handful of SMs pulling all of that from L2).  The CTAs' threads are numbered through (rank * blockDim + thread)
+// and work exactly as the threads of one large block would; the warps' sums of squares are pushed into every
+// CTA's shared memory and folded by the same tree as in block_sum, so the result is bit for bit that of one CTA.
+__device__ __forceinline__ float cluster_block_sum(float v, float* red, int vt, int n_warps, int cl) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    v = warp_sum(v);
+    asm volatile("barrier.cluster.wait.aligned;" ::: "memory");             // every peer has started (arrived at its top)
+    if (lane == 0) {
+        const uint32_t mine = (uint32_t)__cvta_generic_to_shared(&red[vt >> 5]);
+        for (int r = 0; r < cl; ++r) {
+            uint32_t remote;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(mine), "r"(r));
+            asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+        }
+    }
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (warp == 0) {
+        float t = lane < n_warps ? red[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}
+
 template <typename T, int NV>
 __global__ void __launch_bounds__(1024)
 add_rmsnorm_vec_kernel(float* __restrict__ h, const void* __restrict__ pending, int pending_kind, int n_pending,
                        size_t pending_stride, const void* __restrict__ w, int w_is_f32, float eps,
-                       T* __restrict__ y, const int* __restrict__ rows, int H) {
+                       T* __restrict__ y, const int* __restrict__ rows, int H, int cl) {
     pdl_trigger();
     __shared__ float red[34];
-    const int r = blockIdx.x;
+    if (cl > 1) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");    // "started": peers may store here
+    const int r = blockIdx.x / cl;
     const int t = rows ? rows[r] : r;
     const int nvec = H >> 2;
+    int rank = 0;
+    if (cl > 1) asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    const int vt = rank * blockDim.x + threadIdx.x, VT = cl * blockDim.x;       // this thread among the row's threads
     uint4 wraw[NV];                              // the norm's weights (four floats, or four bfloat16 in x and y):
 #pragma unroll                                   // no kernel writes them, so they are fetched while the kernel
     for (int i = 0; i < NV; ++i) {               // before this one still runs
-        const int c = threadIdx.x + i * blockDim.x;
+        const int c = vt + i * VT;
         wraw[i] = make_uint4(0u, 0u, 0u, 0u);
         if (c < nvec) {
             if (w_is_f32) {
@@ -122,12 +155,21 @@ add_rmsnorm_vec_kernel(float* __restrict__ h, const void* __restrict__ pending, 
     float ss = 0.f;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
-        const int c = threadIdx.x + i * blockDim.x;
+        const int c = vt + i * VT;
         if (c < nvec) {
             float4 a = hrow[c];
             if (pending_kind == 1) {
                 const float4* p = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(pending) + (size_t)t * H) + c;
-                for (int s2 = 0; s2 < n_pending; ++s2) {
+                int s2 = 0;
+                for (; s2 + 4 <= n_pending; s2 += 4) {       // four loads in flight, added in index order
+                    float4 b[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        b[u] = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + (size_t)(s2 + u) * pending_stride);
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) { a.x += b[u].x; a.y += b[u].y; a.z += b[u].z; a.w += b[u].w; }
+                }
+                for (; s2 < n_pending; ++s2) {
                     const float4 b = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + (size_t)s2 * pending_stride);
                     a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
                 }
@@ -140,12 +182,12 @@ add_rmsnorm_vec_kernel(float* __restrict__ h, const void* __restrict__ pending, 
             ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
         }
     }
-    const float total = block_sum(ss, red);
+    const float total = cl > 1 ? cluster_block_sum(ss, red, vt, VT >> 5, cl) : block_sum(ss, red);
     const float inv = rsqrtf(total / (float)H + eps);
     T* yrow = y + (size_t)r * H;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
-        const int c = threadIdx.x + i * blockDim.x;
+        const int c = vt + i * VT;
         if (c < nvec) {
             if (!rows && pending_kind != 0) hrow[c] = v[i];
             float w0, w1, w2, w3;
@@ -331,9 +373,19 @@ static int launch_add_rmsnorm(float* h, const void* pending, int kind, int n_pen
         if (n_rows >= 512 && nvec > 256 && nvec <= 1024) threads = 256;
         const int per = (nvec + threads - 1) / threads;
         T* yy = reinterpret_cast<T*>(y);
-        if (per <= 1) rf_launch(add_rmsnorm_vec_kernel<T, 1>, dim3(n_rows), dim3(threads), 0, st, h, pending, kind, n_pending, pstride, w, w_is_f32, eps, yy, rows, H);
-        else if (per <= 2) rf_launch(add_rmsnorm_vec_kernel<T, 2>, dim3(n_rows), dim3(threads), 0, st, h, pending, kind, n_pending, pstride, w, w_is_f32, eps, yy, rows, H);
-        else rf_launch(add_rmsnorm_vec_kernel<T, 4>, dim3(n_rows), dim3(threads), 0, st, h, pending, kind, n_pending, pstride, w, w_is_f32, eps, yy, rows, H);
+        // few rows: the row's threads as a cluster of up to 8 CTAs of whole warps, while that makes no more CTAs than
+        // two per SM
+        int cl = 1;
+        for (int c = 8; c >= 2; --c)
+            if ((threads / 32) % c == 0 && (long long)n_rows * c <= 296) { cl = c; break; }
+        const dim3 grid(n_rows * cl), block(threads / cl);
+        auto go = [&](auto kernel) {
+            if (cl > 1) rf_launch_cluster(kernel, grid, block, 0, st, cl, h, pending, kind, n_pending, pstride, w, w_is_f32, eps, yy, rows, H, cl);
+            else rf_launch(kernel, grid, block, 0, st, h, pending, kind, n_pending, pstride, w, w_is_f32, eps, yy, rows, H, cl);
+        };
+        if (per <= 1) go(add_rmsnorm_vec_kernel<T, 1>);
+        else if (per <= 2) go(add_rmsnorm_vec_kernel<T, 2>);
+        else go(add_rmsnorm_vec_kernel<T, 4>);
         RF_LAUNCH_CHECK();
         return 0;
     }

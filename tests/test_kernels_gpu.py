@@ -69,6 +69,31 @@ def test_add_rmsnorm(dt, H):
 
 
 @pytest.mark.parametrize("dt", DTS)
+@pytest.mark.parametrize("H", [896, 3584, 4100, 5120, 8192, 16384])
+def test_add_rmsnorm_rows_shared_by_a_cluster_give_the_bits_of_one_block(dt, H):
+    """With few rows a row's threads are spread over a thread-block cluster (up to 8 CTAs); with many rows one
+    block works on a row.  Both must give the same bits, with and without partial sums, whatever the number of rows
+    (a token's norm must not depend on the size of its batch)."""
+    from rocmforge_b200 import kernels
+    w = rnd(H, dt=torch.bfloat16, seed=2) + 1.0
+    for n_pending in (0, 1, 3, 10):
+        h = rnd(5, H, seed=5)
+        parts = rnd(n_pending, 5, H, seed=6) if n_pending else None
+        many_h, many_parts = h.repeat(80, 1), (parts.repeat(1, 80, 1) if n_pending else None)     # 400 rows: no clusters
+        y_many = kernels.add_rmsnorm(many_h, w, 1e-6, dt, pending=many_parts)
+        for n in (1, 2, 5):
+            hn = h[:n].clone()
+            yn = kernels.add_rmsnorm(hn, w, 1e-6, dt, pending=parts[:, :n].contiguous() if n_pending else None)
+            assert torch.equal(yn, y_many[:n]), (H, n_pending, n)
+            assert torch.equal(hn, many_h[:n])
+        rows = torch.tensor([4, 1], dtype=torch.int32, device=DEV)
+        y_rows = kernels.add_rmsnorm(h.clone(), w, 1e-6, dt, pending=parts, rows=rows)
+        assert torch.equal(y_rows, y_many[rows.long()])
+        total = h.double() + (parts.double().sum(0) if n_pending else 0)
+        torch.testing.assert_close(y_many[:5].double(), P.rms_norm(total, w.double(), 1e-6), **tol(dt))
+
+
+@pytest.mark.parametrize("dt", DTS)
 @pytest.mark.parametrize("M,N,K", [(1, 7, 5), (5, 130, 33), (65, 64, 64), (130, 200, 257), (3, 1000, 3584), (17, 896, 4864),
                                    (40, 300, 1000), (300, 1152, 896)])
 def test_gemm_simt(dt, M, N, K):
