@@ -249,6 +249,13 @@ def sample(logits: torch.Tensor, temperature: float, top_p: float, top_k: int, s
     return out
 
 
+def set_sample_cached(on: bool) -> None:
+    """Which sampler ``sample`` launches where both can run: the one that keeps a CTA's slice of the row in shared
+    memory (the default), or the one that walks the row in global memory (it also serves vocabularies whose slices do
+    not fit).  Both give the same token."""
+    check(_f("sampling", "rf_sample_set_cached", c_int)(1 if on else 0), "set_sample_cached")
+
+
 def advance_decode(tokens, tok_pos, seq_start, sampled) -> None:
     """tokens <- sampled; positions and starts += 1 (one token per sequence), all on the device."""
     need_cuda(tokens, tok_pos, seq_start, sampled)

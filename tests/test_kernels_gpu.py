@@ -533,11 +533,20 @@ def test_argmax_ties_and_sizes():
     assert kernels.argmax(nans).cpu().tolist() == [0, 4321]
 
 
-@pytest.mark.parametrize("V", [300, 5000, 152064])
-def test_sample_kernel_follows_the_plain_sampler(V):
+@pytest.fixture(params=[True, False], ids=["slice in shared memory", "row in global memory"])
+def cached(request):
+    """Both samplers (they must give the same token; the second also serves vocabularies beyond the first one's reach)."""
+    from rocmforge_b200 import kernels
+    kernels.set_sample_cached(request.param)
+    yield request.param
+    kernels.set_sample_cached(True)
+
+
+@pytest.mark.parametrize("V", [300, 5000, 152064, 200000, 320000])
+def test_sample_kernel_follows_the_plain_sampler(V, cached):
     from rocmforge_b200 import kernels
     from rocmforge_b200.sampling import as_int64, draw_seed
-    R = 24
+    R = 24 if V < 100000 else 12
     logits = rnd(R, V, seed=V, scale=2.5)
     logits[:, 5] = logits[:, 77]                              # equal logits somewhere in every row
     logits[3, :] = 0.25                                       # a row of equal logits but one (all equal
@@ -558,7 +567,7 @@ def test_sample_kernel_follows_the_plain_sampler(V):
 
 
 @pytest.mark.parametrize("R", [1, 3, 8, 24, 60, 100])
-def test_sample_kernel_with_every_cluster_size(R):
+def test_sample_kernel_with_every_cluster_size(R, cached):
     """The CTAs per row go with the number of rows (16, 8, 4, 2, 1); small vocabularies leave some CTAs without an element."""
     from rocmforge_b200 import kernels
     from rocmforge_b200.sampling import as_int64, draw_seed
@@ -571,6 +580,37 @@ def test_sample_kernel_with_every_cluster_size(R):
             got = kernels.sample(logits, temperature, top_p, top_k,
                                  torch.tensor([as_int64(s) for s in seeds], dtype=torch.int64, device=DEV)).cpu().tolist()
             assert got == [S.sample(cpu[r], temperature, top_p, top_k, seeds[r]) for r in range(R)], (R, V, temperature, top_p, top_k)
+
+
+def test_both_samplers_pick_the_same_tokens():
+    """The sampler with the slice in shared memory against the one that walks global memory, on rows of every kind:
+    nearly flat (a random model's logits), peaked, with masked-out tokens, all equal, two values only."""
+    from rocmforge_b200 import kernels
+    R, V = 40, 152064
+    rows = [rnd(R, V, seed=1, scale=0.3), rnd(R, V, seed=2, scale=6.0)]
+    masked = rnd(R, V, seed=3, scale=2.0)
+    masked[:, ::3] = float("-inf")
+    masked[5, :] = float("-inf")
+    masked[5, 777] = 0.5
+    rows.append(masked)
+    flat = torch.zeros(R, V, device=DEV)
+    flat[1::2, 1000:2000] = 1.0
+    rows.append(flat)
+    quant = (rnd(R, V, seed=4, scale=2.0) * 4).round() / 4               # many ties at every level
+    rows.append(quant)
+    seeds = torch.arange(R, dtype=torch.int64, device=DEV) * 7919 + 17
+    try:
+        for logits in rows:
+            for temperature, top_p, top_k in ((1.0, 0.9, 0), (0.7, 1.0, 0), (1.3, 0.3, 0), (1.0, 0.95, 50), (1.0, 1.0, 5)):
+                for draw in range(3):
+                    counter = torch.tensor([draw * 1000003], dtype=torch.int32, device=DEV)
+                    kernels.set_sample_cached(True)
+                    a = kernels.sample(logits, temperature, top_p, top_k, seeds, draw_counter=counter).clone()
+                    kernels.set_sample_cached(False)
+                    b = kernels.sample(logits, temperature, top_p, top_k, seeds, draw_counter=counter)
+                    assert torch.equal(a, b), (temperature, top_p, top_k, draw, (a != b).nonzero().flatten().tolist())
+    finally:
+        kernels.set_sample_cached(True)
 
 
 def test_kernels_refuse_what_they_cannot_do():
