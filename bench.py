@@ -42,6 +42,7 @@ SHAPE_14B = dict(architectures=["Qwen2ForCausalLM"], num_hidden_layers=48, hidde
 CONTEXT = 4096
 PROMPT_LEN = 512
 PREFILL_TOKENS = 2048
+POINTS_WARMUP = 48                   # untimed steps before the batch-1 and batch-64 points are timed
 PREFILL_CHUNK = 16384          # most prompt tokens run in one step when a batch of prompts is brought into the cache
 
 
@@ -506,8 +507,11 @@ def main():
     torch.cuda.empty_cache()
     points = {}
     if not args.skip_points:
+        # steady decoding: the steps right after a batch of prompts run at lower clocks (the power cap after the prompts'
+        # burst, some tens of milliseconds; 64 prompts of 512 tokens are a burst of a third of a second), so these two
+        # points time their steps after POINTS_WARMUP untimed ones
         for b, st in ((1, args.steps), (64, max(args.steps // 2, 16))):
-            r = decode_rate(model, random_prompts(b, PROMPT_LEN, V, args.seed + 3 + b), st, warmup)
+            r = decode_rate(model, random_prompts(b, PROMPT_LEN, V, args.seed + 3 + b), st, max(warmup, POINTS_WARMUP))
             points[f"decode_b{b}"] = round(r["tok_s"], 1)
             points[f"decode_b{b}_hbm_frac"] = round(step_bytes(cfg, b, r["mean_ctx"]) / (r["ms_per_step"] / 1e3) / 1e9
                                                    / pk["hbm_gbs"], 4)
@@ -533,6 +537,7 @@ def main():
                    "context_at_timing": int(main_run["mean_ctx"]), "parallelism": "none (1 GPU)",
                    "cache_page": 64, "l2": "inputs larger than L2 (15 GB of weights per step)",
                    "peaks": pk["source"],
+                   "points_decode": f"decode_b1, decode_b64: prompts of {PROMPT_LEN} tokens, {POINTS_WARMUP} untimed steps, then timed",
                    "points_qwen0.5b": "Qwen2.5-0.5B shape, 24 layers, hidden 896, 14/2 heads of 64, intermediate 4864, "
                                       "vocab 151936 tied; batch 64, prompts uniform 16..1024 (seeded), 256 steps; bf16 and fp32",
                    "points_qwen14b": "Qwen2.5-14B shape, 48 layers, hidden 5120, 40/8 heads of 128, intermediate 13824, "
