@@ -298,57 +298,55 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             const uint32_t taddr = tmem_base + buf * CG_BN + ((uint32_t)(quarter * 32) << 16);
             // accumulator columns per 128-byte slab row: 32 as float, 64 as bfloat16, 128 through SwiGLU
             const int cols_per_slab = (mode == EPI_F32 || mode == EPI_RESIDUAL) ? 32 : (mode == EPI_STORE ? 64 : 128);
-#pragma unroll 1
-            for (int c0 = 0; c0 < bn; c0 += cols_per_slab, ++slab) {
+            // The accumulator leaves tensor memory 32 columns at a time, and the load of the next 32 is under way while
+            // these are converted and written (the last tile's epilogue hides behind nothing).
+            const bool with_bias = part == 0 && p.bias != nullptr;
+            auto put_chunk = [&](int c, const uint32_t* r) {
+                const int cc = c % cols_per_slab, c0 = c - cc;
                 uint8_t* st = staging + (slab & 1) * 16384;
-                // the slab before last used this buffer: TMA must have read it
-                if (leader) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-                epi_barrier();
+                if (cc == 0) {
+                    // the slab before last used this buffer: TMA must have read it
+                    if (leader) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                    epi_barrier();
+                }
                 const uint32_t srow = smem_u32(st) + row * 128;
-#pragma unroll 1
-                for (int cc = 0; cc < cols_per_slab; cc += 32) {
-                    uint32_t r[32];
-                    tcgen05_ld32(taddr + c0 + cc, r);
-                    tcgen05_wait_ld();
-                    const int n0 = tile_n * bn + c0 + cc;
-                    if (mode == EPI_SWIGLU) {            // 32 accumulators -> 16 bfloat16 = 2 chunks of 16 bytes
+                const int n0 = tile_n * bn + c;
+                if (mode == EPI_SWIGLU) {            // 32 accumulators -> 16 bfloat16 = 2 chunks of 16 bytes
 #pragma unroll
-                        for (int h8 = 0; h8 < 2; ++h8) {
-                            uint32_t wv[4];
+                    for (int h8 = 0; h8 < 2; ++h8) {
+                        uint32_t wv[4];
 #pragma unroll
-                            for (int q = 0; q < 4; ++q) {
-                                const int j = h8 * 16 + 4 * q;
-                                wv[q] = pack_bf16x2(silu_fast(__uint_as_float(r[j])) * __uint_as_float(r[j + 1]),
-                                                    silu_fast(__uint_as_float(r[j + 2])) * __uint_as_float(r[j + 3]));
-                            }
-                            const int chunk = (cc >> 4) + h8;
+                        for (int q = 0; q < 4; ++q) {
+                            const int j = h8 * 16 + 4 * q;
+                            wv[q] = pack_bf16x2(silu_fast(__uint_as_float(r[j])) * __uint_as_float(r[j + 1]),
+                                                silu_fast(__uint_as_float(r[j + 2])) * __uint_as_float(r[j + 3]));
+                        }
+                        const int chunk = (cc >> 4) + h8;
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(srow + ((chunk ^ (row & 7)) << 4)),
+                                     "r"(wv[0]), "r"(wv[1]), "r"(wv[2]), "r"(wv[3]) : "memory");
+                    }
+                } else {
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                    if (with_bias) add_bias_columns<32>(v, p.bias, p.bias_is_f32, n0, p.N);
+                    if (mode == EPI_STORE) {         // 32 accumulators -> 4 chunks of 8 bfloat16
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const int chunk = (cc >> 3) + q;
                             asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(srow + ((chunk ^ (row & 7)) << 4)),
-                                         "r"(wv[0]), "r"(wv[1]), "r"(wv[2]), "r"(wv[3]) : "memory");
+                                         "r"(pack_bf16x2(v[8 * q], v[8 * q + 1])), "r"(pack_bf16x2(v[8 * q + 2], v[8 * q + 3])),
+                                         "r"(pack_bf16x2(v[8 * q + 4], v[8 * q + 5])), "r"(pack_bf16x2(v[8 * q + 6], v[8 * q + 7]))
+                                         : "memory");
                         }
-                    } else {
-                        float v[32];
+                    } else {                         // 32 floats = the whole slab row
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            v[j] = __uint_as_float(r[j]);
-                            if (part == 0 && p.bias && n0 + j < p.N) v[j] += load_vec(p.bias, p.bias_is_f32, n0 + j);
-                        }
-                        if (mode == EPI_STORE) {         // 32 accumulators -> 4 chunks of 8 bfloat16
-#pragma unroll
-                            for (int q = 0; q < 4; ++q) {
-                                const int chunk = (cc >> 3) + q;
-                                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(srow + ((chunk ^ (row & 7)) << 4)),
-                                             "r"(pack_bf16x2(v[8 * q], v[8 * q + 1])), "r"(pack_bf16x2(v[8 * q + 2], v[8 * q + 3])),
-                                             "r"(pack_bf16x2(v[8 * q + 4], v[8 * q + 5])), "r"(pack_bf16x2(v[8 * q + 6], v[8 * q + 7]))
-                                             : "memory");
-                            }
-                        } else {                         // 32 floats = the whole slab row
-#pragma unroll
-                            for (int q = 0; q < 8; ++q)
-                                asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(srow + ((q ^ (row & 7)) << 4)),
-                                             "f"(v[4 * q]), "f"(v[4 * q + 1]), "f"(v[4 * q + 2]), "f"(v[4 * q + 3]) : "memory");
-                        }
+                        for (int q = 0; q < 8; ++q)
+                            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(srow + ((q ^ (row & 7)) << 4)),
+                                         "f"(v[4 * q]), "f"(v[4 * q + 1]), "f"(v[4 * q + 2]), "f"(v[4 * q + 3]) : "memory");
                     }
                 }
+                if (cc + 32 < cols_per_slab) return;                               // the slab is not complete yet
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // the slab is for TMA to read
                 epi_barrier();
                 if (leader) {
@@ -374,6 +372,22 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                         else tma_store_2d(omap, oc0, tile_m * TC_BM, smem_u32(st));
                     }
                     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                }
+                ++slab;
+            };
+            {
+                uint32_t ra[32], rb[32];
+                tcgen05_ld32(taddr, ra);
+#pragma unroll 1
+                for (int c = 0; c < bn; c += 64) {
+                    tcgen05_wait_ld();
+                    if (c + 32 < bn) tcgen05_ld32(taddr + c + 32, rb);
+                    put_chunk(c, ra);
+                    if (c + 32 < bn) {
+                        tcgen05_wait_ld();
+                        if (c + 64 < bn) tcgen05_ld32(taddr + c + 64, ra);
+                        put_chunk(c + 32, rb);
+                    }
                 }
             }
             tcgen05_fence_before();
