@@ -89,11 +89,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     uint8_t* kv_s = q_s + Q_BYTES;                       // [2 stages][K | V][HALVES][64][128 B]
     uint8_t* p_s = kv_s + 4 * KV_BYTES;                  // [128][128 B]: 64 keys of bfloat16 per row
     uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + QH_BYTES);
-    // q_full, kv_full[2], kv_free[2], s_full[2], p_ready, pv_done
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+    // q_full, k_full[2], k_free[2], s_full[2], p_ready, pv_done, v_full[2], v_free[2].  Keys and values of a stage have
+    // barriers of their own: a page's keys are done with when its scores are computed, a whole softmax before its values
+    // are, and the next-but-one page's keys can be on their way that much earlier (with one barrier for both, the softmax
+    // warps waited a third of every step for scores whose keys had been asked for too late).
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
     int& abort_flag = *reinterpret_cast<int*>(tmem_slot + 1);
-    const uint32_t b_q = smem_u32(&bars[0]), b_kvfull = smem_u32(&bars[1]), b_kvfree = smem_u32(&bars[3]);
+    const uint32_t b_q = smem_u32(&bars[0]), b_kfull = smem_u32(&bars[1]), b_kfree = smem_u32(&bars[3]);
     const uint32_t b_sfull = smem_u32(&bars[5]), b_pready = smem_u32(&bars[7]), b_pvdone = smem_u32(&bars[8]);
+    const uint32_t b_vfull = smem_u32(&bars[9]), b_vfree = smem_u32(&bars[11]);
 
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -115,7 +119,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     if (threadIdx.x == 0) {
         abort_flag = 0;
         mbar_init(b_q, 1);
-        for (int s = 0; s < 2; ++s) { mbar_init(b_kvfull + 8 * s, 1); mbar_init(b_kvfree + 8 * s, 1); }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(b_kfull + 8 * s, 1); mbar_init(b_kfree + 8 * s, 1);
+            mbar_init(b_vfull + 8 * s, 1); mbar_init(b_vfree + 8 * s, 1);
+        }
         mbar_init(b_sfull, 1);
         mbar_init(b_sfull + 8, 1);
         mbar_init(b_pready, 128);
@@ -144,14 +151,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 tma_load_2d(smem_u32(q_s + h * QH_BYTES), &map_q, head * HD + h * 64, row_base, b_q);
             for (int t = 0; t < n_kt; ++t) {
                 const int st = t & 1;
-                if (!mbar_wait(b_kvfree + 8 * st, ((t >> 1) & 1) ^ 1, &abort_flag)) break;
-                mbar_expect_tx(b_kvfull + 8 * st, 2 * KV_BYTES);
                 uint8_t* kd = kv_s + (size_t)st * 2 * KV_BYTES;
                 const int row = (bt[kt_lo + t] * nkv + kvh) * RF_PAGE;
-                for (int h = 0; h < HALVES; ++h) {
-                    tma_load_2d(smem_u32(kd + h * KH_BYTES), &map_k, h * 64, row, b_kvfull + 8 * st);
-                    tma_load_2d(smem_u32(kd + KV_BYTES + h * KH_BYTES), &map_v, h * 64, row, b_kvfull + 8 * st);
-                }
+                if (!mbar_wait(b_kfree + 8 * st, ((t >> 1) & 1) ^ 1, &abort_flag)) break;
+                mbar_expect_tx(b_kfull + 8 * st, KV_BYTES);
+                for (int h = 0; h < HALVES; ++h)
+                    tma_load_2d(smem_u32(kd + h * KH_BYTES), &map_k, h * 64, row, b_kfull + 8 * st);
+                if (!mbar_wait(b_vfree + 8 * st, ((t >> 1) & 1) ^ 1, &abort_flag)) break;
+                mbar_expect_tx(b_vfull + 8 * st, KV_BYTES);
+                for (int h = 0; h < HALVES; ++h)
+                    tma_load_2d(smem_u32(kd + KV_BYTES + h * KH_BYTES), &map_v, h * 64, row, b_vfull + 8 * st);
             }
         }
     } else if (warp == 1) {
@@ -162,7 +171,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             // warps are still busy with page t, so they find their next input ready when they come back.
             auto issue_s = [&](int t) -> bool {
                 const int st = t & 1;
-                if (!mbar_wait(b_kvfull + 8 * st, (t >> 1) & 1, &abort_flag)) return false;
+                if (!mbar_wait(b_kfull + 8 * st, (t >> 1) & 1, &abort_flag)) return false;
                 tcgen05_fence_after();
                 const uint32_t k_t = smem_u32(kv_s + (size_t)st * 2 * KV_BYTES);
 #pragma unroll
@@ -170,6 +179,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     tcgen05_mma_bf16(tmem_s + st * AT_BN, make_smem_desc(smem_u32(q_s) + (ks >> 2) * QH_BYTES + (ks & 3) * 32),
                                      make_smem_desc(k_t + (ks >> 2) * KH_BYTES + (ks & 3) * 32), idesc_s, ks ? 1u : 0u);
                 tcgen05_commit(b_sfull + 8 * st);
+                tcgen05_commit(b_kfree + 8 * st);          // the keys of this stage are consumed
                 return true;
             };
             bool ok = mbar_wait(b_q, 0, &abort_flag);
@@ -179,13 +189,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 if (t + 1 < n_kt) { ok = issue_s(t + 1); if (!ok) break; }
                 ok = mbar_wait(b_pready, t & 1, &abort_flag);          // P(t) is in shared memory, S(t) has been read
                 if (!ok) break;
+                ok = mbar_wait(b_vfull + 8 * st, (t >> 1) & 1, &abort_flag);
+                if (!ok) break;
                 tcgen05_fence_after();
                 const uint32_t v_t = smem_u32(kv_s + (size_t)st * 2 * KV_BYTES) + KV_BYTES;
 #pragma unroll
                 for (int ks = 0; ks < AT_BN / 16; ++ks)   // O += P V over the page's 64 keys
                     tcgen05_mma_bf16(tmem_o, make_smem_desc(smem_u32(p_s) + ks * 32),
                                      make_smem_desc_mn(v_t + ks * 16 * 128, KH_BYTES), idesc_o, (t | ks) ? 1u : 0u);
-                tcgen05_commit(b_kvfree + 8 * st);        // keys and values of this stage are consumed
+                tcgen05_commit(b_vfree + 8 * st);         // the values of this stage are consumed
                 tcgen05_commit(b_pvdone);
             }
         }
@@ -209,6 +221,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             // the value rows past the sequence's end were never written (or belong to a page that was not
             // loaded): their weights are zero, but 0 * (whatever bits lie there) must be 0
             if (key0 + AT_BN - 1 > seq_last) {
+                ok = mbar_wait(b_vfull + 8 * st, (t >> 1) & 1, &abort_flag);      // the page's values have landed
+                if (!ok) break;
                 uint8_t* v_t = kv_s + (size_t)st * 2 * KV_BYTES + KV_BYTES;
                 const int first_bad = seq_last + 1 - key0;
                 for (int i = threadIdx.x - 64; i < (AT_BN - first_bad) * HALVES * 8; i += 128) {
@@ -337,7 +351,7 @@ static int at_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtenso
                      const int* tiles, int n_tiles, const int* seq_slot, const int* seq_start, const int* seq_nnew,
                      const int* cu_q, const int* block_table, int max_pages, int nh, int nkv, float scale, int window,
                      int* status, cudaStream_t st) {
-    constexpr size_t smem = (size_t)(HD / 64) * AT_BM * 128 + 4 * (size_t)(HD / 64) * AT_BN * 128 + AT_BM * 128 + 9 * 8 + 16;
+    constexpr size_t smem = (size_t)(HD / 64) * AT_BM * 128 + 4 * (size_t)(HD / 64) * AT_BN * 128 + AT_BM * 128 + 13 * 8 + 16;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
