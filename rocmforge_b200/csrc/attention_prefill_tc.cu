@@ -48,6 +48,15 @@ __device__ __forceinline__ void tcgen05_st32(uint32_t taddr, const uint32_t* r) 
           "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
 }
+// A operand in tensor memory (128 lanes = rows, two bfloat16 per 32-bit column), B through a shared-memory descriptor.
+__device__ __forceinline__ void tcgen05_mma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                                    uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void tcgen05_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void at_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -87,8 +96,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     extern __shared__ __align__(1024) uint8_t smem[];   // no static shared memory: the window starts aligned
     uint8_t* q_s = smem;                                 // [HALVES][128][128 B]
     uint8_t* kv_s = q_s + Q_BYTES;                       // [2 stages][K | V][HALVES][64][128 B]
-    uint8_t* p_s = kv_s + 4 * KV_BYTES;                  // [128][128 B]: 64 keys of bfloat16 per row
-    uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + QH_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(kv_s + 4 * KV_BYTES);
     // q_full, k_full[2], k_free[2], s_full[2], p_ready, pv_done, v_full[2], v_free[2].  Keys and values of a stage have
     // barriers of their own: a page's keys are done with when its scores are computed, a whole softmax before its values
     // are, and the next-but-one page's keys can be on their way that much earlier (with one barrier for both, the softmax
@@ -195,7 +203,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 const uint32_t v_t = smem_u32(kv_s + (size_t)st * 2 * KV_BYTES) + KV_BYTES;
 #pragma unroll
                 for (int ks = 0; ks < AT_BN / 16; ++ks)   // O += P V over the page's 64 keys
-                    tcgen05_mma_bf16(tmem_o, make_smem_desc(smem_u32(p_s) + ks * 32),
+                    tcgen05_mma_bf16_ts(tmem_o, tmem_s + st * AT_BN + ks * 8,
                                      make_smem_desc_mn(v_t + ks * 16 * 128, KH_BYTES), idesc_o, (t | ks) ? 1u : 0u);
                 tcgen05_commit(b_vfree + 8 * st);         // the values of this stage are consumed
                 tcgen05_commit(b_pvdone);
@@ -220,7 +228,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             tcgen05_fence_after();
             // the value rows past the sequence's end were never written (or belong to a page that was not
             // loaded): their weights are zero, but 0 * (whatever bits lie there) must be 0
-            if (key0 + AT_BN - 1 > seq_last) {
+            const bool cleared = key0 + AT_BN - 1 > seq_last;
+            if (cleared) {
                 ok = mbar_wait(b_vfull + 8 * st, (t >> 1) & 1, &abort_flag);      // the page's values have landed
                 if (!ok) break;
                 uint8_t* v_t = kv_s + (size_t)st * 2 * KV_BYTES + KV_BYTES;
@@ -280,34 +289,35 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 pk[(j >> 1) + 1] = at_pack_bf16x2(p2, p3);
             }
             const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-            // the previous P V must be complete before P is overwritten or O touched
-            if (t > 0) {
-                ok = mbar_wait(b_pvdone, (t - 1) & 1, &abort_flag);
+            // P takes the place of this page's scores in tensor memory: 64 bfloat16 = 32 columns of this thread's lane, the
+            // A operand of P V as they lie (no way through shared memory, no proxy fence, and nothing of the previous P V
+            // is overwritten, so P need not wait for it)
+            tcgen05_st32(tmem_s + st * AT_BN + lane_base, pk);
+            bool seen = false;                           // whether this step has looked at the previous P V's barrier
+            if (t > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
+                ok = mbar_wait(b_pvdone, (t - 1) & 1, &abort_flag);       // O is touched: that product must be complete
                 if (!ok) break;
+                seen = true;
                 tcgen05_fence_after();
-                if (__any_sync(0xffffffffu, corr != 1.f)) {
 #pragma unroll 1
-                    for (int c0 = 0; c0 < HD; c0 += 32) {
-                        uint32_t r[32];
-                        tcgen05_ld32(tmem_o + lane_base + c0, r);
-                        tcgen05_wait_ld();
+                for (int c0 = 0; c0 < HD; c0 += 32) {
+                    uint32_t r[32];
+                    tcgen05_ld32(tmem_o + lane_base + c0, r);
+                    tcgen05_wait_ld();
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * corr);
-                        tcgen05_st32(tmem_o + lane_base + c0, r);
-                    }
-                    tcgen05_wait_st();
+                    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * corr);
+                    tcgen05_st32(tmem_o + lane_base + c0, r);
                 }
             }
+            tcgen05_wait_st();
             l = l * corr + sum;
-            // P as a swizzled K-major bfloat16 operand: this thread's row, 8 chunks of 8 keys
-            const uint32_t prow = smem_u32(p_s) + row * 128;
-#pragma unroll
-            for (int q = 0; q < 8; ++q)
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(prow + ((q ^ (row & 7)) << 4)),
-                             "r"(pk[4 * q]), "r"(pk[4 * q + 1]), "r"(pk[4 * q + 2]), "r"(pk[4 * q + 3]) : "memory");
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P (and cleared value rows) are for the MMA to read
+            if (cleared) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the cleared value rows are for the MMA to read
             tcgen05_fence_before();
             at_arrive(b_pready);
+            if (t > 0 && !seen) {                        // every phase of that barrier is seen once, or its parity says nothing
+                ok = mbar_wait(b_pvdone, (t - 1) & 1, &abort_flag);
+                if (!ok) break;
+            }
         }
         if (ok && n_kt > 0) ok = mbar_wait(b_pvdone, (n_kt - 1) & 1, &abort_flag);
         if (ok) {
@@ -351,7 +361,7 @@ static int at_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtenso
                      const int* tiles, int n_tiles, const int* seq_slot, const int* seq_start, const int* seq_nnew,
                      const int* cu_q, const int* block_table, int max_pages, int nh, int nkv, float scale, int window,
                      int* status, cudaStream_t st) {
-    constexpr size_t smem = (size_t)(HD / 64) * AT_BM * 128 + 4 * (size_t)(HD / 64) * AT_BN * 128 + AT_BM * 128 + 13 * 8 + 16;
+    constexpr size_t smem = (size_t)(HD / 64) * AT_BM * 128 + 4 * (size_t)(HD / 64) * AT_BN * 128 + 13 * 8 + 16;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
