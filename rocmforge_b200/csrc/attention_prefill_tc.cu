@@ -6,7 +6,7 @@
 //     S[128 x 64]   = Q K^T              tcgen05.mma, A = Q tile, B = key tile, both K-major
 //     softmax       : four warps, one thread per query row: the row of S comes out of tensor memory
 //                     with tcgen05.ld, so its maximum and sum need no shuffles; 32-bit throughout
-//     P (bfloat16)  -> shared memory, swizzled as a K-major A operand
+//     P (bfloat16)  -> tensor memory, in place of the scores it was made from: the A operand of the next product
 //     O[128 x hd]  += P V                tcgen05.mma, B = value tile read as an MN-major operand
 // O stays in tensor memory for the whole row tile.  The reference point of the exponentials is only
 // moved when a row's maximum has grown by more than 8 (in log2 units): weights then stay below 2^8,
