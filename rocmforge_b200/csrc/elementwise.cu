@@ -261,9 +261,17 @@ __global__ void rope_kv_write_kernel(const void* __restrict__ src, int row_strid
     if (PARTIALS) {
         const float* p = reinterpret_cast<const float*>(src) + (size_t)t * row_stride;
         x0 = b0; x1 = b1;
-        for (int sp = 0; sp < n_partials; ++sp) {       // in index order
-            x0 += p[(size_t)sp * partial_stride + col0];
-            x1 += p[(size_t)sp * partial_stride + col1];
+        for (int sp = 0; sp < n_partials; sp += 8) {    // eight pairs of loads in flight at once, added in index order
+            float u0[8], u1[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (sp + u < n_partials) {
+                    u0[u] = p[(size_t)(sp + u) * partial_stride + col0];
+                    u1[u] = p[(size_t)(sp + u) * partial_stride + col1];
+                }
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (sp + u < n_partials) { x0 += u0[u]; x1 += u1[u]; }
         }
     } else {
         x0 = Cvt<T>::to_f32(reinterpret_cast<const T*>(src)[(size_t)t * row_stride + col0]);
