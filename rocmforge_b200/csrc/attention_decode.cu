@@ -582,21 +582,29 @@ attention_decode_warps_kernel(const __grid_constant__ CUtensorMap map_k, const _
     const int DS = HD / splits;                          // output dimensions per CTA of the cluster
     const int slot_floats = 2 * DEC_GP + DEC_GP * DS;
     if (splits > 1) asm volatile("barrier.cluster.wait.aligned;" ::: "memory");      // all peers run (see the arrive above)
-    for (int i = tid; i < G * HD; i += NT) {
-        const int g = i / HD, d = i - g * HD;
-        float O = 0.f;
+    // four neighbouring dimensions per thread: eight 16-byte loads from the warps' states and one 16-byte (remote) store
+    // instead of four times as many scalar ones (the scalar form took 0.9 us of a 6 us kernel)
+    for (int i = tid; i < G * (HD / 4); i += NT) {
+        const int g = i / (HD / 4), d = (i - g * (HD / 4)) * 4;
+        float O[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int w = 0; w < WARPS; ++w)
-            O += f_w[w * DEC_GP + g] * reinterpret_cast<const float*>(ring + (size_t)w * 2 * TILE)[2 * DEC_GP + g * SP + d];
+        for (int w = 0; w < WARPS; ++w) {
+            const float f = f_w[w * DEC_GP + g];
+            const float4 v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(ring + (size_t)w * 2 * TILE) + 2 * DEC_GP + g * SP + d);
+            O[0] += f * v.x; O[1] += f * v.y; O[2] += f * v.z; O[3] += f * v.w;
+        }
         if (splits == 1) {
-            if (!gave_up)
-                out[(size_t)b * out_stride + (size_t)(kvh * G + g) * HD + d] = __float2bfloat16_rn(c_l[g] > 0.f ? O / c_l[g] : 0.f);
-        } else {                                         // to the CTA that owns dimension d, into this CTA's slot there
+            if (!gave_up) {
+                __nv_bfloat16* o = out + (size_t)b * out_stride + (size_t)(kvh * G + g) * HD + d;
+#pragma unroll
+                for (int u = 0; u < 4; ++u) o[u] = __float2bfloat16_rn(c_l[g] > 0.f ? O[u] / c_l[g] : 0.f);
+            }
+        } else {                                         // to the CTA that owns these dimensions, into this CTA's slot there
             const int t = d / DS;
             uint32_t raddr;
             asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr)
                          : "r"(dec_smem_u32(slots + rank * slot_floats + 2 * DEC_GP + g * DS + (d - t * DS))), "r"(t));
-            asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(raddr), "f"(O) : "memory");
+            asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(raddr), "f"(O[0]), "f"(O[1]), "f"(O[2]), "f"(O[3]) : "memory");
         }
     }
     if (splits > 1) {
