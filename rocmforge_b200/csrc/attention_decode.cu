@@ -564,19 +564,23 @@ attention_decode_warps_kernel(const __grid_constant__ CUtensorMap map_k, const _
         }
     }
     __syncthreads();
-    if (tid < DEC_GP) {                                  // the warps' weights for head tid, and the CTA's maximum and sum
-        float M = -INFINITY;
+    if (tid < WARPS * DEC_GP) {
+        // the warps' weights for every head, and the CTA's maximum and sum: thread (head g, warp w) with the warps of a head
+        // in neighbouring lanes, so that maximum and sum are shuffles over WARPS lanes instead of one thread's loops
+        const int g = tid / WARPS, w = tid % WARPS;
+        const float* st = reinterpret_cast<const float*>(ring + (size_t)w * 2 * TILE);
+        const float m = st[g];
+        float M = m;
 #pragma unroll
-        for (int w = 0; w < WARPS; ++w) M = fmaxf(M, reinterpret_cast<const float*>(ring + (size_t)w * 2 * TILE)[tid]);
+        for (int o = 1; o < WARPS; o <<= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+        const float f = m == -INFINITY ? 0.f : expf(m - M);
+        f_w[w * DEC_GP + g] = f;
+        // the sum in the warps' index order, whatever the lanes' timing: lane (g, 0) adds its neighbours' terms one by one
+        const float term = f * st[DEC_GP + g];
         float L = 0.f;
 #pragma unroll
-        for (int w = 0; w < WARPS; ++w) {                // warps in index order
-            const float* st = reinterpret_cast<const float*>(ring + (size_t)w * 2 * TILE);
-            const float f = st[tid] == -INFINITY ? 0.f : expf(st[tid] - M);
-            f_w[w * DEC_GP + tid] = f;
-            L += f * st[DEC_GP + tid];
-        }
-        c_m[tid] = M; c_l[tid] = L;
+        for (int k = 0; k < WARPS; ++k) L += __shfl_sync(0xffffffffu, term, (tid & 31) - w + k);
+        if (w == 0) { c_m[g] = M; c_l[g] = L; }
     }
     __syncthreads();
     const int DS = HD / splits;                          // output dimensions per CTA of the cluster
@@ -620,8 +624,10 @@ attention_decode_warps_kernel(const __grid_constant__ CUtensorMap map_k, const _
             for (int i = tid; i < G * DS; i += NT) {
                 const int g = i / DS, dd = i - g * DS;
                 float M = -INFINITY;
+#pragma unroll 4
                 for (int r = 0; r < splits; ++r) M = fmaxf(M, slots[r * slot_floats + g]);
                 float L = 0.f, O = 0.f;
+#pragma unroll 4
                 for (int r = 0; r < splits; ++r) {       // CTAs in rank order
                     const float* sl = slots + r * slot_floats;
                     const float f = sl[g] == -INFINITY ? 0.f : expf(sl[g] - M);
