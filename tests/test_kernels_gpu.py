@@ -69,6 +69,29 @@ def test_add_rmsnorm(dt, H):
 
 
 @pytest.mark.parametrize("dt", DTS)
+@pytest.mark.parametrize("H", [24, 1000, 3584, 5120, 9000])
+def test_add_rmsnorm_of_a_prompt_step(dt, H):
+    """Many rows without a pending update take a kernel of their own (rows read twice, the second time from L1); with a
+    pending update or a row gather the other one.  All against the plain norm; the two kernels differ by the order of a
+    row's sum of squares at most."""
+    from rocmforge_b200 import kernels
+    T = 700
+    h = rnd(T, H, seed=11)
+    for wdt in (torch.float32, torch.bfloat16):
+        w = rnd(H, dt=wdt, seed=12) + 1.0
+        h0 = h.clone()
+        y = kernels.add_rmsnorm(h0, w, 1e-6, dt)
+        assert torch.equal(h0, h) and tuple(y.shape) == (T, H) and y.dtype == dt
+        torch.testing.assert_close(y.double(), P.rms_norm(h.double(), w.double(), 1e-6), **tol(dt))
+        # the same rows with a zero update: the kernel that keeps a row in registers
+        y2 = kernels.add_rmsnorm(h.clone(), w, 1e-6, dt, pending=torch.zeros(1, T, H, device=DEV))
+        torch.testing.assert_close(y2.float(), y.float(), atol=1e-6 if dt == torch.float32 else 2e-2, rtol=1e-6 if dt == torch.float32 else 1e-2)
+        rows = torch.arange(0, T, 7, dtype=torch.int32, device=DEV)
+        y3 = kernels.add_rmsnorm(h.clone(), w, 1e-6, dt, rows=rows)
+        torch.testing.assert_close(y3.double(), P.rms_norm(h[rows.long()].double(), w.double(), 1e-6), **tol(dt))
+
+
+@pytest.mark.parametrize("dt", DTS)
 @pytest.mark.parametrize("H", [896, 3584, 4100, 5120, 8192, 16384])
 def test_add_rmsnorm_rows_shared_by_a_cluster_give_the_bits_of_one_block(dt, H):
     """With few rows a row's threads are spread over a thread-block cluster (up to 8 CTAs); with many rows one
