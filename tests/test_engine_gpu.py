@@ -43,6 +43,30 @@ def poison_free_pages(cache):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", ["D", "E"])
+def test_a_prompt_of_more_than_512_tokens(folders, name, dtype):
+    """From 512 rows on a prompt step's norm takes a kernel of its own, its attention walks ten and more pages per
+    query tile (E: a window of 200 far behind the newest token), and two prompts in one step share the tile table.
+    Logits at a spread of places, then a few decoded tokens, against the plain model."""
+    from rocmforge_b200 import StepRequest
+    m, p = engine(folders, name, dtype), plain(folders, name, dtype)
+    V = CONFIGS[name]["vocab_size"]
+    cache = m.new_cache(max_tokens=64 * 26, max_slots=4)
+    poison_free_pages(cache)
+    a, b = random_tokens(V, 700, 41), random_tokens(V, 530, 42)
+    ra, rb = p.logits(a), p.logits(b)
+    sa, sb = cache.alloc_slot(), cache.alloc_slot()
+    wa, wb = [0, 1, 63, 64, 199, 200, 201, 511, 512, 513, 639, 640, 689], [0, 255, 256, 511, 512, 519]
+    got = m.step(cache, [StepRequest(sa, a[:690], wa), StepRequest(sb, b[:520], wb)]).cpu()
+    assert_logits_close(got, torch.cat([ra[wa], rb[wb]]), dtype, f"{name} {dtype} two long prompts")
+    for k in range(10):
+        got = m.step(cache, [StepRequest(sa, [a[690 + k]], [0]), StepRequest(sb, [b[520 + k]], [0])]).cpu()
+        assert_logits_close(got, torch.stack([ra[690 + k], rb[520 + k]]), dtype, f"{name} {dtype} decode {k} after long prompts")
+    cache.free_slot(sa); cache.free_slot(sb)
+    assert cache.live_slots == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["D", "E"])
 def test_tuned_kernel_paths_prompt_chunk_decode_and_batch(folders, name, dtype):
     """Sizes at which the bfloat16 engine runs its tensor-core products (clustered for >= 256 rows), the tiled
     prefill attention and the chunked decode attention: a 300-token prompt, a chunk, decoding across page and
