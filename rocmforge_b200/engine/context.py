@@ -103,7 +103,7 @@ class StepContext:
                                                            splits=tc.resnorm_splits(w.shape[0], w.shape[1]), row_ss=row_ss)
                     stream.prepared = (follows, ScaledRows(normed, ss, deferred[1], w.shape[0]))
                     return
-                splits = tc.split_k_for(w.shape[0], w.shape[1]) if bias is None else 1
+                splits = tc.split_k_for(w.shape[0], w.shape[1], tokens=x.shape[0]) if bias is None else 1
                 if splits > 1:
                     stream.add_pending(tc.gemm_tc_skinny(x, w, mode=tc.PARTIAL, splits=splits, row_ss=row_ss))
                     return

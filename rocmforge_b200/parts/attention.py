@@ -117,7 +117,7 @@ class GQAAttention(Mixer):
         rope = dict(rot_dim=rot["rot_dim"], interleaved=rot.get("interleaved", False), tok_seq=ctx.tok_seq, tok_pos=ctx.tok_pos, seq_slot=ctx.seq_slot,
                     block_table=view.block_table, k_pages=view.k_pages, v_pages=view.v_pages, write_kv=view.writes)
         if y.shape[0] <= tc.SKINNY_MAX_TOKENS and ctx.uses_tensor_cores(y, w, tc.PARTIAL):
-            splits = tc.split_k_for(w.shape[0], w.shape[1])
+            splits = tc.split_k_for(w.shape[0], w.shape[1], tokens=y.shape[0])
             if splits > 1:
                 parts = tc.gemm_tc_skinny(y, w, mode=tc.PARTIAL, splits=splits, row_ss=row_ss)
                 return kernels.rope_kv_write(parts, self.n_heads, self.n_kv_heads, self.head_dim,

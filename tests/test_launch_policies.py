@@ -3,7 +3,7 @@ from rocmforge_b200.kernels import basic
 from rocmforge_b200.kernels import tensor_core as tc
 
 
-def test_k_splits_depend_on_the_weight_shape_alone():
+def test_k_splits_depend_on_the_weight_shape_and_the_token_bucket():
     # Qwen2.5-7B layer shapes: about two CTAs per SM, every split at least four blocks of 64
     assert tc.split_k_for(37888, 3584) == 1            # 296 tiles fill the GPU without a split
     for N, K in ((4608, 3584), (3584, 3584), (3584, 18944), (152064, 3584), (128, 64), (1000, 200)):
@@ -14,6 +14,12 @@ def test_k_splits_depend_on_the_weight_shape_alone():
         assert s == 1 or kb // s >= 4
         tiles = (N + 127) // 128
         assert s == 1 or tiles * s <= 2 * 148, "a split product stays within two CTAs per SM"
+        # a step of at most 16 tokens fits three CTAs on an SM: long K ranges are then cut finer, short ones stay
+        few = tc.split_k_for(N, K, tokens=8)
+        assert few >= s and (few == s or (tiles * few <= 3 * 148 and kb // few >= 16))
+        assert tc.split_k_for(N, K, tokens=17) == s and tc.split_k_for(N, K, tokens=128) == s
+    assert tc.split_k_for(3584, 18944, tokens=1) == 15 and tc.split_k_for(3584, 18944) == 10
+    assert tc.split_k_for(4608, 3584, tokens=1) == 8 and tc.split_k_for(3584, 3584, tokens=16) == 10
 
 
 def test_decode_cluster_size_from_batch_and_context():
