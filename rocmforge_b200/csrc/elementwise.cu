@@ -131,8 +131,11 @@ __device__ __forceinline__ float cluster_block_sum(float v, float* red, int vt, 
     return red[32];
 }
 
-template <typename T, int NV>
-__global__ void __launch_bounds__(1024)
+// INF: partial sums of one element group asked for at once.  A decode step's norm is a chain of L2 round trips and
+// nothing else; ten or fifteen K splits read four at a time (and the rest one by one) were four to six trips, sixteen at
+// a time they are one.  The wide form needs its registers: it is compiled for blocks of at most 256 threads.
+template <typename T, int NV, int INF, int MAXT>
+__global__ void __launch_bounds__(MAXT)
 add_rmsnorm_vec_kernel(float* __restrict__ h, const void* __restrict__ pending, int pending_kind, int n_pending,
                        size_t pending_stride, const void* __restrict__ w, int w_is_f32, float eps,
                        T* __restrict__ y, const int* __restrict__ rows, int H, int cl) {
@@ -170,18 +173,31 @@ add_rmsnorm_vec_kernel(float* __restrict__ h, const void* __restrict__ pending, 
             float4 a = hrow[c];
             if (pending_kind == 1) {
                 const float4* p = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(pending) + (size_t)t * H) + c;
-                int s2 = 0;
-                for (; s2 + 4 <= n_pending; s2 += 4) {       // four loads in flight, added in index order
-                    float4 b[4];
+                if constexpr (INF > 4) {
+                    for (int s2 = 0; s2 < n_pending; s2 += INF) {    // INF loads in flight, added in index order
+                        float4 b[INF];
 #pragma unroll
-                    for (int u = 0; u < 4; ++u)
-                        b[u] = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + (size_t)(s2 + u) * pending_stride);
+                        for (int u = 0; u < INF; ++u)
+                            if (s2 + u < n_pending)
+                                b[u] = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + (size_t)(s2 + u) * pending_stride);
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) { a.x += b[u].x; a.y += b[u].y; a.z += b[u].z; a.w += b[u].w; }
-                }
-                for (; s2 < n_pending; ++s2) {
-                    const float4 b = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + (size_t)s2 * pending_stride);
-                    a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+                        for (int u = 0; u < INF; ++u)
+                            if (s2 + u < n_pending) { a.x += b[u].x; a.y += b[u].y; a.z += b[u].z; a.w += b[u].w; }
+                    }
+                } else {
+                    int s2 = 0;
+                    for (; s2 + 4 <= n_pending; s2 += 4) {   // four loads in flight, added in index order
+                        float4 b[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u)
+                            b[u] = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + (size_t)(s2 + u) * pending_stride);
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) { a.x += b[u].x; a.y += b[u].y; a.z += b[u].z; a.w += b[u].w; }
+                    }
+                    for (; s2 < n_pending; ++s2) {
+                        const float4 b = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + (size_t)s2 * pending_stride);
+                        a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+                    }
                 }
             } else if (pending_kind == 2) {
                 const T* p = reinterpret_cast<const T*>(pending) + (size_t)t * H + 4 * c;
@@ -451,9 +467,12 @@ static int launch_add_rmsnorm(float* h, const void* pending, int kind, int n_pen
             if (cl > 1) rf_launch_cluster(kernel, grid, block, 0, st, cl, h, pending, kind, n_pending, pstride, w, w_is_f32, eps, yy, rows, H, cl);
             else rf_launch(kernel, grid, block, 0, st, h, pending, kind, n_pending, pstride, w, w_is_f32, eps, yy, rows, H, cl);
         };
-        if (per <= 1) go(add_rmsnorm_vec_kernel<T, 1>);
-        else if (per <= 2) go(add_rmsnorm_vec_kernel<T, 2>);
-        else go(add_rmsnorm_vec_kernel<T, 4>);
+        const bool wide = block.x <= 256 && kind == 1 && n_pending > 4;      // K splits to add up, and room for the registers
+        if (per <= 1 && wide) go(add_rmsnorm_vec_kernel<T, 1, 16, 256>);
+        else if (per <= 2 && wide) go(add_rmsnorm_vec_kernel<T, 2, 8, 256>);
+        else if (per <= 1) go(add_rmsnorm_vec_kernel<T, 1, 4, 1024>);
+        else if (per <= 2) go(add_rmsnorm_vec_kernel<T, 2, 4, 1024>);
+        else go(add_rmsnorm_vec_kernel<T, 4, 4, 1024>);
         RF_LAUNCH_CHECK();
         return 0;
     }

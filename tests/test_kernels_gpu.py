@@ -99,7 +99,7 @@ def test_add_rmsnorm_rows_shared_by_a_cluster_give_the_bits_of_one_block(dt, H):
     (a token's norm must not depend on the size of its batch)."""
     from rocmforge_b200 import kernels
     w = rnd(H, dt=torch.bfloat16, seed=2) + 1.0
-    for n_pending in (0, 1, 3, 10):
+    for n_pending in (0, 1, 3, 10, 17):     # from five on, small blocks ask for sixteen (eight) partial sums at once
         h = rnd(5, H, seed=5)
         parts = rnd(n_pending, 5, H, seed=6) if n_pending else None
         many_h, many_parts = h.repeat(80, 1), (parts.repeat(1, 80, 1) if n_pending else None)     # 400 rows: no clusters
