@@ -42,7 +42,7 @@ SHAPE_14B = dict(architectures=["Qwen2ForCausalLM"], num_hidden_layers=48, hidde
 CONTEXT = 4096
 PROMPT_LEN = 512
 PREFILL_TOKENS = 2048
-POINTS_WARMUP = 48                   # untimed steps before the batch-1 and batch-64 points are timed
+SETTLE_STEPS = 48                    # untimed decode steps before any decode timing of the default run (see main)
 PREFILL_CHUNK = 16384          # most prompt tokens run in one step when a batch of prompts is brought into the cache
 
 
@@ -495,27 +495,32 @@ def main():
     pre_ms = prefill_rate(model, PREFILL_TOKENS, 3, args.seed + 2)
     sampler = ClockSampler()
     sampler.start()
-    main_run = decode_rate(model, random_prompts(args.batch, PROMPT_LEN, V, args.seed), args.steps, warmup)
+    # Steady decoding is what every decode number of this run means.  The steps right after a batch of prompts run at
+    # lower clocks (the power cap after the prompts' burst: 8 prompts of 512 tokens are 45 ms at full power, and the
+    # next 17 or so decode steps take 2.9 ms instead of 2.6), so each timing runs max(W, SETTLE_STEPS) untimed steps
+    # first and then times exactly K; what the first steps after the prompts give end to end stands in `points`.
+    settle = max(warmup, SETTLE_STEPS)
+    main_run = decode_rate(model, random_prompts(args.batch, PROMPT_LEN, V, args.seed), args.steps, settle)
     clocks = sampler.summary(main_run["t0"], main_run["t1"])
-    llm = rf.LLM(model, cache_tokens=args.batch * (PROMPT_LEN + warmup + args.steps + 80), max_batch=args.batch)
-    e2e = e2e_rate(llm, random_prompts(args.batch, PROMPT_LEN, V, args.seed + 1), args.steps, warmup=warmup)
+    llm = rf.LLM(model, cache_tokens=args.batch * (PROMPT_LEN + settle + args.steps + 80), max_batch=args.batch)
+    e2e = e2e_rate(llm, random_prompts(args.batch, PROMPT_LEN, V, args.seed + 1), args.steps, warmup=settle)
+    e2e["untimed_steps"] = settle
+    e2e_first = e2e_rate(llm, random_prompts(args.batch, PROMPT_LEN, V, args.seed + 1), args.steps, warmup=warmup)
     # the reference's own default is sampled decoding (temperature 1.0, top-p 0.9): the same loop with the device sampler
     sampled = e2e_rate(llm, random_prompts(args.batch, PROMPT_LEN, V, args.seed + 5), max(args.steps // 2, 16),
-                       temperature=1.0, top_p=0.9, warmup=warmup)
+                       temperature=1.0, top_p=0.9, warmup=settle)
     llm.cache = llm.engine = None
     del llm
     torch.cuda.empty_cache()
     points = {}
     if not args.skip_points:
-        # steady decoding: the steps right after a batch of prompts run at lower clocks (the power cap after the prompts'
-        # burst, some tens of milliseconds; 64 prompts of 512 tokens are a burst of a third of a second), so these two
-        # points time their steps after POINTS_WARMUP untimed ones
         for b, st in ((1, args.steps), (64, max(args.steps // 2, 16))):
-            r = decode_rate(model, random_prompts(b, PROMPT_LEN, V, args.seed + 3 + b), st, max(warmup, POINTS_WARMUP))
+            r = decode_rate(model, random_prompts(b, PROMPT_LEN, V, args.seed + 3 + b), st, settle)
             points[f"decode_b{b}"] = round(r["tok_s"], 1)
             points[f"decode_b{b}_hbm_frac"] = round(step_bytes(cfg, b, r["mean_ctx"]) / (r["ms_per_step"] / 1e3) / 1e9
                                                    / pk["hbm_gbs"], 4)
     points["e2e_sampled_t1.0_p0.9"] = round(sampled["value"], 1)
+    points[f"e2e_steps_{warmup + 1}_to_{warmup + args.steps}_after_the_prompts"] = round(e2e_first["value"], 1)
     nbytes = step_bytes(cfg, args.batch, main_run["mean_ctx"])
     achieved = nbytes / (main_run["ms_per_step"] / 1e3) / 1e9
     flops = prefill_flops(cfg, PREFILL_TOKENS)
@@ -527,7 +532,7 @@ def main():
 
     line = {
         "metric": METRIC, "value": round(main_run["tok_s"], 1), "unit": "tok/s", "n_gpus": 1,
-        "steps": args.steps, "warmup": warmup, "ms_per_step": round(main_run["ms_per_step"], 4),
+        "steps": args.steps, "warmup": warmup, "untimed_steps": settle, "ms_per_step": round(main_run["ms_per_step"], 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: seeded random token ids, random-init weights N(0, 0.02)", "impl": "ours",
         "config": {"model": "Qwen2.5-7B shape", "layers": cfg.num_hidden_layers, "layers_of_config": 28,
@@ -537,7 +542,8 @@ def main():
                    "context_at_timing": int(main_run["mean_ctx"]), "parallelism": "none (1 GPU)",
                    "cache_page": 64, "l2": "inputs larger than L2 (15 GB of weights per step)",
                    "peaks": pk["source"],
-                   "points_decode": f"decode_b1, decode_b64: prompts of {PROMPT_LEN} tokens, {POINTS_WARMUP} untimed steps, then timed",
+                   "decode_timing": f"value, e2e, decode_b1, decode_b64: prompts of {PROMPT_LEN} tokens, {settle} untimed decode "
+                                    "steps (the clocks settle after the prompts' burst), then exactly `steps` timed",
                    "points_qwen0.5b": "Qwen2.5-0.5B shape, 24 layers, hidden 896, 14/2 heads of 64, intermediate 4864, "
                                       "vocab 151936 tied; batch 64, prompts uniform 16..1024 (seeded), 256 steps; bf16 and fp32",
                    "points_qwen14b": "Qwen2.5-14B shape, 48 layers, hidden 5120, 40/8 heads of 128, intermediate 13824, "

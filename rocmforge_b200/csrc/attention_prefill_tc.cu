@@ -97,15 +97,22 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     uint8_t* q_s = smem;                                 // [HALVES][128][128 B]
     uint8_t* kv_s = q_s + Q_BYTES;                       // [2 stages][K | V][HALVES][64][128 B]
     uint64_t* bars = reinterpret_cast<uint64_t*>(kv_s + 4 * KV_BYTES);
-    // q_full, k_full[2], k_free[2], s_full[2], p_ready, pv_done, v_full[2], v_free[2].  Keys and values of a stage have
+    // q_full, k_full[2], k_free[2], s_full[2], p_ready[2], pv_done[2], v_full[2], v_free[2].  Keys and values of a stage have
     // barriers of their own: a page's keys are done with when its scores are computed, a whole softmax before its values
     // are, and the next-but-one page's keys can be on their way that much earlier (with one barrier for both, the softmax
     // warps waited a third of every step for scores whose keys had been asked for too late).
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+    // p_ready and pv_done alternate between two barriers from page to page.  A wait names a phase by its parity alone, so
+    // a barrier must never complete two phases between two looks of one of its waiters.  A softmax thread hands P(t) over
+    // BEFORE it looks at the P V of page t - 1 (unless it has to rescale O), so with one barrier each, a warp that was slow
+    // between those two instructions found P V(t - 1) and P V(t) both complete, read the parity as "not yet" and waited
+    // for a product that needed its own next arrival (and the MMA thread the same with the arrivals of pages t and t + 1):
+    // once in some thousand launches a CTA stood still until its wait ran out.  With two barriers the next phase of the
+    // one a thread waits on needs that thread's arrival of the page after next, which comes after the wait.
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
     int& abort_flag = *reinterpret_cast<int*>(tmem_slot + 1);
     const uint32_t b_q = smem_u32(&bars[0]), b_kfull = smem_u32(&bars[1]), b_kfree = smem_u32(&bars[3]);
-    const uint32_t b_sfull = smem_u32(&bars[5]), b_pready = smem_u32(&bars[7]), b_pvdone = smem_u32(&bars[8]);
-    const uint32_t b_vfull = smem_u32(&bars[9]), b_vfree = smem_u32(&bars[11]);
+    const uint32_t b_sfull = smem_u32(&bars[5]), b_pready = smem_u32(&bars[7]), b_pvdone = smem_u32(&bars[9]);
+    const uint32_t b_vfull = smem_u32(&bars[11]), b_vfree = smem_u32(&bars[13]);
 
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -133,8 +140,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         }
         mbar_init(b_sfull, 1);
         mbar_init(b_sfull + 8, 1);
-        mbar_init(b_pready, 128);
-        mbar_init(b_pvdone, 1);
+        mbar_init(b_pready, 128); mbar_init(b_pready + 8, 128);
+        mbar_init(b_pvdone, 1); mbar_init(b_pvdone + 8, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
@@ -195,7 +202,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             for (int t = 0; t < n_kt && ok; ++t) {
                 const int st = t & 1;
                 if (t + 1 < n_kt) { ok = issue_s(t + 1); if (!ok) break; }
-                ok = mbar_wait(b_pready, t & 1, &abort_flag);          // P(t) is in shared memory, S(t) has been read
+                ok = mbar_wait(b_pready + 8 * st, (t >> 1) & 1, &abort_flag);      // P(t) is in tensor memory, S(t) has been read
                 if (!ok) break;
                 ok = mbar_wait(b_vfull + 8 * st, (t >> 1) & 1, &abort_flag);
                 if (!ok) break;
@@ -206,7 +213,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     tcgen05_mma_bf16_ts(tmem_o, tmem_s + st * AT_BN + ks * 8,
                                      make_smem_desc_mn(v_t + ks * 16 * 128, KH_BYTES), idesc_o, (t | ks) ? 1u : 0u);
                 tcgen05_commit(b_vfree + 8 * st);         // the values of this stage are consumed
-                tcgen05_commit(b_pvdone);
+                tcgen05_commit(b_pvdone + 8 * st);
             }
         }
     } else {
@@ -295,7 +302,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             tcgen05_st32(tmem_s + st * AT_BN + lane_base, pk);
             bool seen = false;                           // whether this step has looked at the previous P V's barrier
             if (t > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
-                ok = mbar_wait(b_pvdone, (t - 1) & 1, &abort_flag);       // O is touched: that product must be complete
+                ok = mbar_wait(b_pvdone + 8 * ((t - 1) & 1), ((t - 1) >> 1) & 1, &abort_flag);   // O is touched: that product must be complete
                 if (!ok) break;
                 seen = true;
                 tcgen05_fence_after();
@@ -313,13 +320,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             l = l * corr + sum;
             if (cleared) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the cleared value rows are for the MMA to read
             tcgen05_fence_before();
-            at_arrive(b_pready);
-            if (t > 0 && !seen) {                        // every phase of that barrier is seen once, or its parity says nothing
-                ok = mbar_wait(b_pvdone, (t - 1) & 1, &abort_flag);
+            at_arrive(b_pready + 8 * st);
+            if (t > 0 && !seen) {                        // every phase of a barrier is seen once, or its parity says nothing
+                ok = mbar_wait(b_pvdone + 8 * ((t - 1) & 1), ((t - 1) >> 1) & 1, &abort_flag);
                 if (!ok) break;
             }
         }
-        if (ok && n_kt > 0) ok = mbar_wait(b_pvdone, (n_kt - 1) & 1, &abort_flag);
+        if (ok && n_kt > 0) ok = mbar_wait(b_pvdone + 8 * ((n_kt - 1) & 1), ((n_kt - 1) >> 1) & 1, &abort_flag);
         if (ok) {
             tcgen05_fence_after();
             const float inv = l > 0.f ? 1.f / l : 0.f;
@@ -361,7 +368,7 @@ static int at_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtenso
                      const int* tiles, int n_tiles, const int* seq_slot, const int* seq_start, const int* seq_nnew,
                      const int* cu_q, const int* block_table, int max_pages, int nh, int nkv, float scale, int window,
                      int* status, cudaStream_t st) {
-    constexpr size_t smem = (size_t)(HD / 64) * AT_BM * 128 + 4 * (size_t)(HD / 64) * AT_BN * 128 + 13 * 8 + 16;
+    constexpr size_t smem = (size_t)(HD / 64) * AT_BM * 128 + 4 * (size_t)(HD / 64) * AT_BN * 128 + 15 * 8 + 16;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
