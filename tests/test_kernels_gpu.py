@@ -464,6 +464,48 @@ def test_attention_prefill(nh, nkv, hd, window, kernel):
             t += 1
 
 
+def test_attention_prefill_gives_the_same_bits_launch_after_launch():
+    """Many short launches of the tcgen05 kernel over ragged sequences of one to six pages: every launch the bits of the
+    first one and no wait that ran out.  The kernel's warps hand work to each other through barriers that are
+    told apart by one parity bit; a barrier that completes two phases between two looks of a waiter shows here as a CTA
+    that stands still until its wait's limit, or as other bits."""
+    from rocmforge_b200 import kernels
+    from rocmforge_b200.kernels import tensor_core as tc
+    dt, nh, nkv, hd = torch.bfloat16, 14, 2, 64
+    g = torch.Generator().manual_seed(21)
+    lens = torch.randint(1, 400, (48,), generator=g).tolist()
+    ks, vs, k_pages, v_pages, table = paged(lens, nkv, hd, dt, n_pages=sum((n + 63) // 64 for n in lens) + 2, seed=8)
+    T = sum(lens)
+    q = torch.randn(T, nh * hd, generator=g).to(dt).to(DEV)
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    tiles = [(i, q0) for i, n in enumerate(lens) for q0 in range(0, n, 128)]
+    dev = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    args = (dev(tiles).view(-1), dev(list(range(1, len(lens) + 1))), dev([0] * len(lens)), dev(lens), dev(cu), table,
+            1.0 / math.sqrt(hd), None)
+    first = kernels.attention_prefill_tc(q, nh, nkv, hd, k_pages, v_pages, *args).clone()
+    t = 0
+    for s, n in enumerate(lens[:6]):
+        ref = attention_reference(q[t + n - 1].cpu().view(nh, hd), ks[s], vs[s], n - 1, 1.0 / math.sqrt(hd), None)
+        torch.testing.assert_close(first[t + n - 1].cpu().double().view(nh, hd), ref, atol=2e-2, rtol=2e-2)
+        t += n
+    # as in a prompt step, the product that reads the result is launched behind every attention launch: it starts while
+    # the attention kernel still runs, and its waiting warps take issue slots from the attention's warps
+    w_o = rnd(nh * hd, nh * hd, dt=dt, seed=3) * 0.05
+    h = torch.zeros(T, nh * hd, device=DEV)
+    outs = []
+    for rep in range(200):
+        out = kernels.attention_prefill_tc(q, nh, nkv, hd, k_pages, v_pages, *args)
+        tc.gemm_tc(out, w_o, mode=tc.RESIDUAL, out=h)
+        outs.append(out)
+        if len(outs) == 50:                              # compared in batches, so that the launches follow each other closely
+            differ = sum(int(not torch.equal(o, first)) for o in outs)
+            assert differ == 0, f"{differ} of 50 launches gave other bits than the first"
+            outs = []
+    tc.check_status(DEV)
+
+
 @pytest.mark.parametrize("kernel", ["mma_sync", "tcgen05"])
 def test_attention_prefill_finds_far_keys_and_the_window_edge(kernel):
     from rocmforge_b200 import kernels

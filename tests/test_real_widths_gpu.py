@@ -113,6 +113,46 @@ def test_real_widths_in_the_three_cuttings(name, tmp_path_factory):
     tc.check_status(m.device)
 
 
+def test_ragged_prompts_give_the_same_bits_run_after_run():
+    """Sixty-four prompts of 16 to 1,024 tokens in steps of up to 16,384 tokens through all 24 layers of the 0.5B shape,
+    run again and again into caches of other sizes and other slots: the logits of every run are those of the first, bit
+    for bit, and no kernel's wait ran out.  (With attention grids of several waves and the device busy layer after layer,
+    the prompt attention once stood still for its wait's limit, or gave other bits, in one run of ten of this batch;
+    two layers, or steps of 2,048 tokens, never showed it.)"""
+    import rocmforge_b200 as rf
+    from rocmforge_b200 import StepRequest
+    from rocmforge_b200.config import Qwen2Config
+    from rocmforge_b200.kernels import tensor_core as tc
+    _made.clear()
+    torch.cuda.empty_cache()
+    raw = {k: v for k, v in WIDTHS["0.5B"].items() if k != "seed"}
+    raw["num_hidden_layers"] = 24
+    m = rf.Model.random(Qwen2Config.from_dict(raw), seed=3, dtype=torch.bfloat16)
+    V = raw["vocab_size"]
+    g = torch.Generator().manual_seed(4)
+    prompts = [random_tokens(V, int(n), 40 + i) for i, n in enumerate(torch.randint(16, 1025, (64,), generator=g).tolist())]
+    first = None
+    for rep in range(60):
+        cache = m.new_cache(max_tokens=sum((len(p) + 64 * (1 + rep % 3)) // 64 * 64 for p in prompts), max_slots=len(prompts))
+        slots = [cache.alloc_slot() for _ in prompts]
+        if rep % 2:
+            slots = slots[::-1]
+        outs, i = [], 0
+        while i < len(prompts):
+            j, t = i, 0
+            while j < len(prompts) and (j == i or t + len(prompts[j]) <= 16384):
+                t += len(prompts[j])
+                j += 1
+            outs.append(m.step(cache, [StepRequest(s, p, [len(p) - 1]) for s, p in zip(slots[i:j], prompts[i:j])]))
+            i = j
+        got = torch.cat(outs)
+        tc.check_status(m.device)
+        if first is None:
+            first = got.clone()
+        assert torch.equal(got, first), f"run {rep} gave other logits than the first"
+        del cache
+
+
 @pytest.mark.parametrize("name", ["7B", "0.5B"])
 def test_real_widths_with_norms_prepared_by_the_product_before_them(name, tmp_path_factory):
     """``Options.fused_norm``: the o and down products of few tokens add their K splits into the stream themselves and
