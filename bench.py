@@ -147,6 +147,12 @@ def random_prompts(n, length, vocab, seed):
     return [torch.randint(0, vocab, (m,), generator=g).tolist() for m in lens]
 
 
+def no_kernel_gave_up(model):
+    """Raise if a bounded wait of a kernel ran out since the last look: a number timed over such a step means nothing."""
+    from rocmforge_b200.kernels import tensor_core
+    tensor_core.check_status(model.device)
+
+
 def prefill_prompts(model, cache, slots, prompts):
     """Bring the prompts into the cache, at most PREFILL_CHUNK tokens a step; the argmax of each last row."""
     from rocmforge_b200 import StepRequest, kernels
@@ -221,6 +227,7 @@ def decode_rate(model, prompts, steps, warmup, check=16):
     torch.cuda.empty_cache()
     checked = check_loop(model, prompts, first, all_ids, check) if check else 0
     torch.cuda.empty_cache()
+    no_kernel_gave_up(model)
     return {"tok_s": batch * steps / (ms / 1e3), "ms_per_step": ms / steps, "launches": launches * steps,
             "mean_ctx": mean_ctx, "t0": t0, "t1": t1, "checked_steps": checked}
 
@@ -336,6 +343,7 @@ def e2e_rate(llm, prompts, steps, temperature=0.0, top_p=1.0, warmup=0):
     out = llm.generate(prompts, max_tokens=warmup + steps + 1, temperature=temperature, top_p=top_p, stop_token_ids=[],
                        on_token=on_token)
     torch.cuda.synchronize()
+    no_kernel_gave_up(llm.model)
     stamps = stamps[warmup:]
     n = len(stamps) - 1
     dt = stamps[-1] - stamps[0]
@@ -366,6 +374,7 @@ def prefill_rate(model, tokens, repeats, seed):
     times.sort()
     del cache
     torch.cuda.empty_cache()
+    no_kernel_gave_up(model)
     return times[len(times) // 2]
 
 
