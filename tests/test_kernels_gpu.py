@@ -536,11 +536,14 @@ def test_attention_prefill_finds_far_keys_and_the_window_edge(kernel):
     assert (out[0] - vs[0][699, 0].float()).abs().max() > 0.1
 
 
-def test_rope_kv_write_from_partial_sums():
-    """The rotation kernel adds the 32-bit partial sums of a K-split product and the bias itself."""
+@pytest.mark.parametrize("nh,nkv,hd,S", [(6, 2, 32, 3), (28, 4, 128, 8), (14, 2, 64, 19), (5, 1, 24, 9), (3, 1, 20, 4),
+                                         (40, 8, 128, 11)])
+def test_rope_kv_write_from_partial_sums(nh, nkv, hd, S):
+    """The rotation kernel adds the 32-bit partial sums of a K-split product and the bias itself: up to eight splits in
+    one round of loads, more in several; head sizes that are and are not multiples of 8."""
     from rocmforge_b200 import kernels
     from rocmforge_b200.parts import NeoxRope
-    nh, nkv, hd, T, S = 6, 2, 32, 5, 3
+    T = 5
     width = (nh + 2 * nkv) * hd
     rope = NeoxRope(hd, 1e4); rope.prepare(DEV)
     parts = rnd(S, T, width, seed=1)
