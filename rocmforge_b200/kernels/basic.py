@@ -69,10 +69,12 @@ def add_rmsnorm(h: torch.Tensor, weight: torch.Tensor, eps: float, compute_dtype
         n_rows = rows.shape[0]
     if out is None:
         out = torch.empty((n_rows, H), dtype=compute_dtype, device=h.device)
+    from .tensor_core import status_word
     f = _f("elementwise", "rf_add_rmsnorm", c_int, c_void_p, c_void_p, c_int, c_int, c_ll, c_void_p, c_int,
-           c_float, c_void_p, c_void_p, c_int, c_int, c_void_p)
+           c_float, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p)
     check(f(dtype_code(compute_dtype), ptr(h), ptr(pending), kind, n_pending, pstride, ptr(weight),
-            int(weight.dtype == torch.float32), float(eps), ptr(out), ptr(rows), n_rows, H, stream()),
+            int(weight.dtype == torch.float32), float(eps), ptr(out), ptr(rows), n_rows, H,
+            ptr(status_word(h.device)), stream()),
           f"add_rmsnorm (H={H})")
     return out
 
